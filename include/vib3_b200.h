@@ -1,0 +1,182 @@
+/*
+ * C ABI of libvib3_cuda.so — the B200 (sm_100a) implementation of the vib3 INT4 MoE decode path.
+ *
+ * Conventions (the reference's, src/compute/cuda_ffi.rs:143-1066, cuda/src/kernels.cu:1040):
+ *   - every launcher returns int: 0 launched; > 0 the cudaError_t of the launch; < 0 refused
+ *     before any launch (VIB3_ERR_*);
+ *   - the last argument of a launcher is a cudaStream_t passed as void* (NULL = default stream);
+ *   - launchers never synchronise, never allocate and keep no state; all pointers are device
+ *     pointers owned by the caller unless stated otherwise.
+ *
+ * INT4 page layout (src/compute/kernels.rs:94-98): `rows` rows of ceil(K/2) code bytes (low
+ * nibble = even column, weight = (nibble - 8) * scale), then `rows` rows of ceil(K/group)
+ * fp16 scales.
+ */
+#ifndef VIB3_B200_H
+#define VIB3_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VIB3_OK 0
+#define VIB3_ERR_UNSUPPORTED (-1)
+#define VIB3_ERR_COUNT (-2)
+#define VIB3_ERR_NULL (-3)
+#define VIB3_ERR_ALIGN (-4)
+#define VIB3_ERR_SHAPE (-5)
+#define VIB3_ERR_RANGE (-6)
+#define VIB3_ERR_STATE (-7)
+
+/* activation dtypes (x_dtype) and router-weight dtypes (w_dtype) */
+#define VIB3_X_F32 0
+#define VIB3_X_F16 1
+#define VIB3_X_BF16 2
+#define VIB3_W_F16 0
+#define VIB3_W_F32 1
+
+/* bits of the device status word written by the paged kernels */
+#define VIB3_STATUS_MISSING_PAGE 1
+#define VIB3_STATUS_BAD_EXPERT 2
+
+/* ── Entry points with the reference's signatures ───────────────────────────────────────── */
+
+/* replaces cuda/src/kernels.cu:1043 (declared at src/compute/cuda_ffi.rs, INT4 partial matmul, fp16 x) */
+int vib3_launch_partial_matmul_int4(const void* x_f16, const void* w_packed, const void* scales, void* y_f16,
+                                    int K, int M_slice, int group_size, void* stream);
+/* replaces cuda/src/kernels.cu:1202 (fp32 x) */
+int vib3_launch_partial_matmul_int4_f32(const void* x_f32, const void* w_packed, const void* scales, void* y_f16,
+                                        int K, int M_slice, int group_size, void* stream);
+/* replaces cuda/src/kernels.cu:1278 (src/compute/cuda_ffi.rs:344-355): y = f16(silu(Wg x) * (Wu x)) */
+int vib3_launch_fused_swiglu_int4_f32(const void* x_f32, const void* up_w, const void* up_s, const void* gate_w,
+                                      const void* gate_s, void* y_f16, int K, int M_slice, int group_size,
+                                      void* stream);
+/* replaces cuda/src/kernels.cu:1069: y = f16(silu(first) * second) */
+int vib3_launch_silu_mul(const void* silu_operand_f16, const void* mul_operand_f16, void* y_f16, int dim,
+                         void* stream);
+/* replace cuda/src/kernels.cu:1108, :1120, :2513: out += w * y */
+int vib3_launch_weighted_accumulate(void* out_f16, const void* y_f16, float w, int dim, void* stream);
+int vib3_launch_weighted_accumulate_f32(void* out_f32, const void* y_f16, float w, int dim, void* stream);
+int vib3_launch_weighted_accumulate_f32_f32(void* out_f32, const void* y_f32, float w, int dim, void* stream);
+/* replaces cuda/src/kernels.cu:1132: acc += layer_out */
+int vib3_launch_residual_add_f32_f32(void* acc_f32, const void* layer_out_f32, int dim, void* stream);
+/* replace cuda/src/kernels.cu:1143 and :1477: logits[e] = W[e,:] . x, W fp16 [E,H] */
+int vib3_launch_router_gemv(const void* x_f16, const void* W_f16, float* scores, int hidden_dim, int num_experts,
+                            void* stream);
+int vib3_launch_router_gemv_f32(const void* x_f32, const void* W_f16, float* scores, int hidden_dim,
+                                int num_experts, void* stream);
+/* replaces cuda/src/kernels.cu:4075: GEMV + scoring + top-k, ids u16[top_k] and weights f32[top_k]
+ * stay on the device.  scoring_mode 0 = softmax, 1 = sigmoid (bias used for selection only).
+ * Unlike the reference's kernel, num_experts need not be a power of two (<= 512). */
+int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_buf, const float* bias_or_null,
+                            unsigned short* out_ids, float* out_weights, int hidden_dim, int num_experts,
+                            int top_k, int scoring_mode, float scaling_factor, void* stream);
+
+/* ── Entry points added for the fused, paged path ───────────────────────────────────────── */
+
+/* Single-launch router (no counterpart signature in the reference; semantics of
+ * run_router_with_scoring_and_bias, src/compute/kernels.rs:2307-2440).  x_dtype VIB3_X_*,
+ * w_dtype VIB3_W_*.  scores_buf: num_experts floats, 2*num_experts when exact_order != 0.
+ * exact_order != 0 makes the selected indices equal to those of the reference's CPU router
+ * (sequential fp32 summation) even for near-tied experts.  workspace: one uint32, zero before
+ * the first call, left zero by every call; calls sharing a workspace must not overlap. */
+int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
+                               const float* bias_or_null, unsigned short* out_ids, float* out_weights,
+                               int hidden_dim, int num_experts, int top_k, int scoring_mode, float scaling_factor,
+                               int normalize, int exact_order, unsigned int* workspace, void* stream);
+
+/* Device page-table entry, one per (expert, segment, page): the device form of ResolvedPage
+ * (src/runtime/query_planner.rs:36-42).  ptr == 0 marks an absent page. */
+typedef struct vib3_page_entry {
+    uint64_t ptr;
+    uint16_t row_start;
+    uint16_t row_count;
+    uint32_t reserved;
+} vib3_page_entry;
+
+/* Whole MoE sublayer for one token in two launches (gate/up + SiLU, then down + weighted
+ * accumulate); replaces the per-page sequence of src/runtime/engine.rs:6094-6107, :6215-6223,
+ * :6290-6296 and the role of vib3_launch_moe_experts_fused_gpu (cuda/src/kernels.cu:5868) for
+ * INT4 weights with several pages per segment.
+ *   page_table   [num_experts][3][pages_per_segment] entries, segment 0 up, 1 gate, 2 down
+ *   shared_pages [3][pages_per_segment] entries of the shared expert, or NULL
+ *   expert_ids / expert_weights   [top_k] on the device (router output)
+ *   act_scratch  (top_k + 1) * expert_hidden_dim fp16 values
+ *   out          [hidden_dim] fp32; overwritten, or added to when out_accumulate != 0
+ *   status       device int that receives VIB3_STATUS_* bits, or NULL */
+int vib3_launch_moe_layer_int4_paged(const void* x, int x_dtype, const void* page_table, int num_experts,
+                                     const void* shared_pages, const unsigned short* expert_ids,
+                                     const float* expert_weights, int top_k, float shared_weight,
+                                     void* act_scratch, float* out, int out_accumulate, int hidden_dim,
+                                     int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
+                                     int rows_per_page_down, int group_size, int* status, void* stream);
+
+/* The two halves of vib3_launch_moe_layer_int4_paged as separate launches, same arguments: the
+ * first writes act_scratch (out is not touched), the second reads it and writes out. */
+int vib3_launch_moe_gate_up_int4_paged(const void* x, int x_dtype, const void* page_table, int num_experts,
+                                       const void* shared_pages, const unsigned short* expert_ids,
+                                       const float* expert_weights, int top_k, float shared_weight,
+                                       void* act_scratch, float* out, int out_accumulate, int hidden_dim,
+                                       int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
+                                       int rows_per_page_down, int group_size, int* status, void* stream);
+int vib3_launch_moe_down_int4_paged(const void* x, int x_dtype, const void* page_table, int num_experts,
+                                    const void* shared_pages, const unsigned short* expert_ids,
+                                    const float* expert_weights, int top_k, float shared_weight, void* act_scratch,
+                                    float* out, int out_accumulate, int hidden_dim, int expert_hidden_dim,
+                                    int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down,
+                                    int group_size, int* status, void* stream);
+
+/* ── Host side: VRAM page pool and query planner (C view of the C++ classes) ────────────── */
+/* Mirrors PageBufferManager's T1 pool + resident snapshot (src/storage/buffer_manager.rs:206-288,
+ * :622-761, :883-899) and QueryPlanner::plan_layer (src/runtime/query_planner.rs:158-272). */
+
+typedef struct vib3_pool vib3_pool;
+
+/* Pool of `capacity_pages` slots of 2 MiB.  device_base == NULL: the pool allocates its slots
+ * with one cudaMalloc; otherwise it adopts caller-owned device memory of capacity_pages * 2 MiB.
+ * Slots are handed out in a pseudo-random order derived from slot_seed (0 = sequential). */
+vib3_pool* vib3_pool_create(void* device_base, size_t capacity_pages, uint64_t slot_seed);
+void vib3_pool_destroy(vib3_pool* pool);
+/* Place a page: picks a free slot, copies nbytes from host memory when host_data != NULL
+ * (otherwise the caller fills the slot itself), records the catalog row range.  Returns the
+ * slot index, or VIB3_ERR_*. */
+long long vib3_pool_load_page(vib3_pool* pool, uint16_t layer, uint16_t expert, uint16_t segment,
+                              uint16_t page_idx, uint16_t row_start, uint16_t row_count, const void* host_data,
+                              size_t nbytes);
+void* vib3_pool_slot_ptr(const vib3_pool* pool, long long slot);
+/* Freeze the page table into the resident snapshot; lookups are only allowed afterwards. */
+int vib3_pool_freeze(vib3_pool* pool);
+/* get_page_resident: VIB3_OK and the handle fields, or VIB3_ERR_RANGE when the page is absent. */
+int vib3_pool_get_page_resident(const vib3_pool* pool, uint64_t page_key, void** device_ptr, uint16_t* row_start,
+                                uint16_t* row_count, uint32_t* size);
+size_t vib3_pool_resident_pages(const vib3_pool* pool);
+/* Build (once per layer, cached) the device page table [num_experts][3][pages_per_segment] and
+ * return its device pointer; shared = 1 builds the [3][pages] block of the shared expert
+ * (expert id 0xFFFF, segments 14/15/16 = up/gate/down, src/storage/convert.rs:2014-2032). */
+int vib3_pool_device_page_table(vib3_pool* pool, uint16_t layer, int num_experts, int pages_per_segment,
+                                int shared, void** device_table);
+uint64_t vib3_page_key(uint16_t layer, uint16_t expert, uint16_t segment, uint16_t page_idx);
+
+/* plan_layer on the resident snapshot: for each (expert, weight) the pages of segments 0,1,2 in
+ * catalog order.  Writes up to max_pages resolved pages and returns their number, or
+ * VIB3_ERR_RANGE if a page is missing (Error::PageNotFound). */
+typedef struct vib3_resolved_page {
+    uint64_t key;
+    void* device_ptr;
+    uint16_t expert_id;
+    uint16_t segment;
+    uint16_t row_start;
+    uint16_t row_count;
+} vib3_resolved_page;
+int vib3_planner_plan_layer(const vib3_pool* pool, uint16_t layer, const uint16_t* expert_ids, int num_active,
+                            int pages_per_segment, vib3_resolved_page* out_pages, int max_pages);
+
+const char* vib3_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VIB3_B200_H */

@@ -1,0 +1,184 @@
+"""The fused MoE sublayer (router -> gate/up+SiLU -> down+accumulate over a device page table)
+against the CPU oracle's restatement of the reference engine's call chain, against the per-page
+call sequence, and against the reference's own CUDA kernels driven in that sequence."""
+import numpy as np
+import pytest
+import torch
+
+from tests.parity import assert_close, load_ref_lib, oracle_experts, ref_moe_sublayer
+
+pytestmark = pytest.mark.gpu
+
+
+def _shapes():
+    from vic_b200.core_types import KIMI, MIXTRAL, SCORING_SIGMOID, SCORING_SOFTMAX, MoeShape
+    tiny = MoeShape("tiny", 64, 96, 4, 2, 1, SCORING_SOFTMAX, 1.0, True)
+    # several ragged pages per segment at small size: gate/up 3640+360 rows, down 932+92 rows
+    mid = MoeShape("mid", 1024, 4000, 6, 3, 1, SCORING_SIGMOID, 2.5, True)
+    noshared = MoeShape("noshared", 256, 512, 8, 2, 0, SCORING_SOFTMAX, 1.0, True)
+    return {"tiny": tiny, "mid": mid, "noshared": noshared, "kimi": KIMI, "mixtral": MIXTRAL}
+
+
+_cache = {}
+
+
+def _model(name, dev, seed=1234, slot_seed=99):
+    from vic_b200.synth import build_synthetic_moe
+    key = (name, seed, slot_seed)
+    if key not in _cache:
+        _cache.clear()  # one big model resident at a time
+        torch.cuda.empty_cache()
+        _cache[key] = build_synthetic_moe(_shapes()[name], 1, dev, seed=seed, slot_seed=slot_seed)
+    return _cache[key]
+
+
+@pytest.mark.parametrize("name,xdt,ntok", [
+    ("tiny", torch.float16, 4), ("tiny", torch.float32, 2), ("noshared", torch.bfloat16, 3),
+    ("mid", torch.bfloat16, 3), ("mid", torch.float32, 2),
+    ("mixtral", torch.float16, 2), ("kimi", torch.bfloat16, 3), ("kimi", torch.float32, 1),
+])
+def test_fused_layer_vs_oracle(cuda_dev, oracle, name, xdt, ntok):
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import synth_activation
+    model = _model(name, cuda_dev)
+    sh = model.shape
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(1234 + ntok)
+    xs = synth_activation(sh, g, cuda_dev, xdt, ntok)
+    Wn = model.router_w[0].cpu().numpy()
+    for t in range(ntok):
+        out = dec.forward_layer(0, xs[t]).cpu().numpy()
+        torch.cuda.synchronize()
+        assert int(dec.status.item()) == 0
+        ids, w = dec.routing()
+        x32 = xs[t].float().cpu().numpy()
+        oi, ow, _ = oracle.router(x32, Wn, sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, None, oracle.ORDER_SEQUENTIAL)
+        assert np.array_equal(ids, oi)
+        assert np.allclose(w, ow, rtol=1e-5)
+        want = oracle.moe_layer(x32, oracle_experts(oracle, model, 0, list(zip(oi.tolist(), ow.tolist()))), sh.hidden,
+                                sh.intermediate, oracle.SCALE_FP16, order="gpu")
+        assert_close(out, want, f"{name} {xdt} token {t}")
+        assert np.all(np.isfinite(out))
+
+
+def test_accumulate_into_residual(cuda_dev):
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import synth_activation
+    model = _model("mid", cuda_dev)
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(5)
+    x = synth_activation(model.shape, g, cuda_dev, torch.bfloat16, 1)[0]
+    base = dec.forward_layer(0, x).clone()
+    resid = torch.randn(model.shape.hidden, device=cuda_dev, dtype=torch.float32)
+    want = resid + base
+    dec.forward_layer(0, x, out=resid, accumulate=True)
+    assert torch.equal(resid, want)
+
+
+def test_paged_equals_contiguous_bit_for_bit(cuda_dev):
+    """Same page contents, different slots: scattered pool vs back-to-back pool give identical bits."""
+    from vic_b200.buffer_manager import PageBufferManager
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import SyntheticMoe, synth_activation
+    for name in ("mid", "kimi"):
+        model = _model(name, cuda_dev)
+        sh = model.shape
+        dec = MoeDecoder(model)
+        g = torch.Generator(device=cuda_dev).manual_seed(8)
+        xs = synth_activation(sh, g, cuda_dev, torch.bfloat16, 2)
+        outs, routes = [], []
+        for t in range(2):
+            outs.append(dec.forward_layer(0, xs[t]).clone())
+            routes.append(dec.routing()[0].tolist())
+        needed = sorted(set(sum(routes, []))) + [0xFFFF]
+        pages = [p for p in model.pages if p.pid.expert in needed]
+        for slot_seed in (0, 4242):
+            pool2 = PageBufferManager(len(pages), device=cuda_dev, slot_seed=slot_seed)
+            for p in pages:
+                s2 = pool2.load_page(p.pid, p.row_start, p.row_count, None, p.nbytes)
+                pool2.slot_view(s2, p.nbytes).copy_(model.pool.slot_view(p.slot, p.nbytes))
+            pool2.freeze()
+            m2 = SyntheticMoe(sh, 1, pool2, model.router_w, pages)
+            dec2 = MoeDecoder(m2)
+            for t in range(2):
+                o2 = dec2.forward_layer(0, xs[t])
+                assert int(dec2.status.item()) == 0
+                assert torch.equal(o2, outs[t]), f"{name} slot_seed={slot_seed} token {t}"
+
+
+def test_missing_page_sets_status_and_does_not_fault(cuda_dev):
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import build_synthetic_moe, synth_activation
+    sh = _shapes()["noshared"]
+    model = build_synthetic_moe(sh, 1, cuda_dev, seed=3, slot_seed=5, experts=[0, 1, 2])  # experts 3..7 absent
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(2)
+    hit_missing = False
+    for t in range(12):
+        x = synth_activation(sh, g, cuda_dev, torch.bfloat16, 1)[0]
+        dec.status.zero_()
+        out = dec.forward_layer(0, x)
+        torch.cuda.synchronize()
+        ids = dec.routing()[0]
+        assert torch.isfinite(out).all()
+        if any(int(e) > 2 for e in ids):
+            hit_missing = True
+            assert int(dec.status.item()) & 1
+        else:
+            assert int(dec.status.item()) == 0
+    assert hit_missing
+    # the host planner reports the same condition as an error before any launch
+    from vic_b200.buffer_manager import QueryPlanner
+    from vic_b200.lib import Vib3Error
+    with pytest.raises(Vib3Error):
+        QueryPlanner(model.pool, sh.pages_per_segment).plan_layer(0, [(5, 1.0)])
+
+
+def test_fused_vs_per_page_sequence_and_reference_kernels(cuda_dev, oracle):
+    from vic_b200.buffer_manager import QueryPlanner
+    from vic_b200.moe import MoeDecoder, run_moe_sublayer_paged_calls
+    from vic_b200.synth import synth_activation
+    ref = load_ref_lib()
+    for name in ("mid", "kimi"):
+        model = _model(name, cuda_dev)
+        sh = model.shape
+        dec = MoeDecoder(model, exact_order=False)
+        planner = QueryPlanner(model.pool, sh.pages_per_segment)
+        g = torch.Generator(device=cuda_dev).manual_seed(31)
+        x = synth_activation(sh, g, cuda_dev, torch.bfloat16, 1)[0]
+        x32 = x.float()
+        w16 = model.router_w[0].to(torch.float16)
+        seq_out, activation, launches = run_moe_sublayer_paged_calls(model, 0, x32, planner, w16)
+        # drive the fused experts with the same routing
+        k = sh.top_k
+        dec.ids[:k] = torch.tensor([e for e, _ in activation], dtype=torch.int32).to(torch.int16).to(cuda_dev)
+        dec.weights[:k] = torch.tensor([w for _, w in activation], dtype=torch.float32, device=cuda_dev)
+        fused = dec.experts(0, x).clone()
+        torch.cuda.synchronize()
+        assert_close(fused.cpu().numpy(), seq_out.cpu().numpy(), f"{name}: fused vs per-page sequence")
+        per_expert = 3 * sh.gate_up.num_pages + sh.down.num_pages + 1
+        assert launches == 2 + (k + sh.shared_experts) * per_expert
+        if ref is not None:
+            ref_out, ref_launches = ref_moe_sublayer(ref, model, 0, x32, activation, planner)
+            torch.cuda.synchronize()
+            assert_close(fused.cpu().numpy(), ref_out.cpu().numpy(), f"{name}: fused vs reference kernels")
+            assert_close(seq_out.cpu().numpy(), ref_out.cpu().numpy(), f"{name}: per-page vs reference kernels")
+
+
+def test_fused_launcher_refusals(cuda_dev):
+    from vic_b200.lib import lib
+    L = lib()
+    t = torch.zeros(4096, dtype=torch.float32, device=cuda_dev)
+    p = t.data_ptr()
+    ok = dict(x=p, xd=2, tab=p, E=8, sh=None, ids=p, w=p, k=2, sw=1.0, act=p, out=p, acc=0, H=256, I=512, P=1, rg=512, rd=256, g=32, st=None, s=None)
+    def call(**kw):
+        a = {**ok, **kw}
+        return L.vib3_launch_moe_layer_int4_paged(a["x"], a["xd"], a["tab"], a["E"], a["sh"], a["ids"], a["w"], a["k"], a["sw"], a["act"],
+                                                  a["out"], a["acc"], a["H"], a["I"], a["P"], a["rg"], a["rd"], a["g"], a["st"], a["s"])
+    assert call(x=None) == -3 and call(tab=None) == -3 and call(out=None) == -3 and call(act=None) == -3
+    assert call(g=128) == -1 and call(xd=7) == -1
+    assert call(H=250) == -5 and call(I=0) == -5
+    assert call(k=17) == -2 and call(k=0) == -2 and call(P=17) == -2 and call(E=0) == -2
+    assert call(rg=100) == -5            # pages cannot cover the matrix: row range out of [0, M)
+    assert call(tab=p + 8) == -4
+    torch.cuda.synchronize()

@@ -1,0 +1,166 @@
+"""Router: logits bit-identical to the reference CUDA kernel's summation order, top-k indices
+bit-exact against the reference's CPU router (sequential order), ties, bias, refusals."""
+import numpy as np
+import pytest
+import torch
+
+from tests.parity import load_ref_lib
+
+pytestmark = pytest.mark.gpu
+
+
+class _Router:
+    def __init__(self, dev, E):
+        self.dev = dev
+        self.scores = torch.zeros(2 * E, dtype=torch.float32, device=dev)
+        self.ids = torch.zeros(16, dtype=torch.int16, device=dev)
+        self.w = torch.zeros(16, dtype=torch.float32, device=dev)
+        self.ws = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def run(self, x, W, k, mode, scaling, normalize=True, bias=None, exact=True):
+        from vic_b200 import kernels
+        kernels.router_topk_ex(x, W, self.scores, bias, self.ids, self.w, k, mode, scaling, normalize, exact, self.ws)
+        torch.cuda.synchronize()
+        assert int(self.ws[0].item()) == 0
+        E = W.shape[0]
+        return (self.ids[:k].cpu().numpy().view(np.uint16).copy(), self.w[:k].cpu().numpy().copy(),
+                self.scores[:E].cpu().numpy().copy())
+
+
+def test_logits_bit_identical_to_reference_order(cuda_dev, oracle):
+    from vic_b200 import kernels
+    g = torch.Generator(device="cpu").manual_seed(21)
+    for E, H in [(8, 4096), (384, 7168), (5, 200)]:
+        x = torch.randn(H, generator=g)
+        W = torch.randn(E, H, generator=g) * 0.02
+        W16 = W.to(torch.float16)
+        scores = torch.zeros(E, dtype=torch.float32, device=cuda_dev)
+        kernels.router_gemv_f32(x.to(cuda_dev), W16.to(cuda_dev), scores, H, E)
+        want = oracle.router_logits(x.numpy(), W16.numpy(), oracle.ORDER_GPU128)
+        assert np.array_equal(scores.cpu().numpy().view(np.uint32), want.view(np.uint32))
+        ref = load_ref_lib()
+        if ref is not None:
+            theirs = torch.zeros(E, dtype=torch.float32, device=cuda_dev)
+            xd, wd = x.to(cuda_dev), W16.to(cuda_dev)
+            assert ref.vib3_launch_router_gemv_f32(xd.data_ptr(), wd.data_ptr(), theirs.data_ptr(), H, E,
+                                                   torch.cuda.current_stream().cuda_stream) == 0
+            torch.cuda.synchronize()
+            assert np.array_equal(scores.cpu().numpy().view(np.uint32), theirs.cpu().numpy().view(np.uint32))
+        # fp32 router weights, bf16 activations (the benchmark's configuration)
+        r = _Router(cuda_dev, E)
+        xb = x.to(torch.bfloat16)
+        _, _, lg = r.run(xb.to(cuda_dev), W.to(cuda_dev), min(2, E), 1, 1.0, exact=False)
+        want = oracle.router_logits(xb.float().numpy(), W.numpy(), oracle.ORDER_GPU128)
+        assert np.array_equal(lg.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("name,E,H,k,mode,scaling,xdt,ntok", [
+    ("mixtral", 8, 4096, 2, 0, 1.0, torch.float16, 3000),
+    ("kimi", 384, 7168, 8, 1, 2.827, torch.bfloat16, 10000),
+])
+def test_topk_indices_bit_exact_vs_cpu_router(cuda_dev, oracle, name, E, H, k, mode, scaling, xdt, ntok):
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    W = torch.randn(E, H, generator=g) * 0.02
+    Wd = W.to(cuda_dev)
+    Wn = W.numpy()
+    r = _Router(cuda_dev, E)
+    xs = torch.randn(ntok, H, generator=g).to(xdt)
+    xs_d = xs.to(cuda_dev)
+    xs_n = xs.float().numpy()
+    mismatches_same_order = 0
+    max_w_rel = 0.0
+    for t in range(ntok):
+        ids, w, _ = r.run(xs_d[t], Wd, k, mode, scaling, exact=True)
+        oi, ow, _ = oracle.router(xs_n[t], Wn, k, mode, scaling, True, None, oracle.ORDER_SEQUENTIAL)
+        assert np.array_equal(ids, oi), f"{name} token {t}: {ids} vs {oi}"
+        max_w_rel = max(max_w_rel, float(np.max(np.abs(w - ow) / np.abs(ow))))
+        if t < 500:
+            ids2, _, _ = r.run(xs_d[t], Wd, k, mode, scaling, exact=False)
+            oi2, _, _ = oracle.router(xs_n[t], Wn, k, mode, scaling, True, None, oracle.ORDER_GPU128)
+            mismatches_same_order += int(not np.array_equal(ids2, oi2))
+    assert mismatches_same_order == 0
+    assert max_w_rel < 1e-5
+
+
+def test_ties_and_near_ties(cuda_dev, oracle):
+    g = torch.Generator(device="cpu").manual_seed(9)
+    E, H, k = 384, 7168, 8
+    W = torch.randn(E, H, generator=g) * 0.02
+    x = torch.randn(H, generator=g).to(torch.bfloat16)
+    base = oracle.router_logits(x.float().numpy(), W.numpy(), oracle.ORDER_SEQUENTIAL)
+    top = np.argsort(-base)[:k]
+    # exact ties: duplicate the rows of the best three experts into higher and lower indices
+    W[300] = W[top[0]]
+    W[2] = W[top[1]]
+    # near ties: the same row with its columns summed in another order (a permutation of x and w together
+    # is not available to the router, so instead nudge one weight by one ulp-scale amount)
+    W[77] = W[top[2]]
+    W[77, 5] += 1e-9
+    r = _Router(cuda_dev, E)
+    for mode, scaling in [(1, 2.827), (0, 1.0)]:
+        ids, w, _ = r.run(x.to(cuda_dev), W.to(cuda_dev), k, mode, scaling, exact=True)
+        oi, ow, _ = oracle.router(x.float().numpy(), W.numpy(), k, mode, scaling, True, None, oracle.ORDER_SEQUENTIAL)
+        assert np.array_equal(ids, oi)
+        assert np.allclose(w, ow, rtol=1e-5)
+    # all-equal rows: lowest indices win in order
+    W2 = W[:1].repeat(16, 1)
+    ids, w, _ = _Router(cuda_dev, 16).run(x.to(cuda_dev), W2.to(cuda_dev), 4, 1, 1.0)
+    assert ids.tolist() == [0, 1, 2, 3]
+
+
+def test_selection_bias_and_flags(cuda_dev, oracle):
+    g = torch.Generator(device="cpu").manual_seed(4)
+    E, H, k = 384, 7168, 8
+    W = torch.randn(E, H, generator=g) * 0.02
+    bias = (torch.randn(E, generator=g) * 0.1).float()
+    r = _Router(cuda_dev, E)
+    for t in range(50):
+        x = torch.randn(H, generator=g).to(torch.bfloat16)
+        for normalize in (True, False):
+            ids, w, _ = r.run(x.to(cuda_dev), W.to(cuda_dev), k, 1, 2.827, normalize, bias.to(cuda_dev))
+            oi, ow, _ = oracle.router(x.float().numpy(), W.numpy(), k, 1, 2.827, normalize, bias.numpy(), oracle.ORDER_SEQUENTIAL)
+            assert np.array_equal(ids, oi)
+            assert np.allclose(w, ow, rtol=1e-5)
+
+
+def test_reference_signature_topk(cuda_dev, oracle):
+    """vib3_launch_router_topk with the reference's signature; for E=8 also against the reference's own kernel."""
+    from vic_b200 import kernels
+    g = torch.Generator(device="cpu").manual_seed(77)
+    ref = load_ref_lib()
+    for E, H, k, mode, scaling in [(8, 4096, 2, 0, 1.0), (384, 7168, 8, 1, 2.827), (256, 2048, 8, 1, 1.0)]:
+        W16 = (torch.randn(E, H, generator=g) * 0.02).to(torch.float16)
+        x = torch.randn(H, generator=g)
+        scores = torch.zeros(E, dtype=torch.float32, device=cuda_dev)
+        ids = torch.zeros(16, dtype=torch.int16, device=cuda_dev)
+        ws = torch.zeros(16, dtype=torch.float32, device=cuda_dev)
+        act = kernels.run_router_gpu_topk(x.to(cuda_dev), W16.to(cuda_dev), scores, None, ids, ws, H, E, k, mode, scaling)
+        oi, ow, _ = oracle.router(x.numpy(), W16.numpy(), k, mode, scaling, True, None, oracle.ORDER_GPU128)
+        assert [e for e, _ in act] == oi.tolist()
+        assert np.allclose([w for _, w in act], ow, rtol=1e-5)
+        if ref is not None and (E & (E - 1)) == 0:
+            xd, wd = x.to(cuda_dev), W16.to(cuda_dev)
+            s2 = torch.zeros(E, dtype=torch.float32, device=cuda_dev)
+            i2 = torch.zeros(16, dtype=torch.int16, device=cuda_dev)
+            w2 = torch.zeros(16, dtype=torch.float32, device=cuda_dev)
+            assert ref.vib3_launch_router_topk(xd.data_ptr(), wd.data_ptr(), s2.data_ptr(), None, i2.data_ptr(), w2.data_ptr(),
+                                               H, E, k, mode, scaling, torch.cuda.current_stream().cuda_stream) == 0
+            torch.cuda.synchronize()
+            assert i2[:k].cpu().numpy().view(np.uint16).tolist() == [e for e, _ in act]
+            assert np.allclose(w2[:k].cpu().numpy(), [w for _, w in act], rtol=2e-4)
+
+
+def test_router_refusals(cuda_dev):
+    from vic_b200.lib import lib
+    L = lib()
+    t = torch.zeros(4096, dtype=torch.float32, device=cuda_dev)
+    p = t.data_ptr()
+    assert L.vib3_launch_router_topk(p, p, p, None, p, p, 64, 8, 9, 0, 1.0, None) == -2      # top_k > E
+    assert L.vib3_launch_router_topk(p, p, p, None, p, p, 64, 8, 0, 0, 1.0, None) == -2
+    assert L.vib3_launch_router_topk(p, p, p, None, p, p, 4, 513, 2, 0, 1.0, None) == -2    # > MAX_EXPERTS
+    assert L.vib3_launch_router_topk(p, p, p, None, p, p, 64, 8, 17, 0, 1.0, None) == -2    # > MAX_ACTIVE_EXPERTS
+    assert L.vib3_launch_router_topk(None, p, p, None, p, p, 64, 8, 2, 0, 1.0, None) == -3
+    assert L.vib3_launch_router_topk(p, p, p, None, p, p, 64, 8, 2, 2, 1.0, None) == -1     # unknown scoring mode
+    assert L.vib3_launch_router_topk_ex(p, 0, p, 1, p, None, p, p, 64, 8, 2, 0, 1.0, 1, 1, None, None) == -3  # no workspace
+    assert L.vib3_launch_router_topk_ex(p, 5, p, 1, p, None, p, p, 64, 8, 2, 0, 1.0, 1, 1, p, None) == -1
+    torch.cuda.synchronize()

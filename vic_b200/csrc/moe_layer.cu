@@ -1,0 +1,347 @@
+// Batch-1 MoE sublayer over buffer-manager pages: two launches for the whole layer.
+//
+//   gate/up kernel : for every selected expert (plus the shared expert) and every row of its
+//                    gate and up matrices: act = f16( silu(f16(Wg x)) * f16(Wu x) )
+//   down kernel    : out[r] = sum over experts, in plan order, of w_e * f16(Wd_e[r,:] . act_e)
+//
+// This replaces the reference's per-page launch sequence for INT4 experts
+// (src/runtime/engine.rs:6094-6107, :6215-6223, :6290-6296; src/compute/kernels.rs:493-541):
+// about 150 launches per layer there, 2 here, with the same rounding points (fp16 after each
+// projection and after the SiLU product, fp32 accumulation across experts).
+//
+// Pages are addressed through a device page table: entry [expert][segment][page] holds the
+// page's device pointer and row range (segment 0 = up, 1 = gate, 2 = down,
+// src/core/types.rs:204).  The experts of the token are read from device memory (router
+// output), so no host synchronisation sits between the router and the experts.
+#include "int4_math.cuh"
+#include "launch_common.h"
+
+namespace vib3 {
+
+constexpr int kMaxSlots = 17;   // MAX_ACTIVE_EXPERTS (src/core/types.rs:26) + one shared expert
+constexpr int kMaxPages = 16;   // pages per segment the kernels accept (Mixtral-shape needs 16)
+constexpr int kSegUp = 0, kSegGate = 1, kSegDown = 2;
+
+struct MoeLayerArgs {
+    const void* x;                 // [H] activations
+    int x_dtype;                   // XDType
+    const PageEntry* page_table;   // [num_experts][3][P]
+    const PageEntry* shared_pages; // [3][P] or null
+    const unsigned short* expert_ids;  // [top_k], device
+    const float* expert_weights;       // [top_k], device
+    int top_k;
+    int num_experts;
+    float shared_weight;
+    __half* act;                   // [slots][I] scratch
+    float* out;                    // [H]
+    int out_accumulate;            // 0: out = layer output; 1: out += layer output (residual add)
+    int H, I, P;
+    int rpp_gu, rpp_dn;            // rows per page of gate/up and of down
+    int* status;                   // device status word, or null
+};
+
+enum StatusBits : int { kStatusMissingPage = 1, kStatusBadExpert = 2 };
+
+__device__ __forceinline__ void flag(int* status, int bit) {
+    if (status) atomicOr(status, bit);
+}
+
+// Resolve the page-table block ([3][P] entries) of slot s: routed expert or the shared expert.
+__device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, int s) {
+    if (s < a.top_k) {
+        unsigned e = a.expert_ids[s];
+        if (e >= (unsigned)a.num_experts) return nullptr;
+        return a.page_table + (size_t)e * 3 * a.P;
+    }
+    return a.shared_pages;
+}
+
+// ── gate/up + SiLU ─────────────────────────────────────────────────────────────────────────
+// One warp per (slot, row).  Lane l takes chunks l, l+32, ... of the row: one 16-byte load of
+// codes and one 2-byte scale per chunk for gate and for up; B chunks per lane are requested
+// before any is consumed.
+template <class MATH, int B>
+__global__ void __launch_bounds__(256, 2) moe_gateup_kernel(MoeLayerArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    typename MATH::XS* xs = reinterpret_cast<typename MATH::XS*>(smem_raw);
+    const int nchunks = a.H / kGroupSize;
+    PageEntry* tab = reinterpret_cast<PageEntry*>(smem_raw + (size_t)nchunks * MATH::kStride * sizeof(typename MATH::XS));
+    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+
+    // page entries of gate and up for every slot: tab[(s*2 + seg)*P + p], seg 0 = up, 1 = gate
+    for (int i = threadIdx.x; i < slots * 2 * a.P; i += blockDim.x) {
+        const int s = i / (2 * a.P), rem = i % (2 * a.P);
+        const PageEntry* pg = slot_pages(a, s);
+        PageEntry e{0, 0, 0, 0};
+        if (pg) e = pg[rem];  // segments 0 and 1 are the first 2*P entries
+        else if (rem == 0) flag(a.status, kStatusBadExpert);
+        tab[i] = e;
+    }
+    stage_x<MATH>(xs, a.x, a.x_dtype, a.H, threadIdx.x, blockDim.x);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int total_rows = slots * a.I;
+    const size_t code_row_bytes = (size_t)a.H / 2;
+    const int scale_row = nchunks;  // u16 per row
+
+    for (int g = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); g < total_rows; g += gridDim.x * warps_per_cta) {
+        const int s = g / a.I, row = g - s * a.I;
+        const int p = row / a.rpp_gu, rin = row - p * a.rpp_gu;
+        const PageEntry eu = tab[(s * 2 + kSegUp) * a.P + p];
+        const PageEntry eg = tab[(s * 2 + kSegGate) * a.P + p];
+        float acc[2] = {0.f, 0.f};  // [0] gate, [1] up
+        if (eu.ptr != 0 && eg.ptr != 0 && rin < eu.row_count && rin < eg.row_count) {
+            const unsigned char* gbase = reinterpret_cast<const unsigned char*>(eg.ptr);
+            const unsigned char* ubase = reinterpret_cast<const unsigned char*>(eu.ptr);
+            const uint4* gcodes = reinterpret_cast<const uint4*>(gbase + (size_t)rin * code_row_bytes);
+            const uint4* ucodes = reinterpret_cast<const uint4*>(ubase + (size_t)rin * code_row_bytes);
+            const unsigned short* gsc = reinterpret_cast<const unsigned short*>(gbase + (size_t)eg.row_count * code_row_bytes) + (size_t)rin * scale_row;
+            const unsigned short* usc = reinterpret_cast<const unsigned short*>(ubase + (size_t)eu.row_count * code_row_bytes) + (size_t)rin * scale_row;
+            for (int c0 = lane; c0 < nchunks; c0 += 32 * B) {
+                uint4 q[B][2];
+                unsigned short sc[B][2];
+#pragma unroll
+                for (int i = 0; i < B; ++i) {
+                    const int c = c0 + 32 * i;
+                    if (c < nchunks) {
+                        q[i][0] = ldg_stream16(gcodes + c);
+                        q[i][1] = ldg_stream16(ucodes + c);
+                        sc[i][0] = ldg_stream2(gsc + c);
+                        sc[i][1] = ldg_stream2(usc + c);
+                    } else {
+                        q[i][0] = q[i][1] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+                        sc[i][0] = sc[i][1] = 0;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < B; ++i) {
+                    const int c = min(c0 + 32 * i, nchunks - 1);
+                    const float s2[2] = {scale_to_f32(sc[i][0]), scale_to_f32(sc[i][1])};
+                    MATH::template chunk<2>(q[i], s2, xs + (size_t)c * MATH::kStride, acc);
+                }
+            }
+        } else if (lane == 0) {
+            flag(a.status, kStatusMissingPage);
+        }
+        const float gsum = warp_sum(acc[0]);
+        const float usum = warp_sum(acc[1]);
+        if (lane == 0) {
+            // the reference rounds each projection to fp16 before silu_mul, and its result again
+            const float g16 = __half2float(__float2half_rn(gsum));
+            const float u16 = __half2float(__float2half_rn(usum));
+            a.act[(size_t)s * a.I + row] = __float2half_rn(silu_mul_f32(g16, u16));
+        }
+    }
+}
+
+// ── down + routing weight + accumulate ─────────────────────────────────────────────────────
+// One warp per output row r, all slots: y_s = f16(Wd_s[r,:] . act_s), out[r] = sum_s w_s * y_s
+// accumulated in plan order, so the result does not depend on scheduling.
+template <int B, int SB>
+__global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
+    using MATH = MathF16;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+    const int nchunks = a.I / kGroupSize;
+    __half* acts = reinterpret_cast<__half*>(smem_raw);  // [slots][nchunks * kStride]
+    PageEntry* tab = reinterpret_cast<PageEntry*>(smem_raw + (size_t)slots * nchunks * MATH::kStride * sizeof(__half));
+    float* wts = reinterpret_cast<float*>(tab + slots * a.P);
+
+    for (int i = threadIdx.x; i < slots * a.P; i += blockDim.x) {
+        const int s = i / a.P, p = i - s * a.P;
+        const PageEntry* pg = slot_pages(a, s);
+        PageEntry e{0, 0, 0, 0};
+        if (pg) e = pg[kSegDown * a.P + p];
+        tab[i] = e;
+    }
+    for (int s = threadIdx.x; s < slots; s += blockDim.x) wts[s] = s < a.top_k ? a.expert_weights[s] : a.shared_weight;
+    for (int s = 0; s < slots; ++s)
+        stage_x<MATH>(acts + (size_t)s * nchunks * MATH::kStride, a.act + (size_t)s * a.I, X_F16, a.I, threadIdx.x, blockDim.x);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const size_t code_row_bytes = (size_t)a.I / 2;
+    const uint4 kZeroCodes = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+
+    for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < a.H; r += gridDim.x * warps_per_cta) {
+        const int p = r / a.rpp_dn, rin = r - p * a.rpp_dn;
+        float out = 0.f;
+        for (int s0 = 0; s0 < slots; s0 += SB) {
+            // SB slots at a time: SB*B independent 16-byte loads per lane are requested before use
+            const uint4* codes[SB];
+            const unsigned short* sc[SB];
+            float acc[SB];
+#pragma unroll
+            for (int ss = 0; ss < SB; ++ss) {
+                acc[ss] = 0.f;
+                codes[ss] = nullptr;
+                sc[ss] = nullptr;
+                if (s0 + ss < slots) {
+                    const PageEntry e = tab[(s0 + ss) * a.P + p];
+                    if (e.ptr != 0 && rin < e.row_count) {
+                        const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
+                        codes[ss] = reinterpret_cast<const uint4*>(base + (size_t)rin * code_row_bytes);
+                        sc[ss] = reinterpret_cast<const unsigned short*>(base + (size_t)e.row_count * code_row_bytes) + (size_t)rin * nchunks;
+                    } else if (lane == 0) {
+                        flag(a.status, kStatusMissingPage);
+                    }
+                }
+            }
+            for (int c0 = lane; c0 < nchunks; c0 += 32 * B) {
+                uint4 q[SB][B];
+                unsigned short sb[SB][B];
+#pragma unroll
+                for (int ss = 0; ss < SB; ++ss) {
+#pragma unroll
+                    for (int i = 0; i < B; ++i) {
+                        const int c = c0 + 32 * i;
+                        if (codes[ss] != nullptr && c < nchunks) {
+                            q[ss][i] = ldg_stream16(codes[ss] + c);
+                            sb[ss][i] = ldg_stream2(sc[ss] + c);
+                        } else {
+                            q[ss][i] = kZeroCodes;
+                            sb[ss][i] = 0;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int ss = 0; ss < SB; ++ss) {
+                    const __half* xs = acts + (size_t)min(s0 + ss, slots - 1) * nchunks * MATH::kStride;
+#pragma unroll
+                    for (int i = 0; i < B; ++i) {
+                        const int c = min(c0 + 32 * i, nchunks - 1);
+                        const uint4 q1[1] = {q[ss][i]};
+                        const float s1[1] = {scale_to_f32(sb[ss][i])};
+                        float a1[1] = {acc[ss]};
+                        MATH::template chunk<1>(q1, s1, xs + (size_t)c * MATH::kStride, a1);
+                        acc[ss] = a1[0];
+                    }
+                }
+            }
+#pragma unroll
+            for (int ss = 0; ss < SB; ++ss) {
+                const float y = warp_sum(acc[ss]);
+                // fp16 rounding of the down projection, then out += w * y (cuda/src/kernels.cu:803-813)
+                if (s0 + ss < slots) out = fmaf(wts[s0 + ss], __half2float(__float2half_rn(y)), out);
+            }
+        }
+        if (lane == 0) {
+            if (a.out_accumulate) a.out[r] += out;
+            else a.out[r] = out;
+        }
+    }
+}
+
+// ── host side ──────────────────────────────────────────────────────────────────────────────
+
+static int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v > 0 ? v : 148;
+    }();
+    return n;
+}
+
+template <class K>
+static int ensure_smem(K kernel, size_t bytes) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
+template <class MATH, int B>
+static int launch_gateup(const MoeLayerArgs& a, cudaStream_t st) {
+    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+    const size_t smem = (size_t)(a.H / kGroupSize) * MATH::kStride * sizeof(typename MATH::XS) + (size_t)slots * 2 * a.P * sizeof(PageEntry);
+    if (int e = ensure_smem(moe_gateup_kernel<MATH, B>, smem)) return e;
+    const int total_rows = slots * a.I;
+    int grid = min(2 * sm_count(), (total_rows + 7) / 8);
+    moe_gateup_kernel<MATH, B><<<grid, 256, smem, st>>>(a);
+    return (int)cudaGetLastError();
+}
+
+template <int B, int SB>
+static int launch_down(const MoeLayerArgs& a, cudaStream_t st) {
+    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+    const size_t smem = (size_t)slots * (a.I / kGroupSize) * kXStrideH * sizeof(__half) + (size_t)slots * a.P * sizeof(PageEntry) + slots * sizeof(float);
+    if (int e = ensure_smem(moe_down_kernel<B, SB>, smem)) return e;
+    int grid = min(sm_count(), (a.H + 11) / 12);
+    moe_down_kernel<B, SB><<<grid, 384, smem, st>>>(a);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace vib3
+
+using namespace vib3;
+
+static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void* page_table, int num_experts,
+                              const void* shared_pages, const unsigned short* expert_ids, const float* expert_weights,
+                              int top_k, float shared_weight, void* act_scratch, float* out, int out_accumulate,
+                              int hidden_dim, int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
+                              int rows_per_page_down, int group_size, int* status, void* stream) {
+    if (!x || !page_table || !expert_ids || !expert_weights || !act_scratch || !out) return VIB3_ERR_NULL;
+    if (group_size != kGroupSize) return VIB3_ERR_UNSUPPORTED;
+    if (x_dtype < X_F32 || x_dtype > X_BF16) return VIB3_ERR_UNSUPPORTED;
+    if (hidden_dim <= 0 || expert_hidden_dim <= 0 || hidden_dim % kGroupSize || expert_hidden_dim % kGroupSize) return VIB3_ERR_SHAPE;
+    if (top_k < 0 || top_k > kMaxSlots - 1 || num_experts <= 0) return VIB3_ERR_COUNT;
+    if (top_k + (shared_pages ? 1 : 0) == 0) return VIB3_ERR_COUNT;
+    if (pages_per_segment <= 0 || pages_per_segment > kMaxPages) return VIB3_ERR_COUNT;
+    if (rows_per_page_gate_up <= 0 || rows_per_page_down <= 0) return VIB3_ERR_SHAPE;
+    if ((long long)rows_per_page_gate_up * pages_per_segment < expert_hidden_dim) return VIB3_ERR_SHAPE;
+    if ((long long)rows_per_page_down * pages_per_segment < hidden_dim) return VIB3_ERR_SHAPE;
+    if (((uintptr_t)x & 3) || ((uintptr_t)page_table & 15) || ((uintptr_t)shared_pages & 15) ||
+        ((uintptr_t)act_scratch & 15) || ((uintptr_t)out & 3)) return VIB3_ERR_ALIGN;
+
+    MoeLayerArgs a;
+    a.x = x; a.x_dtype = x_dtype;
+    a.page_table = (const PageEntry*)page_table; a.shared_pages = (const PageEntry*)shared_pages;
+    a.expert_ids = expert_ids; a.expert_weights = expert_weights; a.top_k = top_k; a.num_experts = num_experts;
+    a.shared_weight = shared_weight; a.act = (__half*)act_scratch; a.out = out; a.out_accumulate = out_accumulate;
+    a.H = hidden_dim; a.I = expert_hidden_dim; a.P = pages_per_segment;
+    a.rpp_gu = rows_per_page_gate_up; a.rpp_dn = rows_per_page_down; a.status = status;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    int err = 0;
+    if (phases & 1) {
+        const int lane_chunks_gu = (hidden_dim / kGroupSize + 31) / 32;
+        if (x_dtype == X_F32) {
+            err = lane_chunks_gu % 7 == 0 ? launch_gateup<MathF32, 7>(a, st)
+                : lane_chunks_gu % 4 == 0 ? launch_gateup<MathF32, 4>(a, st)
+                : lane_chunks_gu % 2 == 0 ? launch_gateup<MathF32, 2>(a, st) : launch_gateup<MathF32, 1>(a, st);
+        } else {
+            err = lane_chunks_gu % 7 == 0 ? launch_gateup<MathF16, 7>(a, st)
+                : lane_chunks_gu % 4 == 0 ? launch_gateup<MathF16, 4>(a, st)
+                : lane_chunks_gu % 2 == 0 ? launch_gateup<MathF16, 2>(a, st) : launch_gateup<MathF16, 1>(a, st);
+        }
+        if (err) return err;
+    }
+    if (phases & 2) {
+        const int lane_chunks_dn = (expert_hidden_dim / kGroupSize + 31) / 32;
+        err = lane_chunks_dn % 7 == 0 ? launch_down<7, 2>(a, st)
+            : lane_chunks_dn % 4 == 0 ? launch_down<4, 4>(a, st)
+            : lane_chunks_dn % 2 == 0 ? launch_down<2, 9>(a, st) : launch_down<1, 9>(a, st);
+    }
+    return err;
+}
+
+#define VIB3_MOE_ARGS                                                                                               \
+    const void *x, int x_dtype, const void *page_table, int num_experts, const void *shared_pages,                   \
+        const unsigned short *expert_ids, const float *expert_weights, int top_k, float shared_weight,              \
+        void *act_scratch, float *out, int out_accumulate, int hidden_dim, int expert_hidden_dim,                   \
+        int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down, int group_size, int *status,      \
+        void *stream
+#define VIB3_MOE_PASS                                                                                               \
+    x, x_dtype, page_table, num_experts, shared_pages, expert_ids, expert_weights, top_k, shared_weight, act_scratch, \
+        out, out_accumulate, hidden_dim, expert_hidden_dim, pages_per_segment, rows_per_page_gate_up,               \
+        rows_per_page_down, group_size, status, stream
+
+extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(2, VIB3_MOE_PASS); }

@@ -1,0 +1,367 @@
+// Router: logits GEMV, scoring (softmax / sigmoid), stable top-k, normalise and scale.
+//
+// Reference entry points kept with identical signatures:
+//   vib3_launch_router_gemv       cuda/src/kernels.cu:1143  (x fp16, W fp16)
+//   vib3_launch_router_gemv_f32   cuda/src/kernels.cu:1477  (x fp32, W fp16)
+//   vib3_launch_router_topk       cuda/src/kernels.cu:4075  (GEMV + top-k, results stay on device)
+// and one extended launcher, vib3_launch_router_topk_ex, that also accepts fp32 router weights
+// and fp16/bf16 activations, any expert count up to 512 (the reference's bitonic kernel needs a
+// power of two, kernels.cu:3899), and finishes in a single launch.
+//
+// Summation order of the logits: exactly the reference CUDA kernel's (kernels.cu:665-707) — 128
+// chains per expert, chain t adds d = t, t+128, ... with fused multiply-add, a shfl_down tree
+// per warp, then (s0+s2)+(s1+s3) — so logits are bit-identical to the reference's on a GPU.
+//
+// Scoring and selection follow the reference's CPU router (src/compute/kernels.rs:2364-2437),
+// which is the only well-defined reference for 384 experts: softmax over the selected k only;
+// sigmoid with optional selection bias, weights from the unbiased sigmoid, divided by their sum
+// when it exceeds 1e-20, times the scaling factor; ties resolved towards the lower expert index
+// (stable sort).  exp() is evaluated in double and rounded once, sums and divisions are IEEE
+// fp32 in selection order.
+//
+// Bit-exact indices against the CPU router's sequential summation order: when any two adjacent
+// selection scores among the best k+1 are closer than a bound on the summation-order
+// difference, the near-tied experts' logits are recomputed with one sequential multiply-then-add
+// chain per expert (the CPU order) before the final selection.  This costs tens of microseconds
+// and happens for a few percent of tokens.
+#include "int4_math.cuh"
+#include "launch_common.h"
+
+namespace vib3 {
+
+constexpr int kRouterMaxExperts = 512;  // MAX_EXPERTS, src/core/types.rs:20
+constexpr int kRouterMaxTopK = 16;      // MAX_ACTIVE_EXPERTS, src/core/types.rs:26
+constexpr int kChains = 128;
+
+enum WDType : int { W_F16 = 0, W_F32 = 1 };
+
+struct RouterArgs {
+    const void* x;
+    int x_dtype;
+    const void* W;
+    int w_dtype;
+    float* scores;        // [E] logits; [2E] when exact_order (second half: sum |x*w|)
+    const float* bias;    // [E] or null
+    unsigned short* out_ids;
+    float* out_weights;
+    unsigned int* counter;  // one zeroed word of workspace (single-launch path only)
+    int H, E, top_k, mode;
+    float scaling;
+    int normalize;
+    int exact_order;
+};
+
+__device__ __forceinline__ float load_w(const void* W, int w_dtype, size_t i) {
+    return w_dtype == W_F32 ? reinterpret_cast<const float*>(W)[i]
+                            : __half2float(reinterpret_cast<const __half*>(W)[i]);
+}
+
+// shfl_down tree of the reference (kernels.cu:52-57); only lane 0's value is meaningful.
+__device__ __forceinline__ float warp_sum_down(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Logit of one expert with 128 threads (lane = chain index); result valid in chain 0.
+template <int U>
+__device__ __forceinline__ void expert_logit(const RouterArgs& a, int expert, int chain, float* smem4, float* smem4_abs,
+                                             float& logit, float& absum) {
+    const size_t base = (size_t)expert * a.H;
+    float acc = 0.f, aabs = 0.f;
+    int d = chain;
+    for (; d + (U - 1) * kChains < a.H; d += U * kChains) {
+        float w[U], xv[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            w[i] = load_w(a.W, a.w_dtype, base + d + i * kChains);
+            xv[i] = load_x_as_f32(a.x, a.x_dtype, d + i * kChains);
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            acc = fmaf(xv[i], w[i], acc);
+            aabs += fabsf(xv[i] * w[i]);
+        }
+    }
+    for (; d < a.H; d += kChains) {
+        const float w = load_w(a.W, a.w_dtype, base + d);
+        const float xv = load_x_as_f32(a.x, a.x_dtype, d);
+        acc = fmaf(xv, w, acc);
+        aabs += fabsf(xv * w);
+    }
+    acc = warp_sum_down(acc);
+    aabs = warp_sum_down(aabs);
+    const int wid = chain >> 5, wl = chain & 31;
+    if (wl == 0) { smem4[wid] = acc; smem4_abs[wid] = aabs; }
+    __syncthreads();
+    if (wid == 0) {
+        float f = wl < 4 ? smem4[wl] : 0.f;
+        float g = wl < 4 ? smem4_abs[wl] : 0.f;
+        f = warp_sum_down(f);
+        g = warp_sum_down(g);
+        logit = f;
+        absum = g;
+    }
+}
+
+__device__ __forceinline__ unsigned int orderable(float v) {
+    const unsigned int b = __float_as_uint(v + 0.0f);  // -0 -> +0
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ float exp_rn(float v) { return (float)exp((double)v); }
+
+__device__ __forceinline__ float sigmoid_ref(float z) {
+    return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_rn(-z)));
+}
+
+// Scoring + top-k by one CTA of 256 threads; every thread owns experts tid and tid+256.
+// smem: sel[E], sig[E], keys for the block reductions.
+struct TopKSmem {
+    float logit[kRouterMaxExperts];
+    float sig[kRouterMaxExperts];
+    float sel[kRouterMaxExperts];
+    unsigned long long wmax[2][8];
+    int chosen[kRouterMaxTopK + 1];
+    float eps_max[8];
+    int redo;
+};
+
+__device__ void block_select(const RouterArgs& a, TopKSmem& sm, int nsel) {
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    unsigned long long key[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int e = tid + 256 * j;
+        key[j] = e < a.E ? ((unsigned long long)orderable(sm.sel[e]) << 32) | (unsigned)(0xFFFFu - e) : 0ull;
+    }
+    for (int round = 0; round < nsel; ++round) {
+        unsigned long long m = key[0] > key[1] ? key[0] : key[1];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, m, o);
+            m = other > m ? other : m;
+        }
+        if (lane == 0) sm.wmax[round & 1][wid] = m;
+        __syncthreads();
+        unsigned long long best = sm.wmax[round & 1][0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {
+            const unsigned long long v = sm.wmax[round & 1][w];
+            best = v > best ? v : best;
+        }
+        const int e = 0xFFFF - (int)(best & 0xFFFFu);
+        if (key[0] == best) key[0] = 0ull;
+        if (key[1] == best) key[1] = 0ull;
+        if (tid == 0) sm.chosen[round] = best ? e : -1;
+    }
+    __syncthreads();
+}
+
+__device__ void block_score(const RouterArgs& a, TopKSmem& sm) {
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+        const float z = sm.logit[e];
+        if (a.mode == 0) {
+            sm.sig[e] = z;
+            sm.sel[e] = z;
+        } else {
+            const float s = sigmoid_ref(z);
+            sm.sig[e] = s;
+            sm.sel[e] = a.bias ? __fadd_rn(s, a.bias[e]) : s;
+        }
+    }
+    __syncthreads();
+}
+
+__device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
+    const int tid = threadIdx.x;
+    const int k = min(a.top_k, a.E);
+    for (int e = tid; e < a.E; e += blockDim.x) sm.logit[e] = __ldcg(a.scores + e);
+    __syncthreads();
+    block_score(a, sm);
+    const int nsel = min(k + 1, a.E);
+    block_select(a, sm, nsel);
+
+    if (a.exact_order && nsel > 1) {
+        // Bound on |logit(order A) - logit(order B)| for fp32 sums of H products:
+        // 16 * 2^-24 * (sqrt(H) * |S| + sum|x w|), maximised over experts.
+        float eps = 0.f;
+        for (int e = tid; e < a.E; e += blockDim.x) {
+            const float ab = __ldcg(a.scores + a.E + e);
+            eps = fmaxf(eps, 16.f * 5.9604645e-8f * (sqrtf((float)a.H) * fabsf(sm.logit[e]) + ab));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) eps = fmaxf(eps, __shfl_xor_sync(0xffffffffu, eps, o));
+        if ((tid & 31) == 0) sm.eps_max[tid >> 5] = eps;
+        if (tid == 0) sm.redo = 0;
+        __syncthreads();
+        eps = sm.eps_max[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) eps = fmaxf(eps, sm.eps_max[w]);
+        // selection scores move by at most eps (softmax: raw logits) or eps/4 (sigmoid slope)
+        const float tau = 2.f * (a.mode == 0 ? eps : 0.25f * eps) + 4.f * 1.1920929e-7f;
+        if (tid == 0) {
+            int redo = 0;
+            for (int i = 0; i + 1 < nsel; ++i) {
+                const int e0 = sm.chosen[i], e1 = sm.chosen[i + 1];
+                if (e0 < 0 || e1 < 0) break;
+                if (sm.sel[e0] - sm.sel[e1] <= tau) redo = 1;
+            }
+            sm.redo = redo;
+        }
+        __syncthreads();
+        if (sm.redo) {
+            const int last = sm.chosen[nsel - 1];
+            const float floor_sel = (last >= 0 ? sm.sel[last] : -INFINITY) - tau;
+            for (int e = tid; e < a.E; e += blockDim.x) {
+                if (sm.sel[e] >= floor_sel) {
+                    // the CPU router's order: one chain, multiply then add (kernels.rs:2346-2350)
+                    const size_t base = (size_t)e * a.H;
+                    float acc = 0.f;
+                    for (int d = 0; d < a.H; ++d)
+                        acc = __fadd_rn(acc, __fmul_rn(load_x_as_f32(a.x, a.x_dtype, d), load_w(a.W, a.w_dtype, base + d)));
+                    sm.logit[e] = acc;
+                    a.scores[e] = acc;
+                }
+            }
+            __syncthreads();
+            block_score(a, sm);
+            block_select(a, sm, k);
+        }
+    }
+
+    if (tid == 0) {
+        if (a.mode == 0) {
+            float mx = -INFINITY;
+            for (int i = 0; i < k; ++i) mx = fmaxf(mx, sm.logit[sm.chosen[i]]);
+            float sum = 0.f;
+            for (int i = 0; i < k; ++i) sum = __fadd_rn(sum, exp_rn(__fsub_rn(sm.logit[sm.chosen[i]], mx)));
+            for (int i = 0; i < k; ++i) {
+                a.out_ids[i] = (unsigned short)sm.chosen[i];
+                a.out_weights[i] = __fdiv_rn(exp_rn(__fsub_rn(sm.logit[sm.chosen[i]], mx)), sum);
+            }
+        } else {
+            float w[kRouterMaxTopK];
+            float total = 0.f;
+            for (int i = 0; i < k; ++i) {
+                w[i] = sm.sig[sm.chosen[i]];
+                total = __fadd_rn(total, w[i]);
+            }
+            const bool norm = a.normalize && total > 1e-20f;
+            for (int i = 0; i < k; ++i) {
+                float v = norm ? __fdiv_rn(w[i], total) : w[i];
+                a.out_ids[i] = (unsigned short)sm.chosen[i];
+                a.out_weights[i] = __fmul_rn(v, a.scaling);
+            }
+        }
+    }
+}
+
+// GEMV: 2 experts per CTA, 128 threads each.  When `a.counter` is set, the CTA that finishes
+// last also does the scoring and selection (single launch).
+template <int U>
+__global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
+    __shared__ float red[2][4], red_abs[2][4];
+    __shared__ TopKSmem sm;
+    __shared__ int is_last;
+    const int local = threadIdx.x >> 7, chain = threadIdx.x & 127;
+    const int expert = blockIdx.x * 2 + local;
+    float logit = 0.f, absum = 0.f;
+    // both halves of the CTA must reach the __syncthreads inside expert_logit
+    const int e_clamped = min(expert, a.E - 1);
+    expert_logit<U>(a, e_clamped, chain, red[local], red_abs[local], logit, absum);
+    if (chain == 0 && expert < a.E) {
+        a.scores[expert] = logit;
+        if (a.exact_order) a.scores[a.E + expert] = absum;
+    }
+    if (a.counter == nullptr) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int ticket = atomicAdd(a.counter, 1u);
+        is_last = ticket == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    router_finish(a, sm);
+    if (threadIdx.x == 0) *a.counter = 0u;  // ready for the next launch
+}
+
+__global__ void __launch_bounds__(256) router_topk_kernel(RouterArgs a) {
+    __shared__ TopKSmem sm;
+    router_finish(a, sm);
+}
+
+static int check_router(const RouterArgs& a) {
+    if (!a.x || !a.W || !a.scores) return VIB3_ERR_NULL;
+    if (a.H <= 0 || a.E <= 0) return VIB3_ERR_SHAPE;
+    return VIB3_OK;
+}
+
+static int check_topk(const RouterArgs& a) {
+    if (!a.out_ids || !a.out_weights) return VIB3_ERR_NULL;
+    if (a.E > kRouterMaxExperts) return VIB3_ERR_COUNT;
+    if (a.top_k <= 0 || a.top_k > kRouterMaxTopK || a.top_k > a.E) return VIB3_ERR_COUNT;
+    if (a.mode != 0 && a.mode != 1) return VIB3_ERR_UNSUPPORTED;
+    return VIB3_OK;
+}
+
+}  // namespace vib3
+
+using namespace vib3;
+
+extern "C" int vib3_launch_router_gemv(const void* x_f16, const void* W_f16, float* scores, int hidden_dim,
+                                       int num_experts, void* stream) {
+    RouterArgs a{};
+    a.x = x_f16; a.x_dtype = X_F16; a.W = W_f16; a.w_dtype = W_F16; a.scores = scores; a.H = hidden_dim; a.E = num_experts;
+    if (int e = check_router(a)) return e;
+    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, (cudaStream_t)stream>>>(a);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int vib3_launch_router_gemv_f32(const void* x_f32, const void* W_f16, float* scores, int hidden_dim,
+                                           int num_experts, void* stream) {
+    RouterArgs a{};
+    a.x = x_f32; a.x_dtype = X_F32; a.W = W_f16; a.w_dtype = W_F16; a.scores = scores; a.H = hidden_dim; a.E = num_experts;
+    if (int e = check_router(a)) return e;
+    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, (cudaStream_t)stream>>>(a);
+    return (int)cudaGetLastError();
+}
+
+// Reference signature: two launches (GEMV, then selection), weights always normalised in
+// sigmoid mode as the reference's kernel does (kernels.cu:4056-4062).
+extern "C" int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_buf, const float* bias,
+                                       unsigned short* out_ids, float* out_weights, int hidden_dim, int num_experts,
+                                       int top_k, int scoring_mode, float scaling_factor, void* stream) {
+    RouterArgs a{};
+    a.x = x_f32; a.x_dtype = X_F32; a.W = W_f16; a.w_dtype = W_F16; a.scores = scores_buf; a.bias = bias;
+    a.out_ids = out_ids; a.out_weights = out_weights; a.H = hidden_dim; a.E = num_experts; a.top_k = top_k;
+    a.mode = scoring_mode; a.scaling = scaling_factor; a.normalize = 1; a.exact_order = 0;
+    if (int e = check_router(a)) return e;
+    if (int e = check_topk(a)) return e;
+    cudaStream_t st = (cudaStream_t)stream;
+    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, st>>>(a);
+    if (cudaError_t e = cudaGetLastError()) return (int)e;
+    router_topk_kernel<<<1, 256, 0, st>>>(a);
+    return (int)cudaGetLastError();
+}
+
+// Extended launcher: one launch.  scores_buf holds E floats (2E when exact_order != 0);
+// workspace is one 32-bit word that must be zero before the first call and is left zero.
+extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
+                                          const float* bias, unsigned short* out_ids, float* out_weights,
+                                          int hidden_dim, int num_experts, int top_k, int scoring_mode,
+                                          float scaling_factor, int normalize, int exact_order,
+                                          unsigned int* workspace, void* stream) {
+    RouterArgs a{};
+    a.x = x; a.x_dtype = x_dtype; a.W = W; a.w_dtype = w_dtype; a.scores = scores_buf; a.bias = bias;
+    a.out_ids = out_ids; a.out_weights = out_weights; a.counter = workspace; a.H = hidden_dim; a.E = num_experts;
+    a.top_k = top_k; a.mode = scoring_mode; a.scaling = scaling_factor; a.normalize = normalize; a.exact_order = exact_order;
+    if (int e = check_router(a)) return e;
+    if (int e = check_topk(a)) return e;
+    if (!workspace) return VIB3_ERR_NULL;
+    if (x_dtype < X_F32 || x_dtype > X_BF16 || (w_dtype != W_F16 && w_dtype != W_F32)) return VIB3_ERR_UNSUPPORTED;
+    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, (cudaStream_t)stream>>>(a);
+    return (int)cudaGetLastError();
+}

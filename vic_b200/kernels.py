@@ -1,0 +1,147 @@
+"""Launch wrappers with the names, argument meaning and error behaviour of the reference's Rust
+launchers (src/compute/kernels.rs), over the C ABI of libvib3_cuda.so.
+
+Pointers are raw device addresses (ints) or CUDA tensors; ``stream`` is a raw cudaStream_t (int)
+and defaults to torch's current stream.  A non-zero launcher return raises Vib3Error, as the
+reference maps it to Error::Cuda (kernels.rs:145-150).  There is no CPU path here: the
+reference's ``CudaStream::cpu_only()`` fallbacks are restated only in the test oracle."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .core_types import INT4_GROUP_SIZE, SCORING_SIGMOID, SCORING_SOFTMAX, W_F16, W_F32, X_BF16, X_F16, X_F32
+from .lib import check, lib
+
+
+def _ptr(t) -> int:
+    if t is None:
+        return 0
+    if isinstance(t, int):
+        return t
+    if not t.is_cuda:
+        raise ValueError("device tensor expected")
+    return t.data_ptr()
+
+
+def _stream(stream: Optional[int]) -> int:
+    return torch.cuda.current_stream().cuda_stream if stream is None else stream
+
+
+def x_dtype_code(t: torch.Tensor) -> int:
+    return {torch.float32: X_F32, torch.float16: X_F16, torch.bfloat16: X_BF16}[t.dtype]
+
+
+def partial_matmul(input, weight_page, output, k: int, m_slice: int, stream: Optional[int] = None) -> None:
+    """kernels.rs:25-152, INT4 arm: y_f16[m_slice] = W_page . x_f16; the scales pointer is derived
+    from the page pointer exactly as kernels.rs:94-98 does."""
+    page = _ptr(weight_page)
+    scales = page + ((k + 1) // 2) * m_slice
+    check("partial_matmul_int4", lib().vib3_launch_partial_matmul_int4(
+        _ptr(input), page, scales, _ptr(output), k, m_slice, INT4_GROUP_SIZE, _stream(stream)))
+
+
+def partial_matmul_f32(input, weight_page, output, k: int, m_slice: int, stream: Optional[int] = None) -> None:
+    """kernels.rs:375-455, INT4 arm: fp32 input, fp16 output."""
+    page = _ptr(weight_page)
+    scales = page + ((k + 1) // 2) * m_slice
+    check("partial_matmul_int4_f32", lib().vib3_launch_partial_matmul_int4_f32(
+        _ptr(input), page, scales, _ptr(output), k, m_slice, INT4_GROUP_SIZE, _stream(stream)))
+
+
+def silu_mul(silu_operand, mul_operand, output, dim: int, stream: Optional[int] = None) -> None:
+    check("silu_mul", lib().vib3_launch_silu_mul(_ptr(silu_operand), _ptr(mul_operand), _ptr(output), dim, _stream(stream)))
+
+
+def partial_swiglu_f32(input, up_page, gate_page, output, hidden_dim: int, m_slice: int,
+                       swiglu_temps: Optional[Tuple] = None, stream: Optional[int] = None) -> None:
+    """kernels.rs:459-600, INT4 arm.  With temps: the reference's decomposition (two fp32-input
+    matmuls rounded to fp16, then silu_mul, kernels.rs:493-541).  Without: the fused kernel
+    (cuda_ffi.rs:344-355), one rounding."""
+    if swiglu_temps is not None:
+        up_tmp, gate_tmp = swiglu_temps
+        partial_matmul_f32(input, up_page, up_tmp, hidden_dim, m_slice, stream)
+        partial_matmul_f32(input, gate_page, gate_tmp, hidden_dim, m_slice, stream)
+        silu_mul(gate_tmp, up_tmp, output, m_slice, stream)
+        return
+    up, gate = _ptr(up_page), _ptr(gate_page)
+    off = ((hidden_dim + 1) // 2) * m_slice
+    check("fused_swiglu_int4_f32", lib().vib3_launch_fused_swiglu_int4_f32(
+        _ptr(input), up, up + off, gate, gate + off, _ptr(output), hidden_dim, m_slice, INT4_GROUP_SIZE, _stream(stream)))
+
+
+def weighted_accumulate(output, expert_output, weight: float, dim: int, stream: Optional[int] = None) -> None:
+    check("weighted_accumulate", lib().vib3_launch_weighted_accumulate(_ptr(output), _ptr(expert_output), weight, dim, _stream(stream)))
+
+
+def weighted_accumulate_f32(output, expert_output, weight: float, dim: int, stream: Optional[int] = None) -> None:
+    check("weighted_accumulate_f32", lib().vib3_launch_weighted_accumulate_f32(_ptr(output), _ptr(expert_output), weight, dim, _stream(stream)))
+
+
+def weighted_accumulate_f32_f32(output, expert_output, weight: float, dim: int, stream: Optional[int] = None) -> None:
+    check("weighted_accumulate_f32_f32", lib().vib3_launch_weighted_accumulate_f32_f32(_ptr(output), _ptr(expert_output), weight, dim, _stream(stream)))
+
+
+def residual_add_f32_f32(accumulator, layer_output, dim: int, stream: Optional[int] = None) -> None:
+    check("residual_add_f32_f32", lib().vib3_launch_residual_add_f32_f32(_ptr(accumulator), _ptr(layer_output), dim, _stream(stream)))
+
+
+def router_gemv_f32(hidden_state, router_weights_f16, scores, hidden_dim: int, num_experts: int,
+                    stream: Optional[int] = None) -> None:
+    check("router_gemv_f32", lib().vib3_launch_router_gemv_f32(_ptr(hidden_state), _ptr(router_weights_f16), _ptr(scores),
+                                                              hidden_dim, num_experts, _stream(stream)))
+
+
+def router_gemv(hidden_state_f16, router_weights_f16, scores, hidden_dim: int, num_experts: int,
+                stream: Optional[int] = None) -> None:
+    check("router_gemv", lib().vib3_launch_router_gemv(_ptr(hidden_state_f16), _ptr(router_weights_f16), _ptr(scores),
+                                                      hidden_dim, num_experts, _stream(stream)))
+
+
+def run_router_gpu_topk_nosync(hidden_state_f32, router_weights_f16, scores_buf, bias, out_ids, out_weights,
+                               hidden_dim: int, num_experts: int, top_k: int, scoring_mode: int,
+                               scaling_factor: float, stream: Optional[int] = None) -> None:
+    """kernels.rs:1890-1953: results stay on the device."""
+    check("router_topk", lib().vib3_launch_router_topk(
+        _ptr(hidden_state_f32), _ptr(router_weights_f16), _ptr(scores_buf), _ptr(bias), _ptr(out_ids), _ptr(out_weights),
+        hidden_dim, num_experts, top_k, scoring_mode, scaling_factor, _stream(stream)))
+
+
+def run_router_gpu_topk(hidden_state_f32, router_weights_f16, scores_buf, bias, out_ids, out_weights, hidden_dim: int,
+                        num_experts: int, top_k: int, scoring_mode: int, scaling_factor: float,
+                        stream: Optional[int] = None):
+    """kernels.rs:1811-1873: launch, synchronise, two small D2H copies -> [(expert, weight)]."""
+    run_router_gpu_topk_nosync(hidden_state_f32, router_weights_f16, scores_buf, bias, out_ids, out_weights, hidden_dim,
+                               num_experts, top_k, scoring_mode, scaling_factor, stream)
+    torch.cuda.current_stream().synchronize()
+    ids = out_ids[:top_k].cpu().view(torch.int16).numpy().view("uint16")
+    ws = out_weights[:top_k].cpu().numpy()
+    return [(int(i), float(w)) for i, w in zip(ids, ws)]
+
+
+def router_topk_ex(x: torch.Tensor, W: torch.Tensor, scores_buf, bias, out_ids, out_weights, top_k: int,
+                   scoring_mode: int, scaling_factor: float, normalize: bool, exact_order: bool, workspace,
+                   stream: Optional[int] = None) -> None:
+    """Single-launch router for fp16/bf16/fp32 activations and fp16/fp32 weights."""
+    E, H = W.shape
+    w_dtype = {torch.float16: W_F16, torch.float32: W_F32}[W.dtype]
+    check("router_topk_ex", lib().vib3_launch_router_topk_ex(
+        _ptr(x), x_dtype_code(x), _ptr(W), w_dtype, _ptr(scores_buf), _ptr(bias), _ptr(out_ids), _ptr(out_weights), H, E,
+        top_k, scoring_mode, scaling_factor, int(normalize), int(exact_order), _ptr(workspace), _stream(stream)))
+
+
+def moe_layer_int4_paged(x: torch.Tensor, page_table: int, num_experts: int, shared_pages: int, expert_ids,
+                         expert_weights, top_k: int, shared_weight: float, act_scratch, out, out_accumulate: bool,
+                         hidden_dim: int, expert_hidden_dim: int, pages_per_segment: int, rows_per_page_gate_up: int,
+                         rows_per_page_down: int, status=None, stream: Optional[int] = None, phase: int = 3) -> None:
+    """phase 3: both launches; 1: gate/up + SiLU only; 2: down + accumulate only."""
+    fn = {3: lib().vib3_launch_moe_layer_int4_paged, 1: lib().vib3_launch_moe_gate_up_int4_paged,
+          2: lib().vib3_launch_moe_down_int4_paged}[phase]
+    check("moe_layer_int4_paged", fn(
+        _ptr(x), x_dtype_code(x), page_table, num_experts, shared_pages or 0, _ptr(expert_ids), _ptr(expert_weights), top_k,
+        shared_weight, _ptr(act_scratch), _ptr(out), int(out_accumulate), hidden_dim, expert_hidden_dim,
+        pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status), _stream(stream)))
+
+
+__all__ = [n for n in dir() if not n.startswith("_")] + ["SCORING_SOFTMAX", "SCORING_SIGMOID"]

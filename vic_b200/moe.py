@@ -1,0 +1,111 @@
+"""The MoE sublayer of one decode token on the GPU: router -> experts -> accumulate.
+
+``MoeDecoder.forward_layer`` is the fused path (3 launches, no host synchronisation, graph
+capturable).  ``run_moe_sublayer_paged_calls`` drives the per-page entry points in the order the
+reference engine does (src/runtime/engine.rs:5052-5360, :5801-6306) and exists so that path stays
+exercised and comparable."""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import kernels
+from .buffer_manager import LayerPlan, QueryPlanner
+from .core_types import EXPERT_SHARED, MAX_ACTIVE_EXPERTS, SCORING_SIGMOID
+from .synth import SyntheticMoe
+
+
+class MoeDecoder:
+    """Device buffers and launch sequence for batch-1 decode over a SyntheticMoe (or any pool with
+    the same page-table layout)."""
+
+    def __init__(self, model: SyntheticMoe, exact_order: bool = True):
+        self.model = model
+        sh = model.shape
+        dev = model.router_w.device
+        self.exact_order = exact_order
+        self.scores = torch.zeros(2 * sh.num_experts, dtype=torch.float32, device=dev)
+        self.ids = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
+        self.weights = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
+        self.workspace = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.act = torch.zeros((sh.top_k + 1) * sh.intermediate, dtype=torch.float16, device=dev)
+        self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.tables = [model.page_table(l) for l in range(model.n_layers)]
+        self.shared_tables = [model.shared_table(l) for l in range(model.n_layers)]
+        self.launches_per_layer = 3
+
+    def route(self, layer: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        sh = self.model.shape
+        kernels.router_topk_ex(x, self.model.router_w[layer], self.scores, bias, self.ids, self.weights, sh.top_k,
+                               sh.scoring, sh.scaling_factor, sh.normalize, self.exact_order, self.workspace)
+
+    def experts(self, layer: int, x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+                phase: int = 3) -> torch.Tensor:
+        sh = self.model.shape
+        out = self.out if out is None else out
+        kernels.moe_layer_int4_paged(x, self.tables[layer], sh.num_experts, self.shared_tables[layer], self.ids,
+                                     self.weights, sh.top_k, 1.0, self.act, out, accumulate, sh.hidden,
+                                     sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page,
+                                     sh.down.rows_per_page, self.status, phase=phase)
+        return out
+
+    def forward_layer(self, layer: int, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                      accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: [H] activations (bf16 / fp16 / fp32).  Returns the fp32 [H] sublayer output."""
+        self.route(layer, x, bias)
+        return self.experts(layer, x, out, accumulate)
+
+    def routing(self) -> Tuple[np.ndarray, np.ndarray]:
+        k = self.model.shape.top_k
+        return (self.ids[:k].cpu().numpy().view(np.uint16).copy(), self.weights[:k].cpu().numpy().copy())
+
+
+def run_moe_sublayer_paged_calls(model: SyntheticMoe, layer: int, x_f32: torch.Tensor, planner: QueryPlanner,
+                                 router_w_f16: torch.Tensor, bufs: Optional[dict] = None):
+    """The reference engine's INT4 MoE sublayer, call by call, on this library's per-page entry
+    points: router with host sync (kernels.rs:1811-1873), plan_layer, then per expert the
+    (up, gate) page pairs through partial_swiglu_f32 with temps, the down pages through
+    partial_matmul, weighted_accumulate_f32; shared expert last with weight 1.0.
+    Returns (layer_out_f32 [H], [(expert, weight)], launches)."""
+    sh = model.shape
+    dev = x_f32.device
+    H, I = sh.hidden, sh.intermediate
+    b = bufs if bufs is not None else {}
+    def buf(name, n, dt):
+        if name not in b:
+            b[name] = torch.zeros(n, dtype=dt, device=dev)
+        return b[name]
+    scores = buf("scores", sh.num_experts, torch.float32)
+    ids = buf("ids", MAX_ACTIVE_EXPERTS, torch.int16)
+    ws = buf("ws", MAX_ACTIVE_EXPERTS, torch.float32)
+    up_tmp, gate_tmp = buf("up_tmp", I, torch.float16), buf("gate_tmp", I, torch.float16)
+    expert_out = buf("expert_out", I, torch.float16)
+    down_out = buf("down_out", H, torch.float16)
+    layer_out = buf("layer_out", H, torch.float32)
+    launches = 0
+    activation = kernels.run_router_gpu_topk(x_f32, router_w_f16, scores, None, ids, ws, H, sh.num_experts, sh.top_k,
+                                             sh.scoring, sh.scaling_factor)
+    launches += 2
+    entries = list(activation) + ([(EXPERT_SHARED, 1.0)] if sh.shared_experts else [])
+    plan: LayerPlan = planner.plan_layer(layer, entries)
+    layer_out.zero_()
+    for ep in plan.experts:
+        segs = sorted(set(p.id.segment for p in ep.pages))
+        up_pages = [p for p in ep.pages if p.id.segment == segs[0]]
+        gate_pages = [p for p in ep.pages if p.id.segment == segs[1]]
+        down_pages = [p for p in ep.pages if p.id.segment == segs[2]]
+        expert_out.zero_()
+        for up, gate in zip(up_pages, gate_pages):
+            kernels.partial_swiglu_f32(x_f32, up.device_ptr, gate.device_ptr, expert_out.data_ptr() + 2 * up.row_start,
+                                       H, up.row_count, swiglu_temps=(up_tmp, gate_tmp))
+            launches += 3
+        down_out.zero_()
+        for dp in down_pages:
+            kernels.partial_matmul(expert_out, dp.device_ptr, down_out.data_ptr() + 2 * dp.row_start, I, dp.row_count)
+            launches += 1
+        kernels.weighted_accumulate_f32(layer_out, down_out, ep.weight, H)
+        launches += 1
+    return layer_out, activation, launches
