@@ -41,6 +41,7 @@ extern "C" {
 /* bits of the device status word written by the paged kernels */
 #define VIB3_STATUS_MISSING_PAGE 1
 #define VIB3_STATUS_BAD_EXPERT 2
+#define VIB3_STATUS_TIMEOUT 4       /* a bounded wait inside a kernel gave up */
 
 /* ── Entry points with the reference's signatures ───────────────────────────────────────── */
 
@@ -81,8 +82,9 @@ int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_
  * run_router_with_scoring_and_bias, src/compute/kernels.rs:2307-2440).  x_dtype VIB3_X_*,
  * w_dtype VIB3_W_*.  scores_buf: num_experts floats, 2*num_experts when exact_order != 0.
  * exact_order != 0 makes the selected indices equal to those of the reference's CPU router
- * (sequential fp32 summation) even for near-tied experts.  workspace: one uint32, zero before
- * the first call, left zero by every call; calls sharing a workspace must not overlap. */
+ * (sequential fp32 summation) even for near-tied experts.  workspace: two uint32, zero before
+ * the first call; [0] is left zero by every call, [1] counts near-tie recomputations; calls
+ * sharing a workspace must not overlap. */
 int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
                                const float* bias_or_null, unsigned short* out_ids, float* out_weights,
                                int hidden_dim, int num_experts, int top_k, int scoring_mode, float scaling_factor,
@@ -104,7 +106,8 @@ typedef struct vib3_page_entry {
  *   page_table   [num_experts][3][pages_per_segment] entries, segment 0 up, 1 gate, 2 down
  *   shared_pages [3][pages_per_segment] entries of the shared expert, or NULL
  *   expert_ids / expert_weights   [top_k] on the device (router output)
- *   act_scratch  (top_k + 1) * expert_hidden_dim fp16 values
+ *   x            [hidden_dim] activations, 16-byte aligned
+ *   act_scratch  (top_k + 1) * expert_hidden_dim fp16 values, 16-byte aligned
  *   out          [hidden_dim] fp32; overwritten, or added to when out_accumulate != 0
  *   status       device int that receives VIB3_STATUS_* bits, or NULL */
 int vib3_launch_moe_layer_int4_paged(const void* x, int x_dtype, const void* page_table, int num_experts,
@@ -128,6 +131,10 @@ int vib3_launch_moe_down_int4_paged(const void* x, int x_dtype, const void* page
                                     float* out, int out_accumulate, int hidden_dim, int expert_hidden_dim,
                                     int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down,
                                     int group_size, int* status, void* stream);
+
+/* Library options.  key 0: use the bulk-copy staged MoE kernels where the shape allows (default 1);
+ * 0 forces the direct-load kernels.  Returns the previous value. */
+int vib3_config_set(int key, int value);
 
 /* ── Host side: VRAM page pool and query planner (C view of the C++ classes) ────────────── */
 /* Mirrors PageBufferManager's T1 pool + resident snapshot (src/storage/buffer_manager.rs:206-288,

@@ -54,11 +54,36 @@ def test_fused_layer_vs_oracle(cuda_dev, oracle, name, xdt, ntok):
         x32 = xs[t].float().cpu().numpy()
         oi, ow, _ = oracle.router(x32, Wn, sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, None, oracle.ORDER_SEQUENTIAL)
         assert np.array_equal(ids, oi)
-        assert np.allclose(w, ow, rtol=1e-5)
+        assert np.allclose(w, ow, rtol=1e-4)
         want = oracle.moe_layer(x32, oracle_experts(oracle, model, 0, list(zip(oi.tolist(), ow.tolist()))), sh.hidden,
                                 sh.intermediate, oracle.SCALE_FP16, order="gpu")
         assert_close(out, want, f"{name} {xdt} token {t}")
         assert np.all(np.isfinite(out))
+
+
+@pytest.mark.parametrize("name,xdt", [("kimi", torch.bfloat16), ("kimi", torch.float32), ("mixtral", torch.float16)])
+def test_staged_kernels_equal_direct_kernels_bit_for_bit(cuda_dev, name, xdt):
+    """The bulk-copy staged kernels and the direct-load kernels share their arithmetic: same bits."""
+    from vic_b200.lib import lib
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import synth_activation
+    model = _model(name, cuda_dev)
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(77)
+    xs = synth_activation(model.shape, g, cuda_dev, xdt, 3)
+    try:
+        for t in range(3):
+            lib().vib3_config_set(0, 1)
+            a = dec.forward_layer(0, xs[t]).clone()
+            act_a = dec.act.clone()
+            lib().vib3_config_set(0, 0)
+            b = dec.forward_layer(0, xs[t]).clone()
+            torch.cuda.synchronize()
+            assert int(dec.status.item()) == 0
+            assert torch.equal(act_a, dec.act)
+            assert torch.equal(a, b)
+    finally:
+        lib().vib3_config_set(0, 1)
 
 
 def test_accumulate_into_residual(cuda_dev):
@@ -180,5 +205,5 @@ def test_fused_launcher_refusals(cuda_dev):
     assert call(H=250) == -5 and call(I=0) == -5
     assert call(k=17) == -2 and call(k=0) == -2 and call(P=17) == -2 and call(E=0) == -2
     assert call(rg=100) == -5            # pages cannot cover the matrix: row range out of [0, M)
-    assert call(tab=p + 8) == -4
+    assert call(tab=p + 8) == -4 and call(x=p + 4) == -4
     torch.cuda.synchronize()

@@ -62,16 +62,18 @@ def test_partial_matmul_vs_oracle(cuda_dev, oracle, K, M):
     dpage, y = _dev(page, cuda_dev), torch.zeros(M, dtype=torch.float16, device=cuda_dev)
     kernels.partial_matmul(_dev(x16, cuda_dev), dpage, y, K, M)
     got = y.cpu().numpy().astype(np.float32)
-    assert_close(got, want, f"partial_matmul K={K} M={M}", rel_l2_tol=4e-4)
+    # fp16 outputs: with a handful of rows a single 1-ulp difference (2^-11) dominates the norm
+    tol = 4e-4 if M >= 32 else 1e-3
+    assert_close(got, want, f"partial_matmul K={K} M={M}", rel_l2_tol=tol)
     # fp32 input entry point
     x32 = rng.standard_normal(K).astype(np.float32)
     want32 = oracle.matmul_int4_rows_f32(x32, page, K, M, 32, oracle.SCALE_FP16)
     kernels.partial_matmul_f32(_dev(x32, cuda_dev), dpage, y, K, M)
-    assert_close(y.cpu().numpy().astype(np.float32), want32, f"partial_matmul_f32 K={K} M={M}", rel_l2_tol=4e-4)
+    assert_close(y.cpu().numpy().astype(np.float32), want32, f"partial_matmul_f32 K={K} M={M}", rel_l2_tol=tol)
     # f64 truth: the GPU result must not be further from it than fp16 output rounding explains
     w = oracle.dequantize_int4(page, M, K, 32, oracle.SCALE_FP16).astype(np.float64)
     truth = w @ x32.astype(np.float64)
-    assert rel_l2(y.cpu().numpy().astype(np.float64), truth) < 4e-4
+    assert rel_l2(y.cpu().numpy().astype(np.float64), truth) < tol
 
 
 @pytest.mark.parametrize("K,M", [(32, 2), (96, 7), (7168, 520), (7168, 488), (4096, 686)])

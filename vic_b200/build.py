@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libvib3_cuda.so")
 SOURCES = [
     "page_kernels.cu",
     "moe_layer.cu",
+    "moe_pipe.cu",
     "router.cu",
     "host/page_pool.cpp",
 ]

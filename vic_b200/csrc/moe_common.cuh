@@ -1,0 +1,57 @@
+// Argument block, limits and page-table helpers shared by the MoE sublayer kernels.
+#pragma once
+#include "int4_math.cuh"
+#include "launch_common.h"
+
+namespace vib3 {
+
+constexpr int kMaxSlots = 17;   // MAX_ACTIVE_EXPERTS (src/core/types.rs:26) + one shared expert
+constexpr int kMaxPages = 16;   // pages per segment the kernels accept (Mixtral-shape needs 16)
+constexpr int kSegUp = 0, kSegGate = 1, kSegDown = 2;
+
+struct MoeLayerArgs {
+    const void* x;                 // [H] activations
+    int x_dtype;                   // XDType
+    const PageEntry* page_table;   // [num_experts][3][P]
+    const PageEntry* shared_pages; // [3][P] or null
+    const unsigned short* expert_ids;  // [top_k], device
+    const float* expert_weights;       // [top_k], device
+    int top_k;
+    int num_experts;
+    float shared_weight;
+    __half* act;                   // [slots][I] scratch
+    float* out;                    // [H]
+    int out_accumulate;            // 0: out = layer output; 1: out += layer output (residual add)
+    int H, I, P;
+    int rpp_gu, rpp_dn;            // rows per page of gate/up and of down
+    int* status;                   // device status word, or null
+};
+
+enum StatusBits : int { kStatusMissingPage = 1, kStatusBadExpert = 2, kStatusTimeout = 4 };
+
+__device__ __forceinline__ void flag(int* status, int bit) {
+    if (status) atomicOr(status, bit);
+}
+
+// Resolve the page-table block ([3][P] entries) of slot s: routed expert or the shared expert.
+__device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, int s) {
+    if (s < a.top_k) {
+        unsigned e = a.expert_ids[s];
+        if (e >= (unsigned)a.num_experts) return nullptr;
+        return a.page_table + (size_t)e * 3 * a.P;
+    }
+    return a.shared_pages;
+}
+
+
+// Pipelined (bulk-copy staged) variants, defined in moe_pipe.cu.  They return VIB3_ERR_UNSUPPORTED
+// without launching when the shape does not meet their alignment rules; the caller then uses the
+// direct-load kernels.
+int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st);
+int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st);
+int sm_count();
+
+// Run-time switch: 1 (default) = staged kernels where the shape allows, 0 = direct-load kernels only.
+extern int g_use_pipeline;
+
+}  // namespace vib3

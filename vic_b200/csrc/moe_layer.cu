@@ -13,48 +13,9 @@
 // page's device pointer and row range (segment 0 = up, 1 = gate, 2 = down,
 // src/core/types.rs:204).  The experts of the token are read from device memory (router
 // output), so no host synchronisation sits between the router and the experts.
-#include "int4_math.cuh"
-#include "launch_common.h"
+#include "moe_common.cuh"
 
 namespace vib3 {
-
-constexpr int kMaxSlots = 17;   // MAX_ACTIVE_EXPERTS (src/core/types.rs:26) + one shared expert
-constexpr int kMaxPages = 16;   // pages per segment the kernels accept (Mixtral-shape needs 16)
-constexpr int kSegUp = 0, kSegGate = 1, kSegDown = 2;
-
-struct MoeLayerArgs {
-    const void* x;                 // [H] activations
-    int x_dtype;                   // XDType
-    const PageEntry* page_table;   // [num_experts][3][P]
-    const PageEntry* shared_pages; // [3][P] or null
-    const unsigned short* expert_ids;  // [top_k], device
-    const float* expert_weights;       // [top_k], device
-    int top_k;
-    int num_experts;
-    float shared_weight;
-    __half* act;                   // [slots][I] scratch
-    float* out;                    // [H]
-    int out_accumulate;            // 0: out = layer output; 1: out += layer output (residual add)
-    int H, I, P;
-    int rpp_gu, rpp_dn;            // rows per page of gate/up and of down
-    int* status;                   // device status word, or null
-};
-
-enum StatusBits : int { kStatusMissingPage = 1, kStatusBadExpert = 2 };
-
-__device__ __forceinline__ void flag(int* status, int bit) {
-    if (status) atomicOr(status, bit);
-}
-
-// Resolve the page-table block ([3][P] entries) of slot s: routed expert or the shared expert.
-__device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, int s) {
-    if (s < a.top_k) {
-        unsigned e = a.expert_ids[s];
-        if (e >= (unsigned)a.num_experts) return nullptr;
-        return a.page_table + (size_t)e * 3 * a.P;
-    }
-    return a.shared_pages;
-}
 
 // ── gate/up + SiLU ─────────────────────────────────────────────────────────────────────────
 // One warp per (slot, row).  Lane l takes chunks l, l+32, ... of the row: one 16-byte load of
@@ -77,7 +38,7 @@ __global__ void __launch_bounds__(256, 2) moe_gateup_kernel(MoeLayerArgs a) {
         else if (rem == 0) flag(a.status, kStatusBadExpert);
         tab[i] = e;
     }
-    stage_x<MATH>(xs, a.x, a.x_dtype, a.H, threadIdx.x, blockDim.x);
+    stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, threadIdx.x, blockDim.x);
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -141,12 +102,12 @@ __global__ void __launch_bounds__(256, 2) moe_gateup_kernel(MoeLayerArgs a) {
 // accumulated in plan order, so the result does not depend on scheduling.
 template <int B, int SB>
 __global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
-    using MATH = MathF16;
+    using MATH = MathQ16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const int nchunks = a.I / kGroupSize;
-    __half* acts = reinterpret_cast<__half*>(smem_raw);  // [slots][nchunks * kStride]
-    PageEntry* tab = reinterpret_cast<PageEntry*>(smem_raw + (size_t)slots * nchunks * MATH::kStride * sizeof(__half));
+    MATH::XS* acts = reinterpret_cast<MATH::XS*>(smem_raw);  // [slots][nchunks * kStride]
+    PageEntry* tab = reinterpret_cast<PageEntry*>(smem_raw + (size_t)slots * nchunks * MATH::kStride * sizeof(MATH::XS));
     float* wts = reinterpret_cast<float*>(tab + slots * a.P);
 
     for (int i = threadIdx.x; i < slots * a.P; i += blockDim.x) {
@@ -157,8 +118,8 @@ __global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
         tab[i] = e;
     }
     for (int s = threadIdx.x; s < slots; s += blockDim.x) wts[s] = s < a.top_k ? a.expert_weights[s] : a.shared_weight;
-    for (int s = 0; s < slots; ++s)
-        stage_x<MATH>(acts + (size_t)s * nchunks * MATH::kStride, a.act + (size_t)s * a.I, X_F16, a.I, threadIdx.x, blockDim.x);
+    // act is [slots][I] and the staged layout is [slots][chunks]: one vector of slots * I values
+    stage_activation<MATH>(acts, a.act, X_F16, slots * a.I, threadIdx.x, blockDim.x);
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -209,7 +170,7 @@ __global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
                 }
 #pragma unroll
                 for (int ss = 0; ss < SB; ++ss) {
-                    const __half* xs = acts + (size_t)min(s0 + ss, slots - 1) * nchunks * MATH::kStride;
+                    const MATH::XS* xs = acts + (size_t)min(s0 + ss, slots - 1) * nchunks * MATH::kStride;
 #pragma unroll
                     for (int i = 0; i < B; ++i) {
                         const int c = min(c0 + 32 * i, nchunks - 1);
@@ -237,7 +198,7 @@ __global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
 
 // ── host side ──────────────────────────────────────────────────────────────────────────────
 
-static int sm_count() {
+int sm_count() {
     static int n = [] {
         int dev = 0, v = 0;
         cudaGetDevice(&dev);
@@ -246,6 +207,8 @@ static int sm_count() {
     }();
     return n;
 }
+
+int g_use_pipeline = 1;
 
 template <class K>
 static int ensure_smem(K kernel, size_t bytes) {
@@ -270,7 +233,7 @@ static int launch_gateup(const MoeLayerArgs& a, cudaStream_t st) {
 template <int B, int SB>
 static int launch_down(const MoeLayerArgs& a, cudaStream_t st) {
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-    const size_t smem = (size_t)slots * (a.I / kGroupSize) * kXStrideH * sizeof(__half) + (size_t)slots * a.P * sizeof(PageEntry) + slots * sizeof(float);
+    const size_t smem = (size_t)slots * (a.I / kGroupSize) * MathQ16::kStride + (size_t)slots * a.P * sizeof(PageEntry) + slots * sizeof(float);
     if (int e = ensure_smem(moe_down_kernel<B, SB>, smem)) return e;
     int grid = min(sm_count(), (a.H + 11) / 12);
     moe_down_kernel<B, SB><<<grid, 384, smem, st>>>(a);
@@ -296,7 +259,7 @@ static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void
     if (rows_per_page_gate_up <= 0 || rows_per_page_down <= 0) return VIB3_ERR_SHAPE;
     if ((long long)rows_per_page_gate_up * pages_per_segment < expert_hidden_dim) return VIB3_ERR_SHAPE;
     if ((long long)rows_per_page_down * pages_per_segment < hidden_dim) return VIB3_ERR_SHAPE;
-    if (((uintptr_t)x & 3) || ((uintptr_t)page_table & 15) || ((uintptr_t)shared_pages & 15) ||
+    if (((uintptr_t)x & 15) || ((uintptr_t)page_table & 15) || ((uintptr_t)shared_pages & 15) ||
         ((uintptr_t)act_scratch & 15) || ((uintptr_t)out & 3)) return VIB3_ERR_ALIGN;
 
     MoeLayerArgs a;
@@ -309,17 +272,22 @@ static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void
     cudaStream_t st = (cudaStream_t)stream;
 
     int err = 0;
+    if ((phases & 1) && g_use_pipeline) {
+        err = launch_gateup_pipelined(a, st);
+        if (err == 0) phases &= ~1;
+        else if (err != VIB3_ERR_UNSUPPORTED) return err;
+    }
+    if ((phases & 2) && !(phases & 1) && g_use_pipeline) {
+        err = launch_down_pipelined(a, st);
+        if (err == 0) phases &= ~2;
+        else if (err != VIB3_ERR_UNSUPPORTED) return err;
+    }
+    err = 0;
     if (phases & 1) {
         const int lane_chunks_gu = (hidden_dim / kGroupSize + 31) / 32;
-        if (x_dtype == X_F32) {
-            err = lane_chunks_gu % 7 == 0 ? launch_gateup<MathF32, 7>(a, st)
-                : lane_chunks_gu % 4 == 0 ? launch_gateup<MathF32, 4>(a, st)
-                : lane_chunks_gu % 2 == 0 ? launch_gateup<MathF32, 2>(a, st) : launch_gateup<MathF32, 1>(a, st);
-        } else {
-            err = lane_chunks_gu % 7 == 0 ? launch_gateup<MathF16, 7>(a, st)
-                : lane_chunks_gu % 4 == 0 ? launch_gateup<MathF16, 4>(a, st)
-                : lane_chunks_gu % 2 == 0 ? launch_gateup<MathF16, 2>(a, st) : launch_gateup<MathF16, 1>(a, st);
-        }
+        err = lane_chunks_gu % 7 == 0 ? launch_gateup<MathQ16, 7>(a, st)
+            : lane_chunks_gu % 4 == 0 ? launch_gateup<MathQ16, 4>(a, st)
+            : lane_chunks_gu % 2 == 0 ? launch_gateup<MathQ16, 2>(a, st) : launch_gateup<MathQ16, 1>(a, st);
         if (err) return err;
     }
     if (phases & 2) {
@@ -341,6 +309,14 @@ static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void
     x, x_dtype, page_table, num_experts, shared_pages, expert_ids, expert_weights, top_k, shared_weight, act_scratch, \
         out, out_accumulate, hidden_dim, expert_hidden_dim, pages_per_segment, rows_per_page_gate_up,               \
         rows_per_page_down, group_size, status, stream
+
+// key 0: staged (bulk-copy) kernels on/off.  Returns the previous value, or VIB3_ERR_UNSUPPORTED.
+extern "C" int vib3_config_set(int key, int value) {
+    if (key != 0) return VIB3_ERR_UNSUPPORTED;
+    const int old = g_use_pipeline;
+    g_use_pipeline = value ? 1 : 0;
+    return old;
+}
 
 extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, VIB3_MOE_PASS); }
 extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, VIB3_MOE_PASS); }

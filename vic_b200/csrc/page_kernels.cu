@@ -132,7 +132,7 @@ static int launch_fast(const PageGemvArgs& a, cudaStream_t st) {
 
 template <class MATH, int NR>
 static int launch_page_gemv(const PageGemvArgs& a, cudaStream_t st) {
-    bool fast = a.group_size == kGroupSize && a.K % kGroupSize == 0 && a.K <= 65536;
+    bool fast = a.group_size == kGroupSize && a.K % kGroupSize == 0 && a.K <= 65536 && (((uintptr_t)a.x) & 15) == 0;
     for (int r = 0; r < NR; ++r) fast = fast && (((uintptr_t)a.codes[r]) & 15) == 0 && (((uintptr_t)a.scales[r]) & 1) == 0;
     if (!fast) {
         page_gemv_general_kernel<NR><<<(a.M + 7) / 8, 256, 0, st>>>(a);

@@ -44,7 +44,7 @@ struct RouterArgs {
     const float* bias;    // [E] or null
     unsigned short* out_ids;
     float* out_weights;
-    unsigned int* counter;  // one zeroed word of workspace (single-launch path only)
+    unsigned int* counter;  // two words of workspace (single-launch path only)
     int H, E, top_k, mode;
     float scaling;
     int normalize;
@@ -55,6 +55,21 @@ __device__ __forceinline__ float load_w(const void* W, int w_dtype, size_t i) {
     return w_dtype == W_F32 ? reinterpret_cast<const float*>(W)[i]
                             : __half2float(reinterpret_cast<const __half*>(W)[i]);
 }
+template <int WD>
+__device__ __forceinline__ float load_w_t(const void* W, size_t i) {
+    if (WD == W_F32) {
+        float v;
+        asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(reinterpret_cast<const float*>(W) + i));
+        return v;
+    }
+    return __half2float(__ushort_as_half(ldg_stream2(reinterpret_cast<const __half*>(W) + i)));
+}
+template <int XD>
+__device__ __forceinline__ float load_x_t(const void* x, int i) {
+    if (XD == X_F32) return __ldg(reinterpret_cast<const float*>(x) + i);
+    if (XD == X_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(x) + i));
+    return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(x) + i));
+}
 
 // shfl_down tree of the reference (kernels.cu:52-57); only lane 0's value is meaningful.
 __device__ __forceinline__ float warp_sum_down(float v) {
@@ -64,7 +79,7 @@ __device__ __forceinline__ float warp_sum_down(float v) {
 }
 
 // Logit of one expert with 128 threads (lane = chain index); result valid in chain 0.
-template <int U>
+template <int U, int XD, int WD>
 __device__ __forceinline__ void expert_logit(const RouterArgs& a, int expert, int chain, float* smem4, float* smem4_abs,
                                              float& logit, float& absum) {
     const size_t base = (size_t)expert * a.H;
@@ -74,8 +89,8 @@ __device__ __forceinline__ void expert_logit(const RouterArgs& a, int expert, in
         float w[U], xv[U];
 #pragma unroll
         for (int i = 0; i < U; ++i) {
-            w[i] = load_w(a.W, a.w_dtype, base + d + i * kChains);
-            xv[i] = load_x_as_f32(a.x, a.x_dtype, d + i * kChains);
+            w[i] = load_w_t<WD>(a.W, base + d + i * kChains);
+            xv[i] = load_x_t<XD>(a.x, d + i * kChains);
         }
 #pragma unroll
         for (int i = 0; i < U; ++i) {
@@ -84,8 +99,8 @@ __device__ __forceinline__ void expert_logit(const RouterArgs& a, int expert, in
         }
     }
     for (; d < a.H; d += kChains) {
-        const float w = load_w(a.W, a.w_dtype, base + d);
-        const float xv = load_x_as_f32(a.x, a.x_dtype, d);
+        const float w = load_w_t<WD>(a.W, base + d);
+        const float xv = load_x_t<XD>(a.x, d);
         acc = fmaf(xv, w, acc);
         aabs += fabsf(xv * w);
     }
@@ -117,7 +132,8 @@ __device__ __forceinline__ float sigmoid_ref(float z) {
 
 // Scoring + top-k by one CTA of 256 threads; every thread owns experts tid and tid+256.
 // smem: sel[E], sig[E], keys for the block reductions.
-struct TopKSmem {
+struct __align__(16) TopKSmem {
+    float prod[8][1024];   // per-warp products of the sequential-order recomputation (16-byte aligned: read as float4)
     float logit[kRouterMaxExperts];
     float sig[kRouterMaxExperts];
     float sel[kRouterMaxExperts];
@@ -125,6 +141,8 @@ struct TopKSmem {
     int chosen[kRouterMaxTopK + 1];
     float eps_max[8];
     int redo;
+    int ncand;
+    int cand[kRouterMaxExperts];
 };
 
 __device__ void block_select(const RouterArgs& a, TopKSmem& sm, int nsel) {
@@ -211,20 +229,54 @@ __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
         }
         __syncthreads();
         if (sm.redo) {
+            // candidates: everything that sits within tau of one of the best k+1
             const int last = sm.chosen[nsel - 1];
             const float floor_sel = (last >= 0 ? sm.sel[last] : -INFINITY) - tau;
+            if (tid == 0) sm.ncand = 0;
+            __syncthreads();
             for (int e = tid; e < a.E; e += blockDim.x) {
-                if (sm.sel[e] >= floor_sel) {
-                    // the CPU router's order: one chain, multiply then add (kernels.rs:2346-2350)
-                    const size_t base = (size_t)e * a.H;
-                    float acc = 0.f;
-                    for (int d = 0; d < a.H; ++d)
-                        acc = __fadd_rn(acc, __fmul_rn(load_x_as_f32(a.x, a.x_dtype, d), load_w(a.W, a.w_dtype, base + d)));
+                bool cand = false;
+                if (sm.sel[e] >= floor_sel)
+                    for (int i = 0; i < nsel; ++i) {
+                        const int c = sm.chosen[i];
+                        if (c >= 0 && c != e && fabsf(sm.sel[e] - sm.sel[c]) <= tau) cand = true;
+                    }
+                if (cand) sm.cand[atomicAdd(&sm.ncand, 1)] = e;
+            }
+            __syncthreads();
+            // the CPU router's order: one chain per expert, multiply then add, d = 0 .. H-1
+            // (kernels.rs:2346-2350).  A warp forms 1024 rounded products at a time in parallel;
+            // lane 0 then adds them in order.
+            const int wid = tid >> 5, lane = tid & 31;
+            for (int ci = wid; ci < sm.ncand; ci += 8) {
+                const int e = sm.cand[ci];
+                const size_t base = (size_t)e * a.H;
+                float acc = 0.f;
+                for (int d0 = 0; d0 < a.H; d0 += 1024) {
+                    const int n = min(1024, a.H - d0);
+                    for (int i = lane; i < n; i += 32)
+                        sm.prod[wid][i] = __fmul_rn(load_x_as_f32(a.x, a.x_dtype, d0 + i), load_w(a.W, a.w_dtype, base + d0 + i));
+                    __syncwarp();
+                    if (lane == 0) {
+                        int i = 0;
+                        for (; i + 4 <= n; i += 4) {
+                            const float4 p = *reinterpret_cast<const float4*>(&sm.prod[wid][i]);
+                            acc = __fadd_rn(acc, p.x);
+                            acc = __fadd_rn(acc, p.y);
+                            acc = __fadd_rn(acc, p.z);
+                            acc = __fadd_rn(acc, p.w);
+                        }
+                        for (; i < n; ++i) acc = __fadd_rn(acc, sm.prod[wid][i]);
+                    }
+                    __syncwarp();
+                }
+                if (lane == 0) {
                     sm.logit[e] = acc;
                     a.scores[e] = acc;
                 }
             }
             __syncthreads();
+            if (tid == 0 && a.counter) a.counter[1] += 1u;  // diagnostics: near-tie recomputations so far
             block_score(a, sm);
             block_select(a, sm, k);
         }
@@ -259,7 +311,7 @@ __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
 
 // GEMV: 2 experts per CTA, 128 threads each.  When `a.counter` is set, the CTA that finishes
 // last also does the scoring and selection (single launch).
-template <int U>
+template <int U, int XD, int WD>
 __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
     __shared__ float red[2][4], red_abs[2][4];
     __shared__ TopKSmem sm;
@@ -269,7 +321,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
     float logit = 0.f, absum = 0.f;
     // both halves of the CTA must reach the __syncthreads inside expert_logit
     const int e_clamped = min(expert, a.E - 1);
-    expert_logit<U>(a, e_clamped, chain, red[local], red_abs[local], logit, absum);
+    expert_logit<U, XD, WD>(a, e_clamped, chain, red[local], red_abs[local], logit, absum);
     if (chain == 0 && expert < a.E) {
         a.scores[expert] = logit;
         if (a.exact_order) a.scores[a.E + expert] = absum;
@@ -291,6 +343,23 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
 __global__ void __launch_bounds__(256) router_topk_kernel(RouterArgs a) {
     __shared__ TopKSmem sm;
     router_finish(a, sm);
+}
+
+static int launch_router(const RouterArgs& a, cudaStream_t st) {
+    const int grid = (a.E + 1) / 2;
+#define VIB3_ROUTER_CASE(XD, WD)                                                      \
+    if (a.x_dtype == XD && a.w_dtype == WD) {                                         \
+        router_kernel<14, XD, WD><<<grid, 256, 0, st>>>(a);                           \
+        return (int)cudaGetLastError();                                               \
+    }
+    VIB3_ROUTER_CASE(X_F32, W_F16)
+    VIB3_ROUTER_CASE(X_F32, W_F32)
+    VIB3_ROUTER_CASE(X_F16, W_F16)
+    VIB3_ROUTER_CASE(X_F16, W_F32)
+    VIB3_ROUTER_CASE(X_BF16, W_F16)
+    VIB3_ROUTER_CASE(X_BF16, W_F32)
+#undef VIB3_ROUTER_CASE
+    return VIB3_ERR_UNSUPPORTED;
 }
 
 static int check_router(const RouterArgs& a) {
@@ -316,8 +385,7 @@ extern "C" int vib3_launch_router_gemv(const void* x_f16, const void* W_f16, flo
     RouterArgs a{};
     a.x = x_f16; a.x_dtype = X_F16; a.W = W_f16; a.w_dtype = W_F16; a.scores = scores; a.H = hidden_dim; a.E = num_experts;
     if (int e = check_router(a)) return e;
-    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, (cudaStream_t)stream>>>(a);
-    return (int)cudaGetLastError();
+    return launch_router(a, (cudaStream_t)stream);
 }
 
 extern "C" int vib3_launch_router_gemv_f32(const void* x_f32, const void* W_f16, float* scores, int hidden_dim,
@@ -325,8 +393,7 @@ extern "C" int vib3_launch_router_gemv_f32(const void* x_f32, const void* W_f16,
     RouterArgs a{};
     a.x = x_f32; a.x_dtype = X_F32; a.W = W_f16; a.w_dtype = W_F16; a.scores = scores; a.H = hidden_dim; a.E = num_experts;
     if (int e = check_router(a)) return e;
-    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, (cudaStream_t)stream>>>(a);
-    return (int)cudaGetLastError();
+    return launch_router(a, (cudaStream_t)stream);
 }
 
 // Reference signature: two launches (GEMV, then selection), weights always normalised in
@@ -341,14 +408,14 @@ extern "C" int vib3_launch_router_topk(const void* x_f32, const void* W_f16, flo
     if (int e = check_router(a)) return e;
     if (int e = check_topk(a)) return e;
     cudaStream_t st = (cudaStream_t)stream;
-    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, st>>>(a);
-    if (cudaError_t e = cudaGetLastError()) return (int)e;
+    if (int e = launch_router(a, st)) return e;
     router_topk_kernel<<<1, 256, 0, st>>>(a);
     return (int)cudaGetLastError();
 }
 
 // Extended launcher: one launch.  scores_buf holds E floats (2E when exact_order != 0);
-// workspace is one 32-bit word that must be zero before the first call and is left zero.
+// workspace is two 32-bit words, zero before the first call: [0] is an arrival counter that every
+// call leaves at zero, [1] counts the near-tie recomputations done so far (diagnostics).
 extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
                                           const float* bias, unsigned short* out_ids, float* out_weights,
                                           int hidden_dim, int num_experts, int top_k, int scoring_mode,
@@ -362,6 +429,5 @@ extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void
     if (int e = check_topk(a)) return e;
     if (!workspace) return VIB3_ERR_NULL;
     if (x_dtype < X_F32 || x_dtype > X_BF16 || (w_dtype != W_F16 && w_dtype != W_F32)) return VIB3_ERR_UNSUPPORTED;
-    router_kernel<14><<<(num_experts + 1) / 2, 256, 0, (cudaStream_t)stream>>>(a);
-    return (int)cudaGetLastError();
+    return launch_router(a, (cudaStream_t)stream);
 }

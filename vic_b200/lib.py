@@ -56,6 +56,7 @@ SIGNATURES = {
                                                 _i, _i, _vp, _vp]),
     "vib3_launch_moe_down_int4_paged": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _i, _i, _i,
                                              _i, _i, _vp, _vp]),
+    "vib3_config_set": (_i, [_i, _i]),
     "vib3_pool_create": (_vp, [_vp, C.c_size_t, C.c_uint64]),
     "vib3_pool_destroy": (None, [_vp]),
     "vib3_pool_load_page": (C.c_longlong, [_vp, C.c_uint16, C.c_uint16, C.c_uint16, C.c_uint16, C.c_uint16,
