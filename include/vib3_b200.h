@@ -30,6 +30,7 @@ extern "C" {
 #define VIB3_ERR_SHAPE (-5)
 #define VIB3_ERR_RANGE (-6)
 #define VIB3_ERR_STATE (-7)
+#define VIB3_ERR_CAPACITY (-8)
 
 /* activation dtypes (x_dtype) and router-weight dtypes (w_dtype) */
 #define VIB3_X_F32 0
@@ -131,6 +132,22 @@ int vib3_launch_moe_down_int4_paged(const void* x, int x_dtype, const void* page
                                     float* out, int out_accumulate, int hidden_dim, int expert_hidden_dim,
                                     int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down,
                                     int group_size, int* status, void* stream);
+
+/* Same work as vib3_launch_moe_layer_int4_paged, for callers that cannot supply act_scratch because
+ * they may not allocate device memory (all VRAM already given to a page pool, allocation forbidden
+ * after warm-up, no allocator in the binding).  This entry point has no counterpart in the
+ * reference.  The intermediate lives in a 544 KiB array inside the library image, held by every GPU
+ * the library is loaded on.  Limit: (top_k + 1 if shared_pages) * expert_hidden_dim <= 278,528, else
+ * VIB3_ERR_CAPACITY and nothing is launched.  The first call on a device resolves the array's
+ * address: issue it before any stream capture.  All calls on a device share the array; calls whose
+ * kernels may overlap on the GPU race on it.  Nothing is allocated or freed. */
+int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const void* page_table, int num_experts,
+                                             const void* shared_pages, const unsigned short* expert_ids,
+                                             const float* expert_weights, int top_k, float shared_weight,
+                                             float* out, int out_accumulate, int hidden_dim,
+                                             int expert_hidden_dim, int pages_per_segment,
+                                             int rows_per_page_gate_up, int rows_per_page_down, int group_size,
+                                             int* status, void* stream);
 
 /* Library options.  key 0: use the bulk-copy staged MoE kernels where the shape allows (default 1);
  * 0 forces the direct-load kernels.  Returns the previous value. */

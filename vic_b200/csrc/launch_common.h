@@ -17,3 +17,4 @@
 #define VIB3_ERR_SHAPE (-5)
 #define VIB3_ERR_RANGE (-6)        // row range outside the matrix, page missing
 #define VIB3_ERR_STATE (-7)        // pool / planner object in the wrong state
+#define VIB3_ERR_CAPACITY (-8)     // request larger than a built-in fixed-size buffer

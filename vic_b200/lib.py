@@ -11,7 +11,7 @@ _lib = None
 
 ERR_NAMES = {
     -1: "unsupported", -2: "count out of range", -3: "null pointer", -4: "misaligned pointer",
-    -5: "bad shape", -6: "row range / page missing", -7: "wrong state",
+    -5: "bad shape", -6: "row range / page missing", -7: "wrong state", -8: "larger than the built-in buffer",
 }
 
 
@@ -56,6 +56,8 @@ SIGNATURES = {
                                                 _i, _i, _vp, _vp]),
     "vib3_launch_moe_down_int4_paged": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _i, _i, _i,
                                              _i, _i, _vp, _vp]),
+    "vib3_launch_moe_layer_int4_paged_noalloc": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _i, _i, _i, _i,
+                                                      _i, _vp, _vp]),
     "vib3_config_set": (_i, [_i, _i]),
     "vib3_pool_create": (_vp, [_vp, C.c_size_t, C.c_uint64]),
     "vib3_pool_destroy": (None, [_vp]),
