@@ -193,6 +193,9 @@ def profile_small(n):
     sh = MoeShape("kimi16", KIMI.hidden, KIMI.intermediate, 16, KIMI.top_k, 1, KIMI.scoring, KIMI.scaling_factor, True)
     model = build_synthetic_moe(sh, 2, dev, seed=SEED, slot_seed=99)
     dec = MoeDecoder(model, exact_order=False)
+    if os.environ.get("VIB3_BENCH_DIRECT") == "1":   # A/B: direct-load kernels instead of the staged ones
+        from vic_b200.lib import lib
+        lib().vib3_config_set(0, 0)
     g = torch.Generator(device=dev).manual_seed(1)
     xs = synth_activation(sh, g, dev, torch.bfloat16, 8)
     for i in range(n):

@@ -188,6 +188,22 @@ struct MathF32 {
     static constexpr bool kChunkSums = false;
 };
 
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ unsigned short lds16(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
 // ── Math policy Q16 (integer dot products).  The activation chunk (32 values) is held as 16-bit
 // fixed point relative to the chunk's largest magnitude, x_i = sx * q_i with |q_i| <= 32512 and
 // q_i = 256 * hi_i + lo_i (hi signed, lo in 0..255).  One dp4a multiplies four 4-bit codes
@@ -239,6 +255,38 @@ struct MathQ16 {
         }
         const float sx = *reinterpret_cast<const float*>(xchunk + 64);
         const int sq8 = *reinterpret_cast<const int*>(xchunk + 68);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const int t = dh[r] * 256 + dl[r] - sq8;
+            acc[r] = fmaf((float)t, s[r] * sx, acc[r]);
+        }
+    }
+
+    // Same arithmetic with the staged chunk given as a 32-bit shared-memory address: explicit
+    // ld.shared, offsets that are constants after unrolling fold into the instruction.
+    template <int NR>
+    static __device__ __forceinline__ void chunk_s(const uint4 (&q)[NR], const float (&s)[NR], uint32_t xaddr,
+                                                   float (&acc)[NR]) {
+        int dh[NR], dl[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { dh[r] = 0; dl[r] = 0; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 xv = lds128(xaddr + 16 * j);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const uint32_t w = j == 0 ? q[r].x : j == 1 ? q[r].y : j == 2 ? q[r].z : q[r].w;
+                const uint32_t we = w & 0x0F0F0F0Fu;
+                const uint32_t wo = (w >> 4) & 0x0F0F0F0Fu;
+                dh[r] = dp4a_us(we, xv.x, dh[r]);
+                dl[r] = dp4a_uu(we, xv.z, dl[r]);
+                dh[r] = dp4a_us(wo, xv.y, dh[r]);
+                dl[r] = dp4a_uu(wo, xv.w, dl[r]);
+            }
+        }
+        const uint2 tail = lds64(xaddr + 64);  // {sx, 8 * sum q}
+        const float sx = __uint_as_float(tail.x);
+        const int sq8 = (int)tail.y;
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             const int t = dh[r] * 256 + dl[r] - sq8;

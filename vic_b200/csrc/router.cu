@@ -139,7 +139,7 @@ struct __align__(16) TopKSmem {
     float sel[kRouterMaxExperts];
     unsigned long long wmax[2][8];
     int chosen[kRouterMaxTopK + 1];
-    float eps_max[8];
+    float wid[kRouterMaxExperts];
     int redo;
     int ncand;
     int cand[kRouterMaxExperts];
@@ -201,45 +201,41 @@ __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
     block_select(a, sm, nsel);
 
     if (a.exact_order && nsel > 1) {
-        // Bound on |logit(order A) - logit(order B)| for fp32 sums of H products:
-        // 16 * 2^-24 * (sqrt(H) * |S| + sum|x w|), maximised over experts.
-        float eps = 0.f;
+        // Half-width of each expert's selection score under a change of summation order.  The
+        // logits of two fp32 summation orders of H products differ by less than
+        //     eps = 16 * 2^-24 * (sqrt(H) * |S| + sum |x w|)
+        // (the oracle's tests check this bound with a 4x margin); a selection score moves by at
+        // most eps times the local slope of the scoring function (1 for raw logits, s (1 - s) for
+        // the sigmoid, taken 1.25x for the curvature) plus a few ulps of rounding.
         for (int e = tid; e < a.E; e += blockDim.x) {
             const float ab = __ldcg(a.scores + a.E + e);
-            eps = fmaxf(eps, 16.f * 5.9604645e-8f * (sqrtf((float)a.H) * fabsf(sm.logit[e]) + ab));
+            const float eps = 16.f * 5.9604645e-8f * (sqrtf((float)a.H) * fabsf(sm.logit[e]) + ab);
+            const float slope = a.mode == 0 ? 1.f : 1.25f * sm.sig[e] * (1.f - sm.sig[e]);
+            sm.wid[e] = eps * slope + 2.f * 1.1920929e-7f * fmaxf(fabsf(sm.sel[e]), 1e-30f);
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) eps = fmaxf(eps, __shfl_xor_sync(0xffffffffu, eps, o));
-        if ((tid & 31) == 0) sm.eps_max[tid >> 5] = eps;
         if (tid == 0) sm.redo = 0;
         __syncthreads();
-        eps = sm.eps_max[0];
-#pragma unroll
-        for (int w = 1; w < 8; ++w) eps = fmaxf(eps, sm.eps_max[w]);
-        // selection scores move by at most eps (softmax: raw logits) or eps/4 (sigmoid slope)
-        const float tau = 2.f * (a.mode == 0 ? eps : 0.25f * eps) + 4.f * 1.1920929e-7f;
         if (tid == 0) {
             int redo = 0;
             for (int i = 0; i + 1 < nsel; ++i) {
                 const int e0 = sm.chosen[i], e1 = sm.chosen[i + 1];
                 if (e0 < 0 || e1 < 0) break;
-                if (sm.sel[e0] - sm.sel[e1] <= tau) redo = 1;
+                if (sm.sel[e0] - sm.sel[e1] <= sm.wid[e0] + sm.wid[e1]) redo = 1;
             }
             sm.redo = redo;
         }
         __syncthreads();
         if (sm.redo) {
-            // candidates: everything that sits within tau of one of the best k+1
+            // candidates: every expert whose score interval overlaps that of one of the best k+1
             const int last = sm.chosen[nsel - 1];
-            const float floor_sel = (last >= 0 ? sm.sel[last] : -INFINITY) - tau;
             if (tid == 0) sm.ncand = 0;
             __syncthreads();
             for (int e = tid; e < a.E; e += blockDim.x) {
                 bool cand = false;
-                if (sm.sel[e] >= floor_sel)
+                if (last < 0 || sm.sel[e] + sm.wid[e] >= sm.sel[last] - sm.wid[last])
                     for (int i = 0; i < nsel; ++i) {
                         const int c = sm.chosen[i];
-                        if (c >= 0 && c != e && fabsf(sm.sel[e] - sm.sel[c]) <= tau) cand = true;
+                        if (c >= 0 && c != e && fabsf(sm.sel[e] - sm.sel[c]) <= sm.wid[e] + sm.wid[c]) cand = true;
                     }
                 if (cand) sm.cand[atomicAdd(&sm.ncand, 1)] = e;
             }
