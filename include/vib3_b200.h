@@ -150,7 +150,9 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
                                              int* status, void* stream);
 
 /* Library options.  key 0: use the bulk-copy staged MoE kernels where the shape allows (default 1);
- * 0 forces the direct-load kernels.  Returns the previous value. */
+ * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
+ * launch so that their prologue overlaps the previous kernel's tail (default 1).  Returns the previous
+ * value. */
 int vib3_config_set(int key, int value);
 
 /* ── Host side: VRAM page pool and query planner (C view of the C++ classes) ────────────── */

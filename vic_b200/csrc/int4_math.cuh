@@ -262,6 +262,62 @@ struct MathQ16 {
         }
     }
 
+    // Same arithmetic with the quantised activation chunk held in registers (xv[j] = the uint4 of
+    // word j, sx, sq8 as in the staged layout).
+    static __device__ __forceinline__ float chunk_r(const uint4& q, float s, const uint4 (&xv)[4], float sx, int sq8,
+                                                    float acc) {
+        int dh = 0, dl = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t w = j == 0 ? q.x : j == 1 ? q.y : j == 2 ? q.z : q.w;
+            const uint32_t we = w & 0x0F0F0F0Fu;
+            const uint32_t wo = (w >> 4) & 0x0F0F0F0Fu;
+            dh = dp4a_us(we, xv[j].x, dh);
+            dl = dp4a_uu(we, xv[j].z, dl);
+            dh = dp4a_us(wo, xv[j].y, dh);
+            dl = dp4a_uu(wo, xv[j].w, dl);
+        }
+        const int t = dh * 256 + dl - sq8;
+        return fmaf((float)t, s * sx, acc);
+    }
+
+    // Quantise one chunk (32 consecutive fp16 values at `src`, 16-byte aligned) into registers, with
+    // exactly the arithmetic of stage_x_q16.
+    static __device__ __forceinline__ void quantize_chunk(const __half* src, uint4 (&xv)[4], float& sx, int& sq8) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 r = *reinterpret_cast<const uint4*>(src + 8 * j);
+            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __half2 h = *reinterpret_cast<const __half2*>(&w[k]);
+                v[8 * j + 2 * k] = __low2float(h);
+                v[8 * j + 2 * k + 1] = __high2float(h);
+            }
+        }
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(v[i]));
+        const float inv = m > 0.f ? 32512.f / m : 0.f;
+        int sq = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int q[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                q[k] = max(-32512, min(32512, __float2int_rn(v[8 * j + k] * inv)));
+                sq += q[k];
+            }
+            xv[j].x = (uint32_t)((q[0] >> 8) & 0xFF) | ((uint32_t)((q[2] >> 8) & 0xFF) << 8) | ((uint32_t)((q[4] >> 8) & 0xFF) << 16) | ((uint32_t)((q[6] >> 8) & 0xFF) << 24);
+            xv[j].y = (uint32_t)((q[1] >> 8) & 0xFF) | ((uint32_t)((q[3] >> 8) & 0xFF) << 8) | ((uint32_t)((q[5] >> 8) & 0xFF) << 16) | ((uint32_t)((q[7] >> 8) & 0xFF) << 24);
+            xv[j].z = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[2] & 0xFF) << 8) | ((uint32_t)(q[4] & 0xFF) << 16) | ((uint32_t)(q[6] & 0xFF) << 24);
+            xv[j].w = (uint32_t)(q[1] & 0xFF) | ((uint32_t)(q[3] & 0xFF) << 8) | ((uint32_t)(q[5] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+        }
+        sx = m * (1.0f / 32512.f);
+        sq8 = 8 * sq;
+    }
+
     // Same arithmetic with the staged chunk given as a 32-bit shared-memory address: explicit
     // ld.shared, offsets that are constants after unrolling fold into the instruction.
     template <int NR>

@@ -53,5 +53,7 @@ int sm_count();
 
 // Run-time switch: 1 (default) = staged kernels where the shape allows, 0 = direct-load kernels only.
 extern int g_use_pipeline;
+// 1 (default) = staged kernels are launched with programmatic dependent launch.
+extern int g_use_pdl;
 
 }  // namespace vib3

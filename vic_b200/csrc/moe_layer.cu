@@ -209,6 +209,7 @@ int sm_count() {
 }
 
 int g_use_pipeline = 1;
+int g_use_pdl = 1;
 
 template <class K>
 static int ensure_smem(K kernel, size_t bytes) {
@@ -310,12 +311,20 @@ static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void
         out, out_accumulate, hidden_dim, expert_hidden_dim, pages_per_segment, rows_per_page_gate_up,               \
         rows_per_page_down, group_size, status, stream
 
-// key 0: staged (bulk-copy) kernels on/off.  Returns the previous value, or VIB3_ERR_UNSUPPORTED.
+// key 0: staged (bulk-copy) kernels on/off; key 1: programmatic dependent launch of the staged
+// kernels on/off.  Returns the previous value, or VIB3_ERR_UNSUPPORTED.
 extern "C" int vib3_config_set(int key, int value) {
-    if (key != 0) return VIB3_ERR_UNSUPPORTED;
-    const int old = g_use_pipeline;
-    g_use_pipeline = value ? 1 : 0;
-    return old;
+    if (key == 0) {
+        const int old = g_use_pipeline;
+        g_use_pipeline = value ? 1 : 0;
+        return old;
+    }
+    if (key == 1) {
+        const int old = g_use_pdl;
+        g_use_pdl = value ? 1 : 0;
+        return old;
+    }
+    return VIB3_ERR_UNSUPPORTED;
 }
 
 extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, VIB3_MOE_PASS); }

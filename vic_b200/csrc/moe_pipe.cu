@@ -24,7 +24,7 @@ constexpr int kConsumerWarps = 16;
 constexpr int kGroups = 4;                       // consumer groups; group g takes tiles g, g+4, ...
 constexpr int kTileRows = kConsumerWarps / kGroups;  // rows (row pairs) per stage: one per warp of a group
 constexpr int kPipeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 12;
 constexpr unsigned kSpinLimit = 1u << 22;
 constexpr size_t kSmemBudget = 227 * 1024;
 
@@ -62,6 +62,13 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned b
                  : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start
+// while its predecessor in the stream is still running; it must execute pdl_wait() before it reads
+// anything the predecessor wrote.  pdl_trigger() in the predecessor lets the successor's CTAs be
+// scheduled as soon as SM resources free up.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // A tile: up to kTileRows consecutive rows of one page of one slot.
 struct Tile {
     int slot, page, rin, nrows, row;  // row = first row inside the slot's matrix
@@ -71,10 +78,10 @@ struct Tile {
 // rows cut into pages of `rpp` rows.  Producer and consumers walk it identically.  The position is
 // kept incrementally (no division per tile).
 struct TileWalk {
-    int g, g_end, rows_per_slot, rpp;
+    int g, g_end, rows_per_slot, rpp, tile_rows;
     int slot, row, page, rin;
-    __device__ __forceinline__ TileWalk(int g0, int g1, int rows_per_slot_, int rpp_)
-        : g(g0), g_end(g1), rows_per_slot(rows_per_slot_), rpp(rpp_) {
+    __device__ __forceinline__ TileWalk(int g0, int g1, int rows_per_slot_, int rpp_, int tile_rows_ = kTileRows)
+        : g(g0), g_end(g1), rows_per_slot(rows_per_slot_), rpp(rpp_), tile_rows(tile_rows_) {
         slot = g0 / rows_per_slot;
         row = g0 - slot * rows_per_slot;
         page = row / rpp;
@@ -83,7 +90,7 @@ struct TileWalk {
     __device__ __forceinline__ bool next(Tile& t) {
         if (g >= g_end) return false;
         t.slot = slot; t.row = row; t.page = page; t.rin = rin;
-        int n = min(kTileRows, g_end - g);
+        int n = min(tile_rows, g_end - g);
         n = min(n, rpp - rin);
         n = min(n, rows_per_slot - row);
         t.nrows = n;
@@ -102,7 +109,7 @@ __device__ __forceinline__ void cta_share(int total, int& begin, int& end) {
 }
 
 // Ring bookkeeping.  Tile n of a CTA uses stage n % nstages (use number u = n / nstages of that
-// stage) and is consumed by group n % kGroups.  An mbarrier wait names its phase by one parity bit,
+// stage) and is consumed by group n % (number of groups).  An mbarrier wait names its phase by one parity bit,
 // so a waiter may be at most one phase ahead of the barrier.  Successive uses of a stage can belong
 // to different groups; therefore the group that has seen use u land publishes landed[stage] = u + 1,
 // and a group that wants use u first waits (bounded) until landed[stage] >= u.
@@ -148,6 +155,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     volatile unsigned* landed = reinterpret_cast<volatile unsigned*>(empty + kMaxStages);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
@@ -156,6 +164,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // the activation vector does not come from the router: quantise it before waiting for the router
+    if (warp < kConsumerWarps) stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
+    pdl_wait();  // expert ids and weights are the router's output
     for (int i = tid; i < slots * 2 * a.P; i += blockDim.x) {
         const int s = i / (2 * a.P), rem = i % (2 * a.P);
         const PageEntry* pg = slot_pages(a, s);
@@ -164,7 +175,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
         else if (rem == 0) flag(a.status, kStatusBadExpert);
         tab[i] = e;
     }
-    __syncthreads();  // the page entries are all the producer needs
+    __syncthreads();
 
     int g0, g1;
     cta_share(slots * a.I, g0, g1);
@@ -207,9 +218,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
         return;
     }
 
-    // ── consumers: quantise the activation vector while the first stages are in flight ──
-    stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
-    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");  // consumer warps only
+    // ── consumers ──
     const int group = warp / kTileRows, wi = warp % kTileRows;
     Ring ring{full, empty, landed, nstages};
     const uint32_t stages_addr = smem_u32(stages);
@@ -268,39 +277,48 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
 }
 
 // ── down + routing weight + accumulate, staged ─────────────────────────────────────────────
-// stage layout: per slot [codes R*I/2][scales R*I/16].  A tile is R = 4 output rows x all slots.
-// Its work units are (slot, pair of rows): the two rows share the slot's activation chunk loads.
-// The units of a tile are dealt round-robin to the 4 warps of the group; per-unit results (already
-// rounded to fp16 like the reference's down projection) meet in a small shared buffer, and after a
-// group barrier warp w adds row w's contributions in plan order.
+// Rows of the down matrices are short (I/2 bytes: 1 KB for I = 2048, two 16-byte chunks per lane),
+// and every output row needs all experts.  Re-reading an expert's activation chunks from shared
+// memory for every row would cost more shared-memory bandwidth than the codes themselves, so here
+// the activations stay in REGISTERS: two warps per expert slot; each lane quantises the two
+// activation chunks it is responsible for (the gate/up kernel's fp16 output) once, straight from
+// global memory, and keeps them for the whole kernel.  All consumer warps work on the same tile
+// (4 output rows x all slots; warp (slot, h) takes rows h and h+2), so every ring stage ahead of it
+// is look-ahead.  Per-row results y[row][slot] (rounded to fp16 as the reference's down projection)
+// meet in shared memory; after a barrier of the consumer warps, warp r adds row r in plan order.
+// stage layout: per slot [codes R*I/2][scales R*I/16], R = 4.
+constexpr int kDownRows = 4;
+constexpr int kDownWarpsPerSlot = 2;
+constexpr int kDownMaxThreads = 640;  // 19 warps for 9 slots; leaves ~100 registers per thread
+
 template <int NCH>
-__global__ void __launch_bounds__(kPipeThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int nstages) {
+__global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int nstages) {
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-    const int nchunks = a.I / kGroupSize;
+    const int cwarps = slots * kDownWarpsPerSlot;       // consumer warps; the producer is warp `cwarps`
     const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
-    const unsigned slot_bytes = kTileRows * (code_row + scale_row);
+    const unsigned slot_bytes = kDownRows * (code_row + scale_row);
     const unsigned stage_bytes = slots * slot_bytes;
 
     unsigned char* stages = smem_raw;
-    unsigned char* acts = stages + (size_t)nstages * stage_bytes;
-    PageEntry* tab = reinterpret_cast<PageEntry*>(acts + (size_t)slots * nchunks * MATH::kStride);
+    PageEntry* tab = reinterpret_cast<PageEntry*>(stages + (size_t)nstages * stage_bytes);
     uint64_t* full = reinterpret_cast<uint64_t*>(tab + slots * a.P);
     uint64_t* empty = full + kMaxStages;
-    volatile unsigned* landed = reinterpret_cast<volatile unsigned*>(empty + kMaxStages);
-    float* wts = const_cast<float*>(reinterpret_cast<volatile float*>(landed + kMaxStages));
-    float* ybuf = wts + kMaxSlots;  // [group][parity][row][kMaxSlots]
+    float* wts = reinterpret_cast<float*>(empty + kMaxStages);
+    float* ybuf = wts + kMaxSlots;  // [parity][row][kMaxSlots]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, kTileRows);
-            landed[s] = 0;
+            mbar_init(empty + s, cwarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Expert ids and routing weights were written by the router, which had completed before the
+    // gate/up kernel passed its own dependency wait, so they are visible here without waiting.
     for (int i = tid; i < slots * a.P; i += blockDim.x) {
         const int s = i / a.P, p = i - s * a.P;
         const PageEntry* pg = slot_pages(a, s);
@@ -309,16 +327,16 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_down_pipe_kernel(MoeLayer
         tab[i] = e;
     }
     for (int s = tid; s < slots; s += blockDim.x) wts[s] = s < a.top_k ? a.expert_weights[s] : a.shared_weight;
-    __syncthreads();  // tab is needed by the producer before the activations are staged
+    __syncthreads();
 
     int g0, g1;
     cta_share(a.H, g0, g1);
 
-    if (warp == kConsumerWarps) {
+    if (warp == cwarps) {
         // ── producer warp: the weights do not depend on the previous kernel, so streaming starts at
         // once.  Lane k < 2 * slots issues copy k of a tile (slot k / 2: codes for even k, scales for
         // odd k); the byte total is summed across lanes for lane 0 to arm the barrier ──
-        TileWalk walk(g0, g1, a.H, a.rpp_dn);
+        TileWalk walk(g0, g1, a.H, a.rpp_dn, kDownRows);
         Tile t;
         int n = 0;
         bool ok = true;
@@ -342,7 +360,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_down_pipe_kernel(MoeLayer
             __syncwarp();
             if (mine) {
                 const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
-                if (lane & 1) bulk_load(sb + s * slot_bytes + kTileRows * code_row, base + (size_t)e.row_count * code_row + (size_t)t.rin * scale_row, bytes, full + st);
+                if (lane & 1) bulk_load(sb + s * slot_bytes + kDownRows * code_row, base + (size_t)e.row_count * code_row + (size_t)t.rin * scale_row, bytes, full + st);
                 else bulk_load(sb + s * slot_bytes, base + (size_t)t.rin * code_row, bytes, full + st);
             }
             ++n;
@@ -354,77 +372,58 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_down_pipe_kernel(MoeLayer
         return;
     }
 
-    // consumers quantise the activations of every slot (written by the gate/up kernel)
-    stage_activation<MATH>(acts, a.act, X_F16, slots * a.I, tid, kConsumerWarps * 32);
-    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");  // consumer warps only
+    // ── consumers: warp (s, h) keeps slot s's activation chunks in registers ──
+    const int s = warp / kDownWarpsPerSlot, h = warp % kDownWarpsPerSlot;
+    pdl_wait();  // the activations are the gate/up kernel's output
+    uint4 xv[NCH][4];
+    float sx[NCH];
+    int sq8[NCH];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+        MATH::quantize_chunk(a.act + (size_t)s * a.I + (size_t)(lane + 32 * i) * 32, xv[i], sx[i], sq8[i]);
 
-    const int group = warp / kTileRows, wi = warp % kTileRows;
-    Ring ring{full, empty, landed, nstages};
     const uint32_t stages_addr = smem_u32(stages);
-    const uint32_t acts_addr = smem_u32(acts) + lane * MATH::kStride;
-    float* ygroup = ybuf + group * (2 * kTileRows * kMaxSlots);
-    TileWalk walk(g0, g1, a.H, a.rpp_dn);
+    const uint32_t code_base = s * slot_bytes + lane * 16;
+    const uint32_t scale_base = s * slot_bytes + kDownRows * code_row + lane * 2;
+    TileWalk walk(g0, g1, a.H, a.rpp_dn, kDownRows);
     Tile t;
-    int n = 0, par = 0;
+    int n = 0;
     while (walk.next(t)) {
-        if (n % kGroups != group) { ++n; continue; }
         const int st = n % nstages;
-        if (!ring.wait_full(n, wi == 0 && lane == 0)) {
+        if (!mbar_wait(full + st, (n / nstages) & 1)) {
             if (lane == 0) flag(a.status, kStatusTimeout);
             return;
         }
-        float* yb = ygroup + par * (kTileRows * kMaxSlots);
+        const PageEntry e = tab[s * a.P + t.page];
+        const bool present = e.ptr != 0 && t.rin + t.nrows <= e.row_count;
+        float* yb = ybuf + (n & 1) * (kDownRows * kMaxSlots);
         const uint32_t sb = stages_addr + st * stage_bytes;
-        for (int u = wi; u < slots * (kTileRows / 2); u += kTileRows) {
-            const int s = u / (kTileRows / 2), r0 = 2 * (u % (kTileRows / 2));
-            const PageEntry e = tab[s * a.P + t.page];
-            float acc[2] = {0.f, 0.f};
-            if (r0 < t.nrows) {
-                if (e.ptr != 0 && t.rin + t.nrows <= e.row_count) {
-                    const uint32_t c0 = sb + s * slot_bytes + r0 * code_row + lane * 16;
-                    const uint32_t c1 = c0 + code_row;
-                    const uint32_t s0 = sb + s * slot_bytes + kTileRows * code_row + r0 * scale_row + lane * 2;
-                    const uint32_t s1 = s0 + scale_row;
-                    const uint32_t xa = acts_addr + s * nchunks * MATH::kStride;
-                    if (NCH > 0) {
 #pragma unroll
-                        for (int i = 0; i < NCH; ++i) {
-                            const uint4 q[2] = {lds128(c0 + i * 512), lds128(c1 + i * 512)};
-                            const float s2[2] = {scale_to_f32(lds16(s0 + i * 64)), scale_to_f32(lds16(s1 + i * 64))};
-                            MATH::template chunk_s<2>(q, s2, xa + i * (32 * MATH::kStride), acc);
-                        }
-                    } else {
-                        for (int c = lane; c < nchunks; c += 32) {
-                            const int o = c - lane;
-                            const uint4 q[2] = {lds128(c0 + o * 16), lds128(c1 + o * 16)};
-                            const float s2[2] = {scale_to_f32(lds16(s0 + o * 2)), scale_to_f32(lds16(s1 + o * 2))};
-                            MATH::template chunk_s<2>(q, s2, xa + o * MATH::kStride, acc);
-                        }
-                    }
-                } else if (lane == 0) {
-                    flag(a.status, kStatusMissingPage);
+        for (int r = h; r < kDownRows; r += kDownWarpsPerSlot) {
+            float acc = 0.f;
+            if (r < t.nrows && present) {
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const uint4 q = lds128(sb + code_base + r * code_row + i * 512);
+                    const float sc = scale_to_f32(lds16(sb + scale_base + r * scale_row + i * 64));
+                    acc = MATH::chunk_r(q, sc, xv[i], sx[i], sq8[i], acc);
                 }
             }
-            const float y0 = warp_sum(acc[0]);
-            const float y1 = warp_sum(acc[1]);
-            if (lane == 0) {
-                // fp16 rounding of the down projection (its output buffer is fp16 in the reference)
-                yb[r0 * kMaxSlots + s] = __half2float(__float2half_rn(y0));
-                yb[(r0 + 1) * kMaxSlots + s] = __half2float(__float2half_rn(y1));
-            }
+            const float y = warp_sum(acc);
+            // fp16 rounding of the down projection (its output buffer is fp16 in the reference)
+            if (lane == 0) yb[r * kMaxSlots + s] = __half2float(__float2half_rn(y));
         }
-        asm volatile("bar.sync %0, %1;" ::"r"(2 + group), "r"(kTileRows * 32) : "memory");  // the group's 4 warps
-        if (lane == 0) {
-            if (wi < t.nrows) {
-                float out = 0.f;
-                for (int s = 0; s < slots; ++s) out = fmaf(wts[s], yb[wi * kMaxSlots + s], out);  // plan order
-                const int r = t.row + wi;
-                if (a.out_accumulate) a.out[r] += out;
-                else a.out[r] = out;
-            }
-            mbar_arrive(empty + st);
+        if (!present && h == 0 && lane == 0) flag(a.status, kStatusMissingPage);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + st);  // this warp has read everything it needs from the stage
+        asm volatile("bar.sync 1, %0;" ::"r"(cwarps * 32) : "memory");  // consumer warps only
+        if (warp < t.nrows && lane == 0) {
+            float out = 0.f;
+            for (int k = 0; k < slots; ++k) out = fmaf(wts[k], yb[warp * kMaxSlots + k], out);  // plan order
+            const int r = t.row + warp;
+            if (a.out_accumulate) a.out[r] += out;
+            else a.out[r] = out;
         }
-        par ^= 1;
         ++n;
     }
 }
@@ -435,12 +434,28 @@ static bool pipe_shape_ok(const MoeLayerArgs& a) {
     return a.H % 256 == 0 && a.I % 256 == 0;
 }
 
-// Number of ring stages that fit (at least kGroups so that every group can hold one), 0 = too few.
-static int pick_stages(size_t fixed, size_t stage_bytes) {
+// Number of ring stages that fit (at least one per consumer group), 0 = too few.
+static int pick_stages(size_t fixed, size_t stage_bytes, int groups = kGroups) {
     if (fixed >= kSmemBudget) return 0;
     int n = (int)((kSmemBudget - fixed) / stage_bytes);
     if (n > kMaxStages) n = kMaxStages;
-    return n >= kGroups ? n : 0;
+    return n >= groups ? n : 0;
+}
+
+// Launch with the programmatic-stream-serialization attribute (g_use_pdl) or plainly.
+template <class K>
+static int launch_pipe(K kernel, int grid, int threads, size_t smem, cudaStream_t st, const MoeLayerArgs& a, int nstages) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, a, nstages);
 }
 
 template <class K>
@@ -453,8 +468,7 @@ template <int NCH>
 static int launch_gateup_pipe_t(const MoeLayerArgs& a, cudaStream_t st, int nstages, size_t smem, int grid) {
     static int attr = set_max_smem(moe_gateup_pipe_kernel<NCH>);
     if (attr) return attr;
-    moe_gateup_pipe_kernel<NCH><<<grid, kPipeThreads, smem, st>>>(a, nstages);
-    return (int)cudaGetLastError();
+    return launch_pipe(moe_gateup_pipe_kernel<NCH>, grid, kPipeThreads, smem, st, a, nstages);
 }
 
 int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
@@ -481,34 +495,29 @@ int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
 }
 
 template <int NCH>
-static int launch_down_pipe_t(const MoeLayerArgs& a, cudaStream_t st, int nstages, size_t smem, int grid) {
+static int launch_down_pipe_t(const MoeLayerArgs& a, cudaStream_t st, int nstages, size_t smem, int grid, int threads) {
     static int attr = set_max_smem(moe_down_pipe_kernel<NCH>);
     if (attr) return attr;
-    moe_down_pipe_kernel<NCH><<<grid, kPipeThreads, smem, st>>>(a, nstages);
-    return (int)cudaGetLastError();
+    return launch_pipe(moe_down_pipe_kernel<NCH>, grid, threads, smem, st, a, nstages);
 }
 
 int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-    if (2 * slots > 32) return VIB3_ERR_UNSUPPORTED;  // one producer lane per copy of a tile
-    const size_t stage_bytes = (size_t)slots * kTileRows * ((size_t)a.I / 2 + (size_t)a.I / 16);
-    const size_t fixed = (size_t)slots * (a.I / kGroupSize) * MathQ16::kStride + (size_t)slots * a.P * sizeof(PageEntry) +
-                         2 * kMaxStages * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + kMaxSlots * sizeof(float) +
-                         (size_t)kGroups * 2 * kTileRows * kMaxSlots * sizeof(float) + 128;
-    const int nstages = pick_stages(fixed, stage_bytes);
+    const int nchunks = a.I / kGroupSize;
+    // register-resident activations: at most two chunks per lane; two warps per slot plus the producer
+    if (nchunks != 32 && nchunks != 64) return VIB3_ERR_UNSUPPORTED;
+    if ((slots * kDownWarpsPerSlot + 1) * 32 > kDownMaxThreads) return VIB3_ERR_UNSUPPORTED;
+    const size_t stage_bytes = (size_t)slots * kDownRows * ((size_t)a.I / 2 + (size_t)a.I / 16);
+    const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + 2 * kMaxStages * sizeof(uint64_t) +
+                         kMaxSlots * sizeof(float) + 2 * kDownRows * kMaxSlots * sizeof(float) + 128;
+    const int nstages = pick_stages(fixed, stage_bytes, 2);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
     const size_t smem = fixed + (size_t)nstages * stage_bytes;
-    const int grid = min(sm_count(), (a.H + kTileRows - 1) / kTileRows);
-    const int nchunks = a.I / kGroupSize;
-    const int nch = nchunks % 32 == 0 ? nchunks / 32 : 0;
-    switch (nch) {
-        case 1: return launch_down_pipe_t<1>(a, st, nstages, smem, grid);
-        case 2: return launch_down_pipe_t<2>(a, st, nstages, smem, grid);
-        case 4: return launch_down_pipe_t<4>(a, st, nstages, smem, grid);
-        case 8: return launch_down_pipe_t<8>(a, st, nstages, smem, grid);
-        default: return launch_down_pipe_t<0>(a, st, nstages, smem, grid);
-    }
+    const int grid = min(sm_count(), (a.H + kDownRows - 1) / kDownRows);
+    const int threads = (slots * kDownWarpsPerSlot + 1) * 32;
+    return nchunks == 64 ? launch_down_pipe_t<2>(a, st, nstages, smem, grid, threads)
+                         : launch_down_pipe_t<1>(a, st, nstages, smem, grid, threads);
 }
 
 }  // namespace vib3

@@ -312,6 +312,8 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
     __shared__ float red[2][4], red_abs[2][4];
     __shared__ TopKSmem sm;
     __shared__ int is_last;
+    // let a dependent kernel (launched with programmatic stream serialization) begin its prologue
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int local = threadIdx.x >> 7, chain = threadIdx.x & 127;
     const int expert = blockIdx.x * 2 + local;
     float logit = 0.f, absum = 0.f;
