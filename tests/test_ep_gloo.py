@@ -1,0 +1,88 @@
+"""Expert parallelism on CPU ranks (gloo, world size 2): placement, the per-step message, the gather
+and the cross-rank combine of vic_b200/ep.py, with the CPU oracle standing in for the GPU kernels.
+The summed result of the ranks must equal the single-rank layer output for every rank's token."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _shape():
+    from vic_b200.core_types import SCORING_SIGMOID, MoeShape
+    return MoeShape("ep-tiny", 64, 96, 8, 3, 1, SCORING_SIGMOID, 2.0, True)
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as O
+        from tests.parity import oracle_experts
+        from vic_b200 import ep
+        from vic_b200.core_types import EXPERT_SHARED, MAX_ACTIVE_EXPERTS
+        from vic_b200.synth import build_synthetic_moe
+        sh = _shape()
+        H = sh.hidden
+        full = build_synthetic_moe(sh, 1, "cpu", seed=11, slot_seed=3, per_page_content=True)
+        mine = ep.build_rank_model(sh, 1, "cpu", 11, rank, world, per_page_content=True)
+        assert sorted(set(p.pid.expert for p in mine.pages) - {EXPERT_SHARED}) == ep.local_experts(rank, sh.num_experts, world)
+        assert torch.equal(full.router_w, mine.router_w)
+        g = torch.Generator().manual_seed(100 + rank)
+        x = torch.randn(H, generator=g).to(torch.bfloat16)
+        W = full.router_w[0].numpy()
+        ids, ws, _ = O.router(x.float().numpy(), W, sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize)
+        ids_t = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.int16)
+        ws_t = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.float32)
+        ids_t[:sh.top_k] = torch.from_numpy(ids.astype(np.int16))
+        ws_t[:sh.top_k] = torch.from_numpy(ws)
+        words = H // 2 + 2 * MAX_ACTIVE_EXPERTS
+        send = torch.zeros(words, dtype=torch.int32)
+        recv = torch.zeros(world, words, dtype=torch.int32)
+        ep.pack_message(send, x, ids_t, ws_t)
+        ep.gather_messages(send, recv, world)
+        xs, gids, gws = ep.unpack_messages(recv, H)
+        assert torch.equal(xs[rank], x) and torch.equal(gids[rank], ids_t) and torch.equal(gws[rank], ws_t)
+        # every rank computes, for every token, the contribution of ITS experts (CPU oracle as the kernel)
+        partial = torch.zeros(world, H, dtype=torch.float32)
+        for t in range(world):
+            act = [(int(e), float(w)) for e, w in zip(gids[t, :sh.top_k].tolist(), gws[t, :sh.top_k].tolist())
+                   if ep.expert_owner(int(e), sh.num_experts, world) == rank]
+            experts = oracle_experts(O, mine, 0, act) if t == rank else oracle_experts(O, mine, 0, act)[:len(act)]
+            partial[t] = torch.from_numpy(O.moe_layer(xs[t].float().numpy(), experts, H, sh.intermediate, O.SCALE_FP16, "gpu"))
+        out = torch.zeros(H, dtype=torch.float32)
+        ep.combine_partials(out, partial, rank, world)
+        want = O.moe_layer(x.float().numpy(), oracle_experts(O, full, 0, list(zip(ids.tolist(), ws.tolist()))), H,
+                           sh.intermediate, O.SCALE_FP16, "gpu")
+        err = float(np.max(np.abs(out.numpy() - want)))
+        ret[rank] = (err, float(np.max(np.abs(want))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_flow_on_two_cpu_ranks(oracle):
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for r in range(world):
+        err, mag = ret[r]
+        assert mag > 0 and err <= 1e-5 * max(mag, 1.0), (r, err, mag)
+
+
+def test_placement():
+    from vic_b200.ep import expert_owner, local_experts
+    for world in (1, 2, 4, 8):
+        owners = [expert_owner(e, 384, world) for e in range(384)]
+        assert owners == sorted(owners) and set(owners) == set(range(world))
+        assert all(len(local_experts(r, 384, world)) == 384 // world for r in range(world))
+    assert local_experts(1, 8, 2) == [4, 5, 6, 7]

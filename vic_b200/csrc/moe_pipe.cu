@@ -21,8 +21,10 @@
 namespace vib3 {
 
 constexpr int kConsumerWarps = 16;
-constexpr int kGroups = 4;                       // consumer groups; group g takes tiles g, g+4, ...
-constexpr int kTileRows = kConsumerWarps / kGroups;  // rows (row pairs) per stage: one per warp of a group
+constexpr int kTileRows = 4;                     // row pairs per gate/up stage
+constexpr int kPairsPerWarp = 2;                 // a consumer warp takes two row pairs (4 rows share each activation load)
+constexpr int kGroupWarps = kTileRows / kPairsPerWarp;  // 2 warps consume a stage
+constexpr int kGroups = kConsumerWarps / kGroupWarps;   // 8 groups; group g takes tiles g, g+8, ...
 constexpr int kPipeThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 12;
 constexpr unsigned kSpinLimit = 1u << 22;
@@ -159,7 +161,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, kTileRows);
+            mbar_init(empty + s, kGroupWarps);
             landed[s] = 0;
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -219,7 +221,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     }
 
     // ── consumers ──
-    const int group = warp / kTileRows, wi = warp % kTileRows;
+    const int group = warp / kGroupWarps, wi = warp % kGroupWarps;
     Ring ring{full, empty, landed, nstages};
     const uint32_t stages_addr = smem_u32(stages);
     const uint32_t x_addr = smem_u32(xs) + lane * MATH::kStride;
@@ -233,41 +235,51 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
             if (lane == 0) flag(a.status, kStatusTimeout);
             return;
         }
-        if (wi < t.nrows) {
+        const int p0 = wi * kPairsPerWarp;  // this warp's row pairs: p0 and p0 + 1 of the tile
+        if (p0 < t.nrows) {
             const PageEntry eu = tab[(t.slot * 2 + kSegUp) * a.P + t.page];
             const PageEntry eg = tab[(t.slot * 2 + kSegGate) * a.P + t.page];
             const bool present = eu.ptr != 0 && eg.ptr != 0 && t.rin + t.nrows <= eu.row_count && t.rin + t.nrows <= eg.row_count;
-            float acc[2] = {0.f, 0.f};  // [0] gate, [1] up
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};  // gate p0, up p0, gate p0+1, up p0+1
             if (present) {
                 const uint32_t sb = stages_addr + st * stage_bytes;
-                const uint32_t g_addr = sb + wi * code_row + lane * 16;
+                const uint32_t g_addr = sb + p0 * code_row + lane * 16;
                 const uint32_t u_addr = g_addr + kTileRows * code_row;
-                const uint32_t gs_addr = sb + 2 * kTileRows * code_row + wi * scale_row + lane * 2;
+                const uint32_t gs_addr = sb + 2 * kTileRows * code_row + p0 * scale_row + lane * 2;
                 const uint32_t us_addr = gs_addr + kTileRows * scale_row;
                 if (NCH > 0) {
 #pragma unroll
                     for (int i = 0; i < NCH; ++i) {
-                        const uint4 q[2] = {lds128(g_addr + i * 512), lds128(u_addr + i * 512)};
-                        const float s2[2] = {scale_to_f32(lds16(gs_addr + i * 64)), scale_to_f32(lds16(us_addr + i * 64))};
-                        MATH::template chunk_s<2>(q, s2, x_addr + i * (32 * MATH::kStride), acc);
+                        const uint4 q[4] = {lds128(g_addr + i * 512), lds128(u_addr + i * 512),
+                                            lds128(g_addr + code_row + i * 512), lds128(u_addr + code_row + i * 512)};
+                        const float s4[4] = {scale_to_f32(lds16(gs_addr + i * 64)), scale_to_f32(lds16(us_addr + i * 64)),
+                                             scale_to_f32(lds16(gs_addr + scale_row + i * 64)), scale_to_f32(lds16(us_addr + scale_row + i * 64))};
+                        MATH::template chunk_s<4>(q, s4, x_addr + i * (32 * MATH::kStride), acc);
                     }
                 } else {
                     for (int c = lane; c < nchunks; c += 32) {
                         const int o = c - lane;
-                        const uint4 q[2] = {lds128(g_addr + o * 16), lds128(u_addr + o * 16)};
-                        const float s2[2] = {scale_to_f32(lds16(gs_addr + o * 2)), scale_to_f32(lds16(us_addr + o * 2))};
-                        MATH::template chunk_s<2>(q, s2, x_addr + o * MATH::kStride, acc);
+                        const uint4 q[4] = {lds128(g_addr + o * 16), lds128(u_addr + o * 16),
+                                            lds128(g_addr + code_row + o * 16), lds128(u_addr + code_row + o * 16)};
+                        const float s4[4] = {scale_to_f32(lds16(gs_addr + o * 2)), scale_to_f32(lds16(us_addr + o * 2)),
+                                             scale_to_f32(lds16(gs_addr + scale_row + o * 2)), scale_to_f32(lds16(us_addr + scale_row + o * 2))};
+                        MATH::template chunk_s<4>(q, s4, x_addr + o * MATH::kStride, acc);
                     }
                 }
             } else if (lane == 0) {
                 flag(a.status, kStatusMissingPage);
             }
-            const float gsum = warp_sum(acc[0]);
-            const float usum = warp_sum(acc[1]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc[k] = warp_sum(acc[k]);
             if (lane == 0) {
-                const float g16 = __half2float(__float2half_rn(gsum));
-                const float u16 = __half2float(__float2half_rn(usum));
-                a.act[(size_t)t.slot * a.I + t.row + wi] = __float2half_rn(silu_mul_f32(g16, u16));
+#pragma unroll
+                for (int k = 0; k < kPairsPerWarp; ++k) {
+                    if (p0 + k < t.nrows) {
+                        const float g16 = __half2float(__float2half_rn(acc[2 * k]));
+                        const float u16 = __half2float(__float2half_rn(acc[2 * k + 1]));
+                        a.act[(size_t)t.slot * a.I + t.row + p0 + k] = __float2half_rn(silu_mul_f32(g16, u16));
+                    }
+                }
             }
         }
         __syncwarp();
@@ -434,12 +446,12 @@ static bool pipe_shape_ok(const MoeLayerArgs& a) {
     return a.H % 256 == 0 && a.I % 256 == 0;
 }
 
-// Number of ring stages that fit (at least one per consumer group), 0 = too few.
-static int pick_stages(size_t fixed, size_t stage_bytes, int groups = kGroups) {
+// Number of ring stages that fit, 0 = fewer than min_stages.
+static int pick_stages(size_t fixed, size_t stage_bytes, int min_stages) {
     if (fixed >= kSmemBudget) return 0;
     int n = (int)((kSmemBudget - fixed) / stage_bytes);
     if (n > kMaxStages) n = kMaxStages;
-    return n >= groups ? n : 0;
+    return n >= min_stages ? n : 0;
 }
 
 // Launch with the programmatic-stream-serialization attribute (g_use_pdl) or plainly.
@@ -477,7 +489,7 @@ int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     const size_t stage_bytes = 2 * kTileRows * ((size_t)a.H / 2 + (size_t)a.H / 16);
     const size_t fixed = (size_t)(a.H / kGroupSize) * MathQ16::kStride + (size_t)slots * 2 * a.P * sizeof(PageEntry) +
                          2 * kMaxStages * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + 128;
-    const int nstages = pick_stages(fixed, stage_bytes);
+    const int nstages = pick_stages(fixed, stage_bytes, 3);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
     const size_t smem = fixed + (size_t)nstages * stage_bytes;
     const int total = slots * a.I;

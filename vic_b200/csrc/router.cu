@@ -79,30 +79,38 @@ __device__ __forceinline__ float warp_sum_down(float v) {
 }
 
 // Logit of one expert with 128 threads (lane = chain index); result valid in chain 0.
+// All of a thread's weight loads (NW = ceil(H / 128) <= U) are requested first; while they are in
+// flight the CTA copies the activation vector into shared memory as fp32, so the whole row costs one
+// round trip to memory.  The per-chain order of additions (d = chain, chain + 128, ...) is kept.
 template <int U, int XD, int WD>
 __device__ __forceinline__ void expert_logit(const RouterArgs& a, int expert, int chain, float* smem4, float* smem4_abs,
-                                             float& logit, float& absum) {
+                                             float* xs, float& logit, float& absum) {
     const size_t base = (size_t)expert * a.H;
     float acc = 0.f, aabs = 0.f;
-    int d = chain;
-    for (; d + (U - 1) * kChains < a.H; d += U * kChains) {
-        float w[U], xv[U];
+    float w[U];
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            w[i] = load_w_t<WD>(a.W, base + d + i * kChains);
-            xv[i] = load_x_t<XD>(a.x, d + i * kChains);
-        }
+    for (int i = 0; i < U; ++i) {
+        const int d = chain + i * kChains;
+        w[i] = d < a.H ? load_w_t<WD>(a.W, base + d) : 0.f;
+    }
+    if (xs) {
+        for (int i = threadIdx.x; i < a.H; i += blockDim.x) xs[i] = load_x_t<XD>(a.x, i);
+        __syncthreads();
+    }
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            acc = fmaf(xv[i], w[i], acc);
-            aabs += fabsf(xv[i] * w[i]);
+    for (int i = 0; i < U; ++i) {
+        const int d = chain + i * kChains;
+        if (d < a.H) {
+            const float xv = xs ? xs[d] : load_x_t<XD>(a.x, d);
+            acc = fmaf(xv, w[i], acc);
+            aabs += fabsf(xv * w[i]);
         }
     }
-    for (; d < a.H; d += kChains) {
-        const float w = load_w_t<WD>(a.W, base + d);
-        const float xv = load_x_t<XD>(a.x, d);
-        acc = fmaf(xv, w, acc);
-        aabs += fabsf(xv * w);
+    for (int d = chain + U * kChains; d < a.H; d += kChains) {  // rows wider than U * 128
+        const float wv = load_w_t<WD>(a.W, base + d);
+        const float xv = xs ? xs[d] : load_x_t<XD>(a.x, d);
+        acc = fmaf(xv, wv, acc);
+        aabs += fabsf(xv * wv);
     }
     acc = warp_sum_down(acc);
     aabs = warp_sum_down(aabs);
@@ -317,23 +325,26 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
     const int local = threadIdx.x >> 7, chain = threadIdx.x & 127;
     const int expert = blockIdx.x * 2 + local;
     float logit = 0.f, absum = 0.f;
+    // the activation vector as fp32 in shared memory; the selection phase has not started yet, so
+    // the product buffer of TopKSmem (8192 floats) is free to hold it
+    float* xs = a.H <= 8 * 1024 ? &sm.prod[0][0] : nullptr;
     // both halves of the CTA must reach the __syncthreads inside expert_logit
     const int e_clamped = min(expert, a.E - 1);
-    expert_logit<U, XD, WD>(a, e_clamped, chain, red[local], red_abs[local], logit, absum);
+    expert_logit<U, XD, WD>(a, e_clamped, chain, red[local], red_abs[local], xs, logit, absum);
     if (chain == 0 && expert < a.E) {
         a.scores[expert] = logit;
         if (a.exact_order) a.scores[a.E + expert] = absum;
     }
     if (a.counter == nullptr) return;
-    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int ticket = atomicAdd(a.counter, 1u);
+        // release this CTA's logits and acquire everybody else's in one operation
+        unsigned int ticket;
+        asm volatile("atom.add.acq_rel.gpu.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(a.counter) : "memory");
         is_last = ticket == gridDim.x - 1;
     }
     __syncthreads();
     if (!is_last) return;
-    __threadfence();
     router_finish(a, sm);
     if (threadIdx.x == 0) *a.counter = 0u;  // ready for the next launch
 }
@@ -347,7 +358,7 @@ static int launch_router(const RouterArgs& a, cudaStream_t st) {
     const int grid = (a.E + 1) / 2;
 #define VIB3_ROUTER_CASE(XD, WD)                                                      \
     if (a.x_dtype == XD && a.w_dtype == WD) {                                         \
-        router_kernel<14, XD, WD><<<grid, 256, 0, st>>>(a);                           \
+        router_kernel<56, XD, WD><<<grid, 256, 0, st>>>(a);                           \
         return (int)cudaGetLastError();                                               \
     }
     VIB3_ROUTER_CASE(X_F32, W_F16)

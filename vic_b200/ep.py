@@ -1,0 +1,244 @@
+"""Expert-parallel MoE decode over G GPUs of one node (one process per GPU, torch.distributed).
+
+Placement: routed expert e lives on rank e // (E / G); every rank keeps the router weights and the
+shared expert.  Each rank decodes its own token stream (batch 1 per rank: G tokens per step, weak
+scaling), which is how a data-parallel attention stage feeds an expert-parallel MoE stage:
+
+  1. every rank routes its own token (router weights are replicated, so the top-k is the one a
+     single GPU would compute: bit-exact by construction);
+  2. all_gather of (token activation, expert ids, routing weights): 14.4 KB per rank for Kimi;
+  3. for every token of the step, each rank runs the fused expert kernels over ITS OWN page table,
+     in which only its local experts are resident: the slots of experts that live elsewhere find no
+     page and contribute exactly zero (`out = fma(w, 0, out)`), the shared expert runs only on the
+     token's home rank;
+  4. reduce_scatter of the per-token partial sums [G, H] fp32: each rank receives the full layer
+     output of its own token.
+
+Peer data always lands in local HBM (NCCL receive buffers) before a kernel reads it.  The only
+difference from the single-GPU result is the fp32 association of the cross-rank sum.
+
+Step 3 costs one launch pair per (token, rank); with one local expert per pair on average the
+launches are mostly latency.  A grouped kernel that takes several (token, expert) pairs per launch
+removes that and is the next step of this path.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .core_types import KIMI, MAX_ACTIVE_EXPERTS, MoeShape
+
+
+def expert_owner(expert: int, num_experts: int, world: int) -> int:
+    """Rank that holds a routed expert: contiguous blocks of E / G experts."""
+    per = (num_experts + world - 1) // world
+    return min(expert // per, world - 1)
+
+
+def local_experts(rank: int, num_experts: int, world: int) -> List[int]:
+    return [e for e in range(num_experts) if expert_owner(e, num_experts, world) == rank]
+
+
+def pack_message(buf: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """One rank's per-step message as int32 words: the bf16 token (H/2 words), MAX_ACTIVE_EXPERTS expert
+    ids, MAX_ACTIVE_EXPERTS routing weights (fp32 bit patterns)."""
+    H2 = x.numel() // 2
+    buf[:H2].copy_(x.view(torch.int32))
+    buf[H2:H2 + MAX_ACTIVE_EXPERTS].copy_(ids.to(torch.int32))
+    buf[H2 + MAX_ACTIVE_EXPERTS:H2 + 2 * MAX_ACTIVE_EXPERTS].copy_(weights.view(torch.int32))
+
+
+def unpack_messages(recv: torch.Tensor, hidden: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """[G, words] gathered messages -> (tokens [G, H] bf16 view, ids [G, 16] int16, weights [G, 16] fp32)."""
+    H2 = hidden // 2
+    xs = recv[:, :H2].view(torch.bfloat16)
+    ids = recv[:, H2:H2 + MAX_ACTIVE_EXPERTS].to(torch.int16)
+    ws = recv[:, H2 + MAX_ACTIVE_EXPERTS:H2 + 2 * MAX_ACTIVE_EXPERTS].contiguous().view(torch.float32)
+    return xs, ids, ws
+
+
+def gather_messages(send: torch.Tensor, recv: torch.Tensor, world: int, group=None) -> None:
+    if world > 1:
+        dist.all_gather_into_tensor(recv.view(-1), send, group=group)
+    else:
+        recv[0].copy_(send)
+
+
+def combine_partials(out: torch.Tensor, partial: torch.Tensor, rank: int, world: int, group=None) -> None:
+    """Sum the per-token partial layer outputs [G, H] over ranks; rank r keeps row r."""
+    if world == 1:
+        out.copy_(partial[0])
+    elif dist.get_backend(group) == "nccl":
+        dist.reduce_scatter_tensor(out, partial.view(-1), op=dist.ReduceOp.SUM, group=group)
+    else:  # gloo (CPU tests) has no reduce_scatter
+        tmp = partial.clone()
+        dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=group)
+        out.copy_(tmp[rank])
+
+
+class ExpertParallelDecoder:
+    """One rank's share of an expert-parallel MoE layer stack."""
+
+    def __init__(self, model, rank: int, world: int, group=None):
+        from .moe import MoeDecoder
+        self.model, self.rank, self.world, self.group = model, rank, world, group
+        self.dec = MoeDecoder(model, exact_order=True)
+        sh = model.shape
+        dev = model.router_w.device
+        words = sh.hidden // 2 + 2 * MAX_ACTIVE_EXPERTS
+        self.send = torch.zeros(words, dtype=torch.int32, device=dev)
+        self.recv = torch.zeros(world, words, dtype=torch.int32, device=dev)
+        self.partial = torch.zeros(world, sh.hidden, dtype=torch.float32, device=dev)
+        self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
+        self.ids_t = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
+        self.w_t = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
+        self.ep_status = torch.zeros(1, dtype=torch.int32, device=dev)  # the missing-page bit is expected here
+        self.launches_per_step = 1 + 2 * world
+
+    def step(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+        """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
+        from . import kernels
+        sh, dec = self.model.shape, self.dec
+        H = sh.hidden
+        dec.route(layer, x)
+        pack_message(self.send, x, dec.ids, dec.weights)
+        gather_messages(self.send, self.recv, self.world, self.group)
+        xs, ids, ws = unpack_messages(self.recv, H)
+        self.ids_t.copy_(ids)
+        self.w_t.copy_(ws)
+        for t in range(self.world):
+            shared = dec.shared_tables[layer] if t == self.rank else 0
+            kernels.moe_layer_int4_paged(xs[t], dec.tables[layer], sh.num_experts, shared, self.ids_t[t], self.w_t[t],
+                                         sh.top_k, 1.0, dec.act, self.partial[t], False, H, sh.intermediate,
+                                         sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page,
+                                         self.ep_status)
+        combine_partials(self.out, self.partial, self.rank, self.world, self.group)
+        return self.out
+
+
+def build_rank_model(shape: MoeShape, n_layers: int, device, seed: int, rank: int, world: int, per_page_content=False):
+    from .synth import build_synthetic_moe
+    return build_synthetic_moe(shape, n_layers, device, seed=seed, slot_seed=99 + rank,
+                               experts=local_experts(rank, shape.num_experts, world), per_page_content=per_page_content)
+
+
+def bench_main(args) -> None:
+    """bench.py --gpus N (N > 1), launched by torch.distributed.run: one rank per GPU."""
+    import bench as B
+    from .synth import synth_activation
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    sh = KIMI
+    layers = B.PHYS_LAYERS
+    model = build_rank_model(sh, layers, dev, B.SEED, rank, world)
+    ep = ExpertParallelDecoder(model, rank, world)
+    gen = torch.Generator(device=dev).manual_seed(B.SEED + 1000 * rank)
+    xs = synth_activation(sh, gen, dev, torch.bfloat16, B.N_TOKENS)
+    K, W = args.steps, args.warmup
+
+    def step(i):
+        ep.step(i % layers, xs[i % B.N_TOKENS])
+
+    for i in range(W):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    # The step (kernels + NCCL collectives) is captured into a CUDA graph so that the 2G+1 launches
+    # per step are not bound by the host; if capture is refused the loop runs eagerly.
+    chunk = min(K, 32)
+    graph, mode = None, "eager"
+    if os.environ.get("VIB3_EP_NO_GRAPH") != "1":
+        try:
+            stream = torch.cuda.Stream(device=dev)
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for i in range(chunk):
+                        step(i)
+            torch.cuda.synchronize()
+            g.replay()
+            torch.cuda.synchronize()
+            graph, mode = g, "cuda-graph"
+        except Exception as exc:  # noqa: BLE001
+            graph, mode = None, f"eager (graph capture refused: {type(exc).__name__})"
+            torch.cuda.synchronize()
+    ok = torch.tensor([1 if graph is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 0:
+        graph = None
+    dist.barrier()
+    sampler = B.ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    if graph is not None:
+        for _ in range(K // chunk):
+            graph.replay()
+        for i in range(K % chunk):
+            step(i)
+    else:
+        for i in range(K):
+            step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_local = e0.elapsed_time(e1)
+    dist.barrier()
+    clocks = sampler.stop() if sampler else None
+
+    # e2e: token from pinned host memory in, layer output back to the host, every step
+    x_host = [xs[i].cpu().pin_memory() for i in range(B.N_TOKENS)]
+    out_host = torch.zeros(sh.hidden, dtype=torch.float32).pin_memory()
+    x_dev = torch.zeros(sh.hidden, dtype=torch.bfloat16, device=dev)
+
+    def e2e_step(i):
+        x_dev.copy_(x_host[i % B.N_TOKENS], non_blocking=True)
+        out_host.copy_(ep.step(i % layers, x_dev), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    for i in range(min(W, 4)):
+        e2e_step(i)
+    dist.barrier()
+    e0.record()
+    for i in range(K):
+        e2e_step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_local = e0.elapsed_time(e1)
+
+    t = torch.tensor([ms_local, e2e_local], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        b_gu, b_dn, b_r = B.algorithmic_bytes(sh)
+        line = {
+            "metric": B.METRIC, "value": world * K / (ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int4 weights, 16-bit fixed-point activations, int32/fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "C1 kimi-k2.5-shape MoE layer, batch-1 decode per rank, experts sharded expert-parallel",
+                       "hidden": sh.hidden, "experts": sh.num_experts, "experts_per_gpu": sh.num_experts // world,
+                       "top_k": sh.top_k, "shared_experts": 1, "intermediate": sh.intermediate, "tokens_per_step": world,
+                       "physical_layers": layers, "launch_mode": mode, "l2_policy": "inputs larger than L2: layers and tokens rotate",
+                       "parallelism": f"ep{world}: all_gather(token, routing) + reduce_scatter(partial sums), NCCL"},
+            "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": world * sh.hidden * 2,
+                    "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms / K},
+            "gpu_launches": K * ep.launches_per_step * world,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": world * (b_gu + b_dn + b_r) / (ms * 1e-3 / K) / 1e9,
+                         "peak": world * B.measured_peaks()[0], "unit": "GB/s",
+                         "frac": (b_gu + b_dn + b_r) / (ms * 1e-3 / K) / 1e9 / B.measured_peaks()[0],
+                         "traffic": None, "note": "whole step over all ranks (per-kernel roofline is reported at N=1)"},
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()

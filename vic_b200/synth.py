@@ -72,9 +72,14 @@ def pages_needed(shape: MoeShape, n_layers: int, n_experts: Optional[int] = None
 
 def build_synthetic_moe(shape: MoeShape, n_layers: int, device, seed: int, slot_seed: int = 0,
                         experts: Optional[Iterable[int]] = None, router_dtype=torch.float32,
-                        spare_pages: int = 0) -> SyntheticMoe:
+                        spare_pages: int = 0, per_page_content: bool = False) -> SyntheticMoe:
     """Place every page of ``n_layers`` layers (all experts, or only ``experts``) into a fresh pool in a
-    seeded random slot order, fill codes and scales from a seeded generator, freeze the pool."""
+    seeded random slot order, fill codes and scales from a seeded generator, freeze the pool.
+
+    ``per_page_content``: derive every page's bytes from (seed, page id) alone, so that a pool holding
+    only a subset of the experts (one expert-parallel rank's shard) holds exactly the same bytes for
+    them as the pool holding all experts, and the router weights are the same too.  Slower to build;
+    meant for parity tests."""
     device = torch.device(device)
     elist = list(range(shape.num_experts)) if experts is None else sorted(set(int(e) for e in experts))
     n_pages = n_layers * (len(elist) + shape.shared_experts) * shape.pages_per_expert + spare_pages
@@ -91,6 +96,20 @@ def build_synthetic_moe(shape: MoeShape, n_layers: int, device, seed: int, slot_
                     nbytes = rc * geom.bytes_per_row
                     slot = pool.load_page(PageId(layer, e, seg, p), r0, rc, None, nbytes)
                     placed.append(PlacedPage(PageId(layer, e, seg, p), slot, r0, rc, geom.cols, nbytes))
+    if per_page_content:
+        pg_gen = torch.Generator(device=device)
+        for pg in placed:
+            pg_gen.manual_seed((seed * 0x9E3779B1 + pg.pid.key() * 0x85EBCA6B) % (2 ** 63))
+            view = pool.slot_view(pg.slot, pg.nbytes)
+            ncode = pg.row_count * ((pg.cols + 1) // 2)
+            view[:ncode].random_(0, 256, generator=pg_gen)
+            sc = synth_scales((pg.nbytes - ncode) // 2, pg_gen, device)
+            view[ncode:].copy_(sc.view(torch.uint8))
+        pool.freeze()
+        gen.manual_seed(seed)
+        router_w = (torch.randn(n_layers, shape.num_experts, shape.hidden, generator=gen, device=device,
+                                dtype=torch.float32) * 0.02).to(router_dtype)
+        return SyntheticMoe(shape, n_layers, pool, router_w, placed, None if experts is None else elist)
     fill_random_codes(pool, gen)
     # scales: one vectorised write per page geometry
     pool2d = pool.storage.view(n_pages, PAGE_SIZE)
