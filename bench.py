@@ -184,12 +184,23 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
-def profile_small(n):
+def profile_small(n, router_only=False):
     import torch
     from vic_b200.core_types import KIMI, MoeShape
     from vic_b200.moe import MoeDecoder
     from vic_b200.synth import build_synthetic_moe, synth_activation
     dev = torch.device("cuda:0")
+    if router_only:
+        # full-width router (384 experts, exact-order checks on) over a pool that holds 16 experts' pages
+        model = build_synthetic_moe(KIMI, 2, dev, seed=SEED, slot_seed=99, experts=range(16))
+        dec = MoeDecoder(model, exact_order=True)
+        g = torch.Generator(device=dev).manual_seed(1)
+        xs = synth_activation(KIMI, g, dev, torch.bfloat16, 8)
+        for i in range(n):
+            dec.route(i % 2, xs[i % 8])
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_router": n}))
+        return
     sh = MoeShape("kimi16", KIMI.hidden, KIMI.intermediate, 16, KIMI.top_k, 1, KIMI.scoring, KIMI.scaling_factor, True)
     model = build_synthetic_moe(sh, 2, dev, seed=SEED, slot_seed=99)
     dec = MoeDecoder(model, exact_order=False)
@@ -216,9 +227,14 @@ def main():
                     help="run N untimed layer-steps of a 16-expert Kimi-shape layer (same per-launch work as the full "
                          "workload: 8 routed + 1 shared expert, 223 MB of weights per step, 0.8 GB resident) and exit; "
                          "this is the command the ncu captures under profiles/ run")
+    ap.add_argument("--profile-router", type=int, default=0, metavar="N",
+                    help="run N untimed launches of the full-width (384-expert) router and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_small:
         profile_small(args.profile_small)
+        return
+    if args.profile_router:
+        profile_small(args.profile_router, router_only=True)
         return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -290,7 +306,6 @@ def main():
         # ── roofline: the dominant kernel (gate/up + SiLU) alone ──
         for i in range(4):
             dec.route(i % PHYS_LAYERS, xs[i])
-        g2 = torch.cuda.CUDAGraph()
         n_k = 32
         # routing differs per launch: pre-route into separate id/weight buffers
         ids_all = torch.zeros(n_k, 16, dtype=torch.int16, device=dev)
@@ -301,26 +316,56 @@ def main():
             w_all[i].copy_(dec.weights)
         stream.synchronize()
 
-        def gate_up(i):
+        def phase_launch(i, phase):
             kernels.moe_layer_int4_paged(xs[i], dec.tables[i % PHYS_LAYERS], sh.num_experts, dec.shared_tables[i % PHYS_LAYERS],
                                          ids_all[i], w_all[i], sh.top_k, 1.0, dec.act, dec.out, False, sh.hidden,
                                          sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page,
-                                         sh.down.rows_per_page, dec.status, phase=1)
-        for i in range(3):
-            gate_up(i)
-        stream.synchronize()
-        with torch.cuda.graph(g2, stream=stream):
-            for i in range(n_k):
-                gate_up(i)
-        g2.replay()
-        stream.synchronize()
+                                         sh.down.rows_per_page, dec.status, phase=phase)
+
+        def time_kernel(fn):
+            """Average duration of one launch: CUDA graph of n_k launches (rotating layers and tokens),
+            CUDA events on the launching stream around `reps` replays."""
+            for i in range(3):
+                fn(i)
+            stream.synchronize()
+            gk = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gk, stream=stream):
+                for i in range(n_k):
+                    fn(i)
+            gk.replay()
+            stream.synchronize()
+            e0.record(stream)
+            for _ in range(reps):
+                gk.replay()
+            e1.record(stream)
+            stream.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / (reps * n_k)
+
         reps = 8
-        e0.record(stream)
-        for _ in range(reps):
-            g2.replay()
-        e1.record(stream)
-        stream.synchronize()
-        k_us = e0.elapsed_time(e1) * 1e3 / (reps * n_k)
+        k_us = time_kernel(lambda i: phase_launch(i, 1))
+        down_us = time_kernel(lambda i: phase_launch(i, 2))
+        router_us = time_kernel(lambda i: dec.route(i % PHYS_LAYERS, xs[i]))
+        variants = {}
+        if os.environ.get("VIB3_BENCH_VARIANTS") == "1":   # A/B of library options in one process
+            from vic_b200.lib import lib as _lib
+            for v in (3, 0):
+                _lib().vib3_config_set(2, v)
+                variants[f"router_variant_{v}"] = time_kernel(lambda i: dec.route(i % PHYS_LAYERS, xs[i]))
+            w16 = [model.router_w[l].to(torch.float16) for l in range(PHYS_LAYERS)]
+            x32 = xs.float()
+            sc = torch.zeros(sh.num_experts, dtype=torch.float32, device=dev)
+            variants["router_gemv_only_f16w"] = time_kernel(lambda i: kernels.router_gemv_f32(x32[i], w16[i % PHYS_LAYERS], sc, sh.hidden, sh.num_experts))
+            dec.exact_order = False
+            variants["router_no_exact"] = time_kernel(lambda i: dec.route(i % PHYS_LAYERS, xs[i]))
+            dec.exact_order = True
+            _lib().vib3_config_set(1, 0)
+            variants["gate_up_no_pdl"] = time_kernel(lambda i: phase_launch(i, 1))
+            variants["down_no_pdl"] = time_kernel(lambda i: phase_launch(i, 2))
+            _lib().vib3_config_set(1, 1)
+            _lib().vib3_config_set(0, 0)
+            variants["gate_up_direct"] = time_kernel(lambda i: phase_launch(i, 1))
+            variants["down_direct"] = time_kernel(lambda i: phase_launch(i, 2))
+            _lib().vib3_config_set(0, 1)
 
         # ── e2e: host buffers every step, through the same public calls ──
         x_host = [xs[i].cpu().pin_memory() for i in range(N_TOKENS)]
@@ -362,9 +407,12 @@ def main():
         "roofline": {"bound": "hbm", "kernel": "moe_gateup_pipe_kernel (gate/up + SiLU, 9 experts)", "achieved": achieved,
                      "peak": peak, "peak_source": f"of {peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst)", "unit": "GB/s",
                      "frac": achieved / peak, "bytes_per_launch": b_gu, "us_per_launch": k_us,
-                     "traffic": 152.4e6, "traffic_source": "ncu dram__bytes_read+write, same launch shape (profiles/)"},
+                     "traffic": 152.43e6, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same shape (profiles/moe_gateup_down_kimi_batch1.md)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sh.hidden * 2, "d2h_bytes_per_step": sh.hidden * 4,
                 "ms_per_step": e2e_ms / K},
+        "kernel_us": {"router": router_us, "gate_up": k_us, "down": down_us,
+                      "note": "each kernel alone, back to back in a CUDA graph over rotating layers/tokens"},
+        "variants_us": variants,
         "gpu_launches": 3 * K,
         "clocks": clocks,
         "router_recomputations": int(dec.workspace[1].item()),

@@ -81,13 +81,16 @@ int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_
 
 /* Single-launch router (no counterpart signature in the reference; semantics of
  * run_router_with_scoring_and_bias, src/compute/kernels.rs:2307-2440).  x_dtype VIB3_X_*,
- * w_dtype VIB3_W_*.  scores_buf: num_experts floats, 2*num_experts when exact_order != 0.
+ * w_dtype VIB3_W_*.  bias: added to the score for selection only (the reference's correction bias);
+ * logit_offset: added to the logit before scoring.  scores_buf: num_experts floats, 2*num_experts
+ * when exact_order != 0.
  * exact_order != 0 makes the selected indices equal to those of the reference's CPU router
  * (sequential fp32 summation) even for near-tied experts.  workspace: two uint32, zero before
  * the first call; [0] is left zero by every call, [1] counts near-tie recomputations; calls
  * sharing a workspace must not overlap. */
 int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
-                               const float* bias_or_null, unsigned short* out_ids, float* out_weights,
+                               const float* bias_or_null, const float* logit_offset_or_null,
+                               unsigned short* out_ids, float* out_weights,
                                int hidden_dim, int num_experts, int top_k, int scoring_mode, float scaling_factor,
                                int normalize, int exact_order, unsigned int* workspace, void* stream);
 
@@ -151,8 +154,9 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
 
 /* Library options.  key 0: use the bulk-copy staged MoE kernels where the shape allows (default 1);
  * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
- * launch so that their prologue overlaps the previous kernel's tail (default 1).  Returns the previous
- * value. */
+ * launch so that their prologue overlaps the previous kernel's tail (default 1).  key 2: router
+ * load-batching variant (0: 14 loads per batch, 1 default: whole row in one batch, 2: two batches).
+ * Returns the previous value. */
 int vib3_config_set(int key, int value);
 
 /* ── Host side: VRAM page pool and query planner (C view of the C++ classes) ────────────── */

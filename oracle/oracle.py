@@ -180,9 +180,13 @@ def router_select(logits, top_k: int, mode: int, scaling_factor: float = 1.0, no
 
 
 def router(x_f32, W, top_k: int, mode: int, scaling_factor: float = 1.0, normalize: bool = True,
-           bias=None, order: int = ORDER_SEQUENTIAL) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
-    """``run_router_with_scoring_and_bias``: returns (ids u16[k], weights f32[k], logits f32[E])."""
+           bias=None, order: int = ORDER_SEQUENTIAL, logit_offset=None) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """``run_router_with_scoring_and_bias``: returns (ids u16[k], weights f32[k], logits f32[E]).
+    ``logit_offset`` (not in the reference: the synthetic expert-load skew of the multi-token
+    benchmark config) is added to the logits with one fp32 addition before scoring."""
     logits = router_logits(x_f32, W, order)
+    if logit_offset is not None:
+        logits = (logits + np.asarray(logit_offset, np.float32)).astype(np.float32)
     ids, w = router_select(logits, top_k, mode, scaling_factor, normalize, bias)
     return ids, w, logits
 

@@ -162,6 +162,6 @@ def test_router_refusals(cuda_dev):
     assert L.vib3_launch_router_topk(p, p, p, None, p, p, 64, 8, 17, 0, 1.0, None) == -2    # > MAX_ACTIVE_EXPERTS
     assert L.vib3_launch_router_topk(None, p, p, None, p, p, 64, 8, 2, 0, 1.0, None) == -3
     assert L.vib3_launch_router_topk(p, p, p, None, p, p, 64, 8, 2, 2, 1.0, None) == -1     # unknown scoring mode
-    assert L.vib3_launch_router_topk_ex(p, 0, p, 1, p, None, p, p, 64, 8, 2, 0, 1.0, 1, 1, None, None) == -3  # no workspace
-    assert L.vib3_launch_router_topk_ex(p, 5, p, 1, p, None, p, p, 64, 8, 2, 0, 1.0, 1, 1, p, None) == -1
+    assert L.vib3_launch_router_topk_ex(p, 0, p, 1, p, None, None, p, p, 64, 8, 2, 0, 1.0, 1, 1, None, None) == -3  # no workspace
+    assert L.vib3_launch_router_topk_ex(p, 5, p, 1, p, None, None, p, p, 64, 8, 2, 0, 1.0, 1, 1, p, None) == -1
     torch.cuda.synchronize()

@@ -312,7 +312,10 @@ static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void
         rows_per_page_down, group_size, status, stream
 
 // key 0: staged (bulk-copy) kernels on/off; key 1: programmatic dependent launch of the staged
-// kernels on/off.  Returns the previous value, or VIB3_ERR_UNSUPPORTED.
+// kernels on/off; key 2: router load-batching variant (0, 1 default, 2).  Returns the previous
+// value, or VIB3_ERR_UNSUPPORTED.
+extern "C" int vib3_router_config_set(int value);  // router.cu
+
 extern "C" int vib3_config_set(int key, int value) {
     if (key == 0) {
         const int old = g_use_pipeline;
@@ -324,6 +327,7 @@ extern "C" int vib3_config_set(int key, int value) {
         g_use_pdl = value ? 1 : 0;
         return old;
     }
+    if (key == 2) return vib3_router_config_set(value);
     return VIB3_ERR_UNSUPPORTED;
 }
 

@@ -41,7 +41,8 @@ struct RouterArgs {
     const void* W;
     int w_dtype;
     float* scores;        // [E] logits; [2E] when exact_order (second half: sum |x*w|)
-    const float* bias;    // [E] or null
+    const float* bias;    // [E] or null: added to the score for selection only
+    const float* logit_offset;  // [E] or null: added to the logit before scoring (a pre-activation bias)
     unsigned short* out_ids;
     float* out_weights;
     unsigned int* counter;  // two words of workspace (single-launch path only)
@@ -87,30 +88,28 @@ __device__ __forceinline__ void expert_logit(const RouterArgs& a, int expert, in
                                              float* xs, float& logit, float& absum) {
     const size_t base = (size_t)expert * a.H;
     float acc = 0.f, aabs = 0.f;
-    float w[U];
+    bool staged = xs == nullptr;
+    for (int d0 = chain; d0 < a.H; d0 += U * kChains) {
+        float w[U];
 #pragma unroll
-    for (int i = 0; i < U; ++i) {
-        const int d = chain + i * kChains;
-        w[i] = d < a.H ? load_w_t<WD>(a.W, base + d) : 0.f;
-    }
-    if (xs) {
-        for (int i = threadIdx.x; i < a.H; i += blockDim.x) xs[i] = load_x_t<XD>(a.x, i);
-        __syncthreads();
-    }
-#pragma unroll
-    for (int i = 0; i < U; ++i) {
-        const int d = chain + i * kChains;
-        if (d < a.H) {
-            const float xv = xs ? xs[d] : load_x_t<XD>(a.x, d);
-            acc = fmaf(xv, w[i], acc);
-            aabs += fabsf(xv * w[i]);
+        for (int i = 0; i < U; ++i) {
+            const int d = d0 + i * kChains;
+            w[i] = d < a.H ? load_w_t<WD>(a.W, base + d) : 0.f;
         }
-    }
-    for (int d = chain + U * kChains; d < a.H; d += kChains) {  // rows wider than U * 128
-        const float wv = load_w_t<WD>(a.W, base + d);
-        const float xv = xs ? xs[d] : load_x_t<XD>(a.x, d);
-        acc = fmaf(xv, wv, acc);
-        aabs += fabsf(xv * wv);
+        if (!staged) {  // first batch of weight loads is in flight: copy the activations meanwhile
+            for (int i = threadIdx.x; i < a.H; i += blockDim.x) xs[i] = load_x_t<XD>(a.x, i);
+            __syncthreads();
+            staged = true;
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const int d = d0 + i * kChains;
+            if (d < a.H) {
+                const float xv = xs ? xs[d] : load_x_t<XD>(a.x, d);
+                acc = fmaf(xv, w[i], acc);
+                aabs += fabsf(xv * w[i]);
+            }
+        }
     }
     acc = warp_sum_down(acc);
     aabs = warp_sum_down(aabs);
@@ -202,7 +201,11 @@ __device__ void block_score(const RouterArgs& a, TopKSmem& sm) {
 __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
     const int tid = threadIdx.x;
     const int k = min(a.top_k, a.E);
-    for (int e = tid; e < a.E; e += blockDim.x) sm.logit[e] = __ldcg(a.scores + e);
+    // one round trip: logits and (exact-order mode) the sums of |x w| together
+    for (int e = tid; e < a.E; e += blockDim.x) {
+        sm.logit[e] = __ldcg(a.scores + e);
+        if (a.exact_order) sm.wid[e] = __ldcg(a.scores + a.E + e);
+    }
     __syncthreads();
     block_score(a, sm);
     const int nsel = min(k + 1, a.E);
@@ -216,7 +219,7 @@ __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
         // most eps times the local slope of the scoring function (1 for raw logits, s (1 - s) for
         // the sigmoid, taken 1.25x for the curvature) plus a few ulps of rounding.
         for (int e = tid; e < a.E; e += blockDim.x) {
-            const float ab = __ldcg(a.scores + a.E + e);
+            const float ab = sm.wid[e];  // same thread wrote it above
             const float eps = 16.f * 5.9604645e-8f * (sqrtf((float)a.H) * fabsf(sm.logit[e]) + ab);
             const float slope = a.mode == 0 ? 1.f : 1.25f * sm.sig[e] * (1.f - sm.sig[e]);
             sm.wid[e] = eps * slope + 2.f * 1.1920929e-7f * fmaxf(fabsf(sm.sel[e]), 1e-30f);
@@ -275,6 +278,7 @@ __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
                     __syncwarp();
                 }
                 if (lane == 0) {
+                    if (a.logit_offset) acc = __fadd_rn(acc, a.logit_offset[e]);
                     sm.logit[e] = acc;
                     a.scores[e] = acc;
                 }
@@ -315,7 +319,7 @@ __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
 
 // GEMV: 2 experts per CTA, 128 threads each.  When `a.counter` is set, the CTA that finishes
 // last also does the scoring and selection (single launch).
-template <int U, int XD, int WD>
+template <int U, int XD, int WD, bool XSMEM>
 __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
     __shared__ float red[2][4], red_abs[2][4];
     __shared__ TopKSmem sm;
@@ -327,11 +331,12 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
     float logit = 0.f, absum = 0.f;
     // the activation vector as fp32 in shared memory; the selection phase has not started yet, so
     // the product buffer of TopKSmem (8192 floats) is free to hold it
-    float* xs = a.H <= 8 * 1024 ? &sm.prod[0][0] : nullptr;
+    float* xs = (XSMEM && a.H <= 8 * 1024) ? &sm.prod[0][0] : nullptr;
     // both halves of the CTA must reach the __syncthreads inside expert_logit
     const int e_clamped = min(expert, a.E - 1);
     expert_logit<U, XD, WD>(a, e_clamped, chain, red[local], red_abs[local], xs, logit, absum);
     if (chain == 0 && expert < a.E) {
+        if (a.logit_offset) logit = __fadd_rn(logit, a.logit_offset[expert]);
         a.scores[expert] = logit;
         if (a.exact_order) a.scores[a.E + expert] = absum;
     }
@@ -354,11 +359,19 @@ __global__ void __launch_bounds__(256) router_topk_kernel(RouterArgs a) {
     router_finish(a, sm);
 }
 
+// 0 (default): 14 loads per batch, activations from global memory; 1: whole row in one batch,
+// activations via shared memory; 2: two batches.  Set through vib3_config_set(2, v).
+int g_router_variant = 0;
+
 static int launch_router(const RouterArgs& a, cudaStream_t st) {
     const int grid = (a.E + 1) / 2;
 #define VIB3_ROUTER_CASE(XD, WD)                                                      \
     if (a.x_dtype == XD && a.w_dtype == WD) {                                         \
-        router_kernel<56, XD, WD><<<grid, 256, 0, st>>>(a);                           \
+        if (g_router_variant == 0) router_kernel<14, XD, WD, false><<<grid, 256, 0, st>>>(a);      \
+        else if (g_router_variant == 2) router_kernel<28, XD, WD, true><<<grid, 256, 0, st>>>(a);  \
+        else if (g_router_variant == 3) router_kernel<56, XD, WD, false><<<grid, 256, 0, st>>>(a); \
+        else if (g_router_variant == 4) router_kernel<28, XD, WD, false><<<grid, 256, 0, st>>>(a); \
+        else router_kernel<56, XD, WD, true><<<grid, 256, 0, st>>>(a);                \
         return (int)cudaGetLastError();                                               \
     }
     VIB3_ROUTER_CASE(X_F32, W_F16)
@@ -388,6 +401,12 @@ static int check_topk(const RouterArgs& a) {
 }  // namespace vib3
 
 using namespace vib3;
+
+extern "C" int vib3_router_config_set(int value) {
+    const int old = g_router_variant;
+    g_router_variant = value;
+    return old;
+}
 
 extern "C" int vib3_launch_router_gemv(const void* x_f16, const void* W_f16, float* scores, int hidden_dim,
                                        int num_experts, void* stream) {
@@ -426,12 +445,14 @@ extern "C" int vib3_launch_router_topk(const void* x_f32, const void* W_f16, flo
 // workspace is two 32-bit words, zero before the first call: [0] is an arrival counter that every
 // call leaves at zero, [1] counts the near-tie recomputations done so far (diagnostics).
 extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
-                                          const float* bias, unsigned short* out_ids, float* out_weights,
+                                          const float* bias, const float* logit_offset, unsigned short* out_ids,
+                                          float* out_weights,
                                           int hidden_dim, int num_experts, int top_k, int scoring_mode,
                                           float scaling_factor, int normalize, int exact_order,
                                           unsigned int* workspace, void* stream) {
     RouterArgs a{};
     a.x = x; a.x_dtype = x_dtype; a.W = W; a.w_dtype = w_dtype; a.scores = scores_buf; a.bias = bias;
+    a.logit_offset = logit_offset;
     a.out_ids = out_ids; a.out_weights = out_weights; a.counter = workspace; a.H = hidden_dim; a.E = num_experts;
     a.top_k = top_k; a.mode = scoring_mode; a.scaling = scaling_factor; a.normalize = normalize; a.exact_order = exact_order;
     if (int e = check_router(a)) return e;

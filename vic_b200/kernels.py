@@ -122,12 +122,13 @@ def run_router_gpu_topk(hidden_state_f32, router_weights_f16, scores_buf, bias, 
 
 def router_topk_ex(x: torch.Tensor, W: torch.Tensor, scores_buf, bias, out_ids, out_weights, top_k: int,
                    scoring_mode: int, scaling_factor: float, normalize: bool, exact_order: bool, workspace,
-                   stream: Optional[int] = None) -> None:
+                   stream: Optional[int] = None, logit_offset=None) -> None:
     """Single-launch router for fp16/bf16/fp32 activations and fp16/fp32 weights."""
     E, H = W.shape
     w_dtype = {torch.float16: W_F16, torch.float32: W_F32}[W.dtype]
     check("router_topk_ex", lib().vib3_launch_router_topk_ex(
-        _ptr(x), x_dtype_code(x), _ptr(W), w_dtype, _ptr(scores_buf), _ptr(bias), _ptr(out_ids), _ptr(out_weights), H, E,
+        _ptr(x), x_dtype_code(x), _ptr(W), w_dtype, _ptr(scores_buf), _ptr(bias), _ptr(logit_offset), _ptr(out_ids),
+        _ptr(out_weights), H, E,
         top_k, scoring_mode, scaling_factor, int(normalize), int(exact_order), _ptr(workspace), _stream(stream)))
 
 

@@ -49,7 +49,7 @@ SIGNATURES = {
     "vib3_launch_router_gemv": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "vib3_launch_router_gemv_f32": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "vib3_launch_router_topk": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
-    "vib3_launch_router_topk_ex": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp, _vp]),
+    "vib3_launch_router_topk_ex": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp, _vp]),
     "vib3_launch_moe_layer_int4_paged": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _i, _i, _i,
                                               _i, _i, _vp, _vp]),
     "vib3_launch_moe_gate_up_int4_paged": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _i, _i, _i,

@@ -37,10 +37,12 @@ class MoeDecoder:
         self.shared_tables = [model.shared_table(l) for l in range(model.n_layers)]
         self.launches_per_layer = 3
 
-    def route(self, layer: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    def route(self, layer: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              logit_offset: Optional[torch.Tensor] = None) -> None:
         sh = self.model.shape
         kernels.router_topk_ex(x, self.model.router_w[layer], self.scores, bias, self.ids, self.weights, sh.top_k,
-                               sh.scoring, sh.scaling_factor, sh.normalize, self.exact_order, self.workspace)
+                               sh.scoring, sh.scaling_factor, sh.normalize, self.exact_order, self.workspace,
+                               logit_offset=logit_offset)
 
     def experts(self, layer: int, x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
                 phase: int = 3) -> torch.Tensor:
@@ -53,10 +55,28 @@ class MoeDecoder:
         return out
 
     def forward_layer(self, layer: int, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                      accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      accumulate: bool = False, bias: Optional[torch.Tensor] = None,
+                      logit_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: [H] activations (bf16 / fp16 / fp32).  Returns the fp32 [H] sublayer output."""
-        self.route(layer, x, bias)
+        self.route(layer, x, bias, logit_offset)
         return self.experts(layer, x, out, accumulate)
+
+    def forward_tokens(self, layer: int, xs: torch.Tensor, outs: Optional[torch.Tensor] = None,
+                       logit_offset: Optional[torch.Tensor] = None, routing_out=None) -> torch.Tensor:
+        """Multi-token decode, xs [T, H] -> [T, H] fp32: every token takes the batch-1 path in turn
+        (the reference runs prefill the same way, src/runtime/engine.rs:1837-1838).  Experts that no
+        token selects are never touched.  ``routing_out``: optional (ids int16 [T,16], weights fp32
+        [T,16]) device tensors that receive each token's routing."""
+        T = xs.shape[0]
+        if outs is None:
+            outs = torch.zeros(T, self.model.shape.hidden, dtype=torch.float32, device=xs.device)
+        for t in range(T):
+            self.route(layer, xs[t], None, logit_offset)
+            if routing_out is not None:
+                routing_out[0][t].copy_(self.ids)
+                routing_out[1][t].copy_(self.weights)
+            self.experts(layer, xs[t], outs[t])
+        return outs
 
     def routing(self) -> Tuple[np.ndarray, np.ndarray]:
         k = self.model.shape.top_k
