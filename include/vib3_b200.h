@@ -136,6 +136,23 @@ int vib3_launch_moe_down_int4_paged(const void* x, int x_dtype, const void* page
                                     int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down,
                                     int group_size, int* status, void* stream);
 
+/* vib3_launch_moe_layer_int4_paged with a device-side slot count: only the first
+ * min(top_k, *num_active_dev) entries of expert_ids / expert_weights are used (0 is allowed: with no
+ * shared expert the output is zero).  For expert parallelism, where the number of a token's experts
+ * that live on this GPU is known only on the device. */
+int vib3_launch_moe_layer_int4_paged_var(const void* x, int x_dtype, const void* page_table, int num_experts,
+                                         const void* shared_pages, const unsigned short* expert_ids,
+                                         const float* expert_weights, int top_k, float shared_weight,
+                                         void* act_scratch, float* out, int out_accumulate, int hidden_dim,
+                                         int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
+                                         int rows_per_page_down, int group_size, int* status, void* stream,
+                                         const int* num_active_dev);
+/* Keep, in order, the (expert, weight) pairs with expert_lo <= expert < expert_hi; *count_out = how
+ * many.  ids_out / weights_out have top_k entries (unused ones are filled with expert_lo / 0). */
+int vib3_launch_select_local_experts(const unsigned short* ids, const float* weights, int top_k, int expert_lo,
+                                     int expert_hi, unsigned short* ids_out, float* weights_out, int* count_out,
+                                     void* stream);
+
 /* Same work as vib3_launch_moe_layer_int4_paged, for callers that cannot supply act_scratch because
  * they may not allocate device memory (all VRAM already given to a page pool, allocation forbidden
  * after warm-up, no allocator in the binding).  This entry point has no counterpart in the

@@ -17,6 +17,7 @@ struct MoeLayerArgs {
     const unsigned short* expert_ids;  // [top_k], device
     const float* expert_weights;       // [top_k], device
     int top_k;
+    const int* num_active_dev;     // optional device int: use only the first min(top_k, *num_active_dev) routed slots
     int num_experts;
     float shared_weight;
     __half* act;                   // [slots][I] scratch
@@ -28,6 +29,12 @@ struct MoeLayerArgs {
 };
 
 enum StatusBits : int { kStatusMissingPage = 1, kStatusBadExpert = 2, kStatusTimeout = 4 };
+
+// Routed slots actually used by this launch (see MoeLayerArgs::num_active_dev).
+__device__ __forceinline__ int active_top_k(const MoeLayerArgs& a) {
+    if (a.num_active_dev == nullptr) return a.top_k;
+    return min(a.top_k, max(0, *a.num_active_dev));
+}
 
 __device__ __forceinline__ void flag(int* status, int bit) {
     if (status) atomicOr(status, bit);

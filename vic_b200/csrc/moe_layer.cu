@@ -23,6 +23,7 @@ namespace vib3 {
 // before any is consumed.
 template <class MATH, int B>
 __global__ void __launch_bounds__(256, 2) moe_gateup_kernel(MoeLayerArgs a) {
+    a.top_k = active_top_k(a);
     extern __shared__ __align__(16) unsigned char smem_raw[];
     typename MATH::XS* xs = reinterpret_cast<typename MATH::XS*>(smem_raw);
     const int nchunks = a.H / kGroupSize;
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(256, 2) moe_gateup_kernel(MoeLayerArgs a) {
 // accumulated in plan order, so the result does not depend on scheduling.
 template <int B, int SB>
 __global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
+    a.top_k = active_top_k(a);
     using MATH = MathQ16;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
@@ -245,7 +247,7 @@ static int launch_down(const MoeLayerArgs& a, cudaStream_t st) {
 
 using namespace vib3;
 
-static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void* page_table, int num_experts,
+static int moe_layer_dispatch(int phases, const int* num_active_dev, const void* x, int x_dtype, const void* page_table, int num_experts,
                               const void* shared_pages, const unsigned short* expert_ids, const float* expert_weights,
                               int top_k, float shared_weight, void* act_scratch, float* out, int out_accumulate,
                               int hidden_dim, int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
@@ -267,6 +269,7 @@ static int moe_layer_dispatch(int phases, const void* x, int x_dtype, const void
     a.x = x; a.x_dtype = x_dtype;
     a.page_table = (const PageEntry*)page_table; a.shared_pages = (const PageEntry*)shared_pages;
     a.expert_ids = expert_ids; a.expert_weights = expert_weights; a.top_k = top_k; a.num_experts = num_experts;
+    a.num_active_dev = num_active_dev;
     a.shared_weight = shared_weight; a.act = (__half*)act_scratch; a.out = out; a.out_accumulate = out_accumulate;
     a.H = hidden_dim; a.I = expert_hidden_dim; a.P = pages_per_segment;
     a.rpp_gu = rows_per_page_gate_up; a.rpp_dn = rows_per_page_down; a.status = status;
@@ -331,6 +334,44 @@ extern "C" int vib3_config_set(int key, int value) {
     return VIB3_ERR_UNSUPPORTED;
 }
 
-extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, VIB3_MOE_PASS); }
-extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, VIB3_MOE_PASS); }
-extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(2, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(2, nullptr, VIB3_MOE_PASS); }
+// Same as vib3_launch_moe_layer_int4_paged, but only the first min(top_k, *num_active_dev) routed slots
+// are used (a device-side count, e.g. the experts of a token that are resident on this GPU).
+extern "C" int vib3_launch_moe_layer_int4_paged_var(VIB3_MOE_ARGS, const int* num_active_dev) {
+    if (!num_active_dev) return VIB3_ERR_NULL;
+    return moe_layer_dispatch(3, num_active_dev, VIB3_MOE_PASS);
+}
+
+// Keep, in order, the (expert, weight) pairs whose expert lies in [expert_lo, expert_hi): the slots of
+// a token that an expert-parallel rank owns.  ids_out/weights_out have room for top_k entries; the
+// rest is filled with expert_lo / 0; *count_out receives the number kept.
+__global__ void select_local_experts_kernel(const unsigned short* ids, const float* w, int top_k, int lo, int hi,
+                                            unsigned short* ids_out, float* w_out, int* count_out) {
+    if (threadIdx.x != 0) return;
+    int n = 0;
+    for (int i = 0; i < top_k; ++i) {
+        const int e = ids[i];
+        if (e >= lo && e < hi) {
+            ids_out[n] = (unsigned short)e;
+            w_out[n] = w[i];
+            ++n;
+        }
+    }
+    *count_out = n;
+    for (int i = n; i < top_k; ++i) {
+        ids_out[i] = (unsigned short)lo;
+        w_out[i] = 0.f;
+    }
+}
+
+extern "C" int vib3_launch_select_local_experts(const unsigned short* ids, const float* weights, int top_k,
+                                                int expert_lo, int expert_hi, unsigned short* ids_out,
+                                                float* weights_out, int* count_out, void* stream) {
+    if (!ids || !weights || !ids_out || !weights_out || !count_out) return VIB3_ERR_NULL;
+    if (top_k <= 0 || top_k > kMaxSlots - 1 || expert_lo < 0 || expert_hi < expert_lo) return VIB3_ERR_COUNT;
+    select_local_experts_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ids, weights, top_k, expert_lo, expert_hi, ids_out,
+                                                                   weights_out, count_out);
+    return (int)cudaGetLastError();
+}

@@ -145,14 +145,14 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nchunks = a.H / kGroupSize;
-    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+    const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);  // shared-memory layout; the slots used may be fewer
     const unsigned code_row = (unsigned)a.H / 2, scale_row = (unsigned)a.H / 16;
     const unsigned stage_bytes = 2 * kTileRows * (code_row + scale_row);
 
     unsigned char* stages = smem_raw;
     unsigned char* xs = stages + (size_t)nstages * stage_bytes;
     PageEntry* tab = reinterpret_cast<PageEntry*>(xs + (size_t)nchunks * MATH::kStride);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tab + slots * 2 * a.P);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tab + max_slots * 2 * a.P);
     uint64_t* empty = full + kMaxStages;
     volatile unsigned* landed = reinterpret_cast<volatile unsigned*>(empty + kMaxStages);
 
@@ -168,7 +168,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     }
     // the activation vector does not come from the router: quantise it before waiting for the router
     if (warp < kConsumerWarps) stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
-    pdl_wait();  // expert ids and weights are the router's output
+    pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
+    a.top_k = active_top_k(a);
+    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     for (int i = tid; i < slots * 2 * a.P; i += blockDim.x) {
         const int s = i / (2 * a.P), rem = i % (2 * a.P);
         const PageEntry* pg = slot_pages(a, s);
@@ -307,15 +309,20 @@ template <int NCH>
 __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int nstages) {
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);  // launch shape and shared-memory layout
+    // The slot count may come from device memory; the kernel that wrote it had completed before the
+    // gate/up kernel passed its dependency wait, like the expert ids (see below).
+    a.top_k = active_top_k(a);
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-    const int cwarps = slots * kDownWarpsPerSlot;       // consumer warps; the producer is warp `cwarps`
+    const int cwarps = slots * kDownWarpsPerSlot;       // consumer warps in use
+    const int producer_warp = (int)(blockDim.x >> 5) - 1;
     const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
     const unsigned slot_bytes = kDownRows * (code_row + scale_row);
-    const unsigned stage_bytes = slots * slot_bytes;
+    const unsigned stage_bytes = max_slots * slot_bytes;
 
     unsigned char* stages = smem_raw;
     PageEntry* tab = reinterpret_cast<PageEntry*>(stages + (size_t)nstages * stage_bytes);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tab + slots * a.P);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tab + max_slots * a.P);
     uint64_t* empty = full + kMaxStages;
     float* wts = reinterpret_cast<float*>(empty + kMaxStages);
     float* ybuf = wts + kMaxSlots;  // [parity][row][kMaxSlots]
@@ -325,7 +332,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, cwarps);
+            mbar_init(empty + s, max(cwarps, 1));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -344,7 +351,14 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     int g0, g1;
     cta_share(a.H, g0, g1);
 
-    if (warp == cwarps) {
+    if (slots == 0) {  // nothing selected: the layer output is zero
+        if (!a.out_accumulate)
+            for (int r = g0 + tid; r < g1; r += blockDim.x) a.out[r] = 0.f;
+        return;
+    }
+    if (warp != producer_warp && warp >= cwarps) return;  // warps of unused slots
+
+    if (warp == producer_warp) {
         // ── producer warp: the weights do not depend on the previous kernel, so streaming starts at
         // once.  Lane k < 2 * slots issues copy k of a tile (slot k / 2: codes for even k, scales for
         // odd k); the byte total is summed across lanes for lane 0 to arm the barrier ──

@@ -7,10 +7,9 @@ scaling), which is how a data-parallel attention stage feeds an expert-parallel 
   1. every rank routes its own token (router weights are replicated, so the top-k is the one a
      single GPU would compute: bit-exact by construction);
   2. all_gather of (token activation, expert ids, routing weights): 14.4 KB per rank for Kimi;
-  3. for every token of the step, each rank runs the fused expert kernels over ITS OWN page table,
-     in which only its local experts are resident: the slots of experts that live elsewhere find no
-     page and contribute exactly zero (`out = fma(w, 0, out)`), the shared expert runs only on the
-     token's home rank;
+  3. for every token of the step, each rank keeps the (expert, weight) pairs of the experts it owns
+     (a device-side selection, order preserved) and runs the fused expert kernels over exactly those
+     slots of ITS OWN page table; the shared expert runs only on the token's home rank;
   4. reduce_scatter of the per-token partial sums [G, H] fp32: each rank receives the full layer
      output of its own token.
 
@@ -96,8 +95,12 @@ class ExpertParallelDecoder:
         self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
         self.ids_t = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
         self.w_t = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
-        self.ep_status = torch.zeros(1, dtype=torch.int32, device=dev)  # the missing-page bit is expected here
-        self.launches_per_step = 1 + 2 * world
+        self.ids_loc = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
+        self.w_loc = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
+        self.n_loc = torch.zeros(world, dtype=torch.int32, device=dev)
+        mine = local_experts(rank, sh.num_experts, world)
+        self.expert_lo, self.expert_hi = (mine[0], mine[-1] + 1) if mine else (0, 0)
+        self.launches_per_step = 1 + 3 * world
 
     def step(self, layer: int, x: torch.Tensor) -> torch.Tensor:
         """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
@@ -111,11 +114,15 @@ class ExpertParallelDecoder:
         self.ids_t.copy_(ids)
         self.w_t.copy_(ws)
         for t in range(self.world):
+            # the token's experts that live here, compacted on the device; the kernels then balance
+            # their work over exactly those slots (plus the shared expert on the token's home rank)
+            kernels.select_local_experts(self.ids_t[t], self.w_t[t], sh.top_k, self.expert_lo, self.expert_hi,
+                                         self.ids_loc[t], self.w_loc[t], self.n_loc[t:t + 1])
             shared = dec.shared_tables[layer] if t == self.rank else 0
-            kernels.moe_layer_int4_paged(xs[t], dec.tables[layer], sh.num_experts, shared, self.ids_t[t], self.w_t[t],
-                                         sh.top_k, 1.0, dec.act, self.partial[t], False, H, sh.intermediate,
-                                         sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page,
-                                         self.ep_status)
+            kernels.moe_layer_int4_paged_var(xs[t], dec.tables[layer], sh.num_experts, shared, self.ids_loc[t],
+                                             self.w_loc[t], sh.top_k, 1.0, dec.act, self.partial[t], False, H,
+                                             sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page,
+                                             sh.down.rows_per_page, self.n_loc[t:t + 1], dec.status)
         combine_partials(self.out, self.partial, self.rank, self.world, self.group)
         return self.out
 
@@ -240,5 +247,9 @@ def bench_main(args) -> None:
                          "traffic": None, "note": "whole step over all ranks (per-kernel roofline is reported at N=1)"},
         }
         print(json.dumps(line))
-    dist.barrier()
-    dist.destroy_process_group()
+    # leave without tearing the communicator down under a live CUDA graph that holds its kernels
+    graph = None
+    torch.cuda.synchronize()
+    import sys
+    sys.stdout.flush()
+    os._exit(0)

@@ -145,4 +145,24 @@ def moe_layer_int4_paged(x: torch.Tensor, page_table: int, num_experts: int, sha
         pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status), _stream(stream)))
 
 
+def moe_layer_int4_paged_var(x: torch.Tensor, page_table: int, num_experts: int, shared_pages: int, expert_ids,
+                             expert_weights, top_k: int, shared_weight: float, act_scratch, out, out_accumulate: bool,
+                             hidden_dim: int, expert_hidden_dim: int, pages_per_segment: int,
+                             rows_per_page_gate_up: int, rows_per_page_down: int, num_active_dev, status=None,
+                             stream: Optional[int] = None) -> None:
+    """The fused sublayer over the first min(top_k, *num_active_dev) routed slots (device-side count)."""
+    check("moe_layer_int4_paged_var", lib().vib3_launch_moe_layer_int4_paged_var(
+        _ptr(x), x_dtype_code(x), page_table, num_experts, shared_pages or 0, _ptr(expert_ids), _ptr(expert_weights), top_k,
+        shared_weight, _ptr(act_scratch), _ptr(out), int(out_accumulate), hidden_dim, expert_hidden_dim,
+        pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status), _stream(stream),
+        _ptr(num_active_dev)))
+
+
+def select_local_experts(ids, weights, top_k: int, expert_lo: int, expert_hi: int, ids_out, weights_out, count_out,
+                         stream: Optional[int] = None) -> None:
+    check("select_local_experts", lib().vib3_launch_select_local_experts(
+        _ptr(ids), _ptr(weights), top_k, expert_lo, expert_hi, _ptr(ids_out), _ptr(weights_out), _ptr(count_out),
+        _stream(stream)))
+
+
 __all__ = [n for n in dir() if not n.startswith("_")] + ["SCORING_SOFTMAX", "SCORING_SIGMOID"]
