@@ -37,20 +37,24 @@ def _worker(rank, world, port, ret):
         epd = ep.ExpertParallelDecoder(mine, rank, world)
         ref = MoeDecoder(full)
         g = torch.Generator(device=dev).manual_seed(100 + rank)
-        worst = 0.0
-        for step in range(4):
+        # every rank runs every step's collectives whatever it observes; verdicts are reported at the end
+        worst, problems = 0.0, []
+        for step in range(6):
             x = torch.randn(sh.hidden, generator=g, device=dev).to(torch.bfloat16)
             layer = step % 2
             out = epd.step(layer, x).clone()
             ids_ep = epd.dec.routing()[0].tolist()
             want = ref.forward_layer(layer, x).clone()
             torch.cuda.synchronize()
-            assert ids_ep == ref.routing()[0].tolist()
-            assert int(ref.status.item()) == 0
+            if ids_ep != ref.routing()[0].tolist():
+                problems.append(f"step {step}: routing differs")
+            if int(ref.status.item()) != 0 or int(epd.dec.status.item()) != 0:
+                problems.append(f"step {step}: status word set")
             a, b = out.cpu().numpy(), want.cpu().numpy()
             worst = max(worst, float(np.linalg.norm(a - b) / np.linalg.norm(b)))
-            assert np.max(np.abs(a - b)) <= 2e-2
-        ret[rank] = worst
+            if np.max(np.abs(a - b)) > 2e-2:
+                problems.append(f"step {step}: max-abs {np.max(np.abs(a - b)):.3e}")
+        ret[rank] = (worst, problems)
     finally:
         dist.destroy_process_group()
 
@@ -66,4 +70,6 @@ def test_expert_parallel_equals_single_gpu():
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert len(ret) == world
     for r in range(world):
-        assert ret[r] <= 1e-3, (r, ret[r])   # relative L2 of the layer output
+        worst, problems = ret[r]
+        assert not problems, (r, problems)
+        assert worst <= 1e-3, (r, worst)   # relative L2 of the layer output

@@ -190,7 +190,7 @@ def test_fused_vs_per_page_sequence_and_reference_kernels(cuda_dev, oracle):
             assert_close(seq_out.cpu().numpy(), ref_out.cpu().numpy(), f"{name}: per-page vs reference kernels")
 
 
-def test_device_side_slot_count_and_local_selection(cuda_dev):
+def test_device_side_slot_count_and_local_selection(cuda_dev, oracle):
     """vib3_launch_select_local_experts keeps a rank's experts in order; the `_var` launcher over the
     kept slots equals the plain launcher given the same experts explicitly (bit for bit)."""
     from vic_b200 import kernels
@@ -206,8 +206,12 @@ def test_device_side_slot_count_and_local_selection(cuda_dev):
     n_loc = torch.zeros(1, dtype=torch.int32, device=cuda_dev)
     out_var = torch.zeros(sh.hidden, dtype=torch.float32, device=cuda_dev)
     out_ref = torch.zeros(sh.hidden, dtype=torch.float32, device=cuda_dev)
-    for t, (lo, hi, shared) in enumerate([(0, 192, True), (192, 384, False), (380, 384, False)]):
-        dec.route(0, xs[t])
+    for t, (lo, hi, shared) in enumerate([(0, 192, True), (192, 384, False), (380, 384, False)] * 2):
+        if t >= 3:   # second round: ranges that leave exactly one or two slots
+            dec.route(0, xs[t % 3])
+            one = int(dec.routing()[0][t % 3 + 1])
+            lo, hi, shared = one, one + 1, (t == 5)
+        dec.route(0, xs[t % 3])
         ids, ws = dec.routing()
         kernels.select_local_experts(dec.ids, dec.weights, sh.top_k, lo, hi, ids_loc, w_loc, n_loc)
         torch.cuda.synchronize()
@@ -217,11 +221,11 @@ def test_device_side_slot_count_and_local_selection(cuda_dev):
         assert ids_loc[:n].cpu().numpy().view(np.uint16).tolist() == [e for e, _ in keep]
         assert w_loc[:n].cpu().tolist() == [w for _, w in keep]
         sp = dec.shared_tables[0] if shared else 0
-        kernels.moe_layer_int4_paged_var(xs[t], dec.tables[0], sh.num_experts, sp, ids_loc, w_loc, sh.top_k, 1.0, dec.act,
+        kernels.moe_layer_int4_paged_var(xs[t % 3], dec.tables[0], sh.num_experts, sp, ids_loc, w_loc, sh.top_k, 1.0, dec.act,
                                          out_var, False, sh.hidden, sh.intermediate, sh.pages_per_segment,
                                          sh.gate_up.rows_per_page, sh.down.rows_per_page, n_loc, dec.status)
         if n + (1 if shared else 0) > 0:
-            kernels.moe_layer_int4_paged(xs[t], dec.tables[0], sh.num_experts, sp, ids_loc, w_loc, n, 1.0, dec.act, out_ref,
+            kernels.moe_layer_int4_paged(xs[t % 3], dec.tables[0], sh.num_experts, sp, ids_loc, w_loc, n, 1.0, dec.act, out_ref,
                                          False, sh.hidden, sh.intermediate, sh.pages_per_segment,
                                          sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status) if n > 0 or shared else None
         else:
@@ -229,6 +233,12 @@ def test_device_side_slot_count_and_local_selection(cuda_dev):
         torch.cuda.synchronize()
         assert int(dec.status.item()) == 0
         assert torch.equal(out_var, out_ref), (t, n)
+        if t >= 3:   # one or two slots: check against the oracle as well
+            ex = oracle_experts(oracle, model, 0, keep)
+            if not shared:
+                ex = ex[:len(keep)]
+            want = oracle.moe_layer(xs[t % 3].float().cpu().numpy(), ex, sh.hidden, sh.intermediate, oracle.SCALE_FP16, "gpu")
+            assert_close(out_var.cpu().numpy(), want, f"{n} routed slot(s), shared={shared}")
 
 
 def test_fused_launcher_refusals(cuda_dev):

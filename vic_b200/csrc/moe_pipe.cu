@@ -299,7 +299,8 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
 // global memory, and keeps them for the whole kernel.  All consumer warps work on the same tile
 // (4 output rows x all slots; warp (slot, h) takes rows h and h+2), so every ring stage ahead of it
 // is look-ahead.  Per-row results y[row][slot] (rounded to fp16 as the reference's down projection)
-// meet in shared memory; after a barrier of the consumer warps, warp r adds row r in plan order.
+// meet in shared memory; after a barrier of the consumer warps, lane r of warp 0 adds row r in plan
+// order.
 // stage layout: per slot [codes R*I/2][scales R*I/16], R = 4.
 constexpr int kDownRows = 4;
 constexpr int kDownWarpsPerSlot = 2;
@@ -443,10 +444,10 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + st);  // this warp has read everything it needs from the stage
         asm volatile("bar.sync 1, %0;" ::"r"(cwarps * 32) : "memory");  // consumer warps only
-        if (warp < t.nrows && lane == 0) {
+        if (warp == 0 && lane < t.nrows) {  // lane r adds row r's contributions
             float out = 0.f;
-            for (int k = 0; k < slots; ++k) out = fmaf(wts[k], yb[warp * kMaxSlots + k], out);  // plan order
-            const int r = t.row + warp;
+            for (int k = 0; k < slots; ++k) out = fmaf(wts[k], yb[lane * kMaxSlots + k], out);  // plan order
+            const int r = t.row + lane;
             if (a.out_accumulate) a.out[r] += out;
             else a.out[r] = out;
         }
