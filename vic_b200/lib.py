@@ -81,7 +81,7 @@ SIGNATURES = {
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
-        path = _build.LIB_PATH
+        path = os.environ.get("VIB3_CUDA_LIB") or _build.LIB_PATH   # override: a differently tuned build of the same ABI
         if not os.path.exists(path):
             path = _build.build()
         handle = C.CDLL(path)
