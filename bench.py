@@ -264,7 +264,8 @@ def main():
     torch.cuda.set_device(dev)
     sh = KIMI
     model = build_synthetic_moe(sh, PHYS_LAYERS, dev, seed=SEED, slot_seed=99)
-    dec = MoeDecoder(model, exact_order=True)
+    # A/B: VIB3_BENCH_TWO_KERNELS=1 runs gate/up and down as two launches instead of one cooperative kernel
+    dec = MoeDecoder(model, exact_order=True, single_kernel=os.environ.get("VIB3_BENCH_TWO_KERNELS") != "1")
     gen = torch.Generator(device=dev).manual_seed(SEED)
     xs = synth_activation(sh, gen, dev, torch.bfloat16, N_TOKENS)
     outs = torch.zeros(N_TOKENS, sh.hidden, dtype=torch.float32, device=dev)
@@ -345,6 +346,13 @@ def main():
         k_us = time_kernel(lambda i: phase_launch(i, 1))
         down_us = time_kernel(lambda i: phase_launch(i, 2))
         router_us = time_kernel(lambda i: dec.route(i % PHYS_LAYERS, xs[i]))
+
+        def single_launch(i):
+            kernels.moe_layer_int4_paged_fused(xs[i], dec.tables[i % PHYS_LAYERS], sh.num_experts,
+                                               dec.shared_tables[i % PHYS_LAYERS], ids_all[i], w_all[i], sh.top_k, 1.0,
+                                               dec.act, dec.out, False, sh.hidden, sh.intermediate, sh.pages_per_segment,
+                                               sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.workspace[2:], dec.status)
+        single_us = time_kernel(single_launch)
         variants = {}
         if os.environ.get("VIB3_BENCH_VARIANTS") == "1":   # A/B of library options in one process
             from vic_b200.lib import lib as _lib
@@ -410,10 +418,10 @@ def main():
                      "traffic": 152.43e6, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same shape (profiles/moe_gateup_down_kimi_batch1.md)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sh.hidden * 2, "d2h_bytes_per_step": sh.hidden * 4,
                 "ms_per_step": e2e_ms / K},
-        "kernel_us": {"router": router_us, "gate_up": k_us, "down": down_us,
+        "kernel_us": {"router": router_us, "gate_up": k_us, "down": down_us, "gate_up_and_down_single_kernel": single_us,
                       "note": "each kernel alone, back to back in a CUDA graph over rotating layers/tokens"},
         "variants_us": variants,
-        "gpu_launches": 3 * K,
+        "gpu_launches": dec.launches_per_layer * K,
         "clocks": clocks,
         "router_recomputations": int(dec.workspace[1].item()),
     }

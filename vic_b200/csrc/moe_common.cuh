@@ -56,6 +56,9 @@ __device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, in
 // direct-load kernels.
 int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st);
 int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st);
+// both phases in one cooperative kernel (moe_fused.cu); `grid_ws` = two zeroed words for its grid barrier
+int launch_layer_fused(const MoeLayerArgs& a, unsigned* grid_ws, cudaStream_t st);
+extern int g_fused_mode;
 int sm_count();
 
 // Run-time switch: 1 (default) = staged kernels where the shape allows, 0 = direct-load kernels only.
