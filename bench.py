@@ -264,8 +264,11 @@ def main():
     torch.cuda.set_device(dev)
     sh = KIMI
     model = build_synthetic_moe(sh, PHYS_LAYERS, dev, seed=SEED, slot_seed=99)
-    # A/B: VIB3_BENCH_TWO_KERNELS=1 runs gate/up and down as two launches instead of one cooperative kernel
-    dec = MoeDecoder(model, exact_order=True, single_kernel=os.environ.get("VIB3_BENCH_TWO_KERNELS") != "1")
+    # A/B: VIB3_BENCH_SINGLE_KERNEL=1 runs gate/up and down as one cooperative kernel instead of two launches
+    dec = MoeDecoder(model, exact_order=True, single_kernel=os.environ.get("VIB3_BENCH_SINGLE_KERNEL") == "1")
+    if os.environ.get("VIB3_BENCH_SINGLE_KERNEL_MODE"):   # A/B: 1 cooperative launch only, 2 with programmatic dependent launch
+        from vic_b200.lib import lib as _l
+        _l().vib3_config_set(3, int(os.environ["VIB3_BENCH_SINGLE_KERNEL_MODE"]))
     gen = torch.Generator(device=dev).manual_seed(SEED)
     xs = synth_activation(sh, gen, dev, torch.bfloat16, N_TOKENS)
     outs = torch.zeros(N_TOKENS, sh.hidden, dtype=torch.float32, device=dev)
@@ -345,7 +348,10 @@ def main():
         reps = 8
         k_us = time_kernel(lambda i: phase_launch(i, 1))
         down_us = time_kernel(lambda i: phase_launch(i, 2))
+        redo0 = int(dec.workspace[1].item())
         router_us = time_kernel(lambda i: dec.route(i % PHYS_LAYERS, xs[i]))
+        # share of the timed router launches that recomputed near-tied logits in sequential order
+        router_redo_share = (int(dec.workspace[1].item()) - redo0) / float(3 + n_k * (reps + 1))
 
         def single_launch(i):
             kernels.moe_layer_int4_paged_fused(xs[i], dec.tables[i % PHYS_LAYERS], sh.num_experts,
@@ -424,6 +430,7 @@ def main():
         "gpu_launches": dec.launches_per_layer * K,
         "clocks": clocks,
         "router_recomputations": int(dec.workspace[1].item()),
+        "router_recomputation_share_in_kernel_timing": router_redo_share,
     }
 
     if not args.no_cpu_baseline:

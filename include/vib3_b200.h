@@ -82,8 +82,8 @@ int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_
 /* Single-launch router (no counterpart signature in the reference; semantics of
  * run_router_with_scoring_and_bias, src/compute/kernels.rs:2307-2440).  x_dtype VIB3_X_*,
  * w_dtype VIB3_W_*.  bias: added to the score for selection only (the reference's correction bias);
- * logit_offset: added to the logit before scoring.  scores_buf: num_experts floats, 2*num_experts
- * when exact_order != 0.
+ * logit_offset: added to the logit before scoring.  scores_buf: 3 * num_experts floats; the first
+ * num_experts receive the logits, the rest is scratch.
  * exact_order != 0 makes the selected indices equal to those of the reference's CPU router
  * (sequential fp32 summation) even for near-tied experts.  workspace: two uint32, zero before
  * the first call; [0] is left zero by every call, [1] counts near-tie recomputations; calls

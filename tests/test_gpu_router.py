@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 class _Router:
     def __init__(self, dev, E):
         self.dev = dev
-        self.scores = torch.zeros(2 * E, dtype=torch.float32, device=dev)
+        self.scores = torch.zeros(3 * E, dtype=torch.float32, device=dev)
         self.ids = torch.zeros(16, dtype=torch.int16, device=dev)
         self.w = torch.zeros(16, dtype=torch.float32, device=dev)
         self.ws = torch.zeros(4, dtype=torch.int32, device=dev)

@@ -182,12 +182,15 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
 // global memory, and keeps them for the whole kernel.  All consumer warps work on the same tile
 // (4 output rows x all slots; warp (slot, h) takes rows h and h+2), so every ring stage ahead of it
 // is look-ahead.  Per-row results y[row][slot] (rounded to fp16 as the reference's down projection)
-// meet in shared memory; after a barrier of the consumer warps, lane r of warp 0 adds row r in plan
-// order.
+// go to a small ring in shared memory; a separate combiner warp adds each row in plan order and
+// writes the output.  The hand-over is by mbarriers (y-full: one arrival per consumer warp, y-empty:
+// one arrival by the combiner), so consumer warps never wait for one another: they drift apart by
+// up to the depth of the rings, and loads, integer math and shuffles of different warps overlap.
 // stage layout: per slot [codes R*I/2][scales R*I/16], R = 4.
 constexpr int kDownRows = 4;
 constexpr int kDownWarpsPerSlot = 2;
-constexpr int kDownMaxThreads = 640;  // 19 warps for 9 slots; leaves ~100 registers per thread
+constexpr int kDownYStages = 4;
+constexpr int kDownMaxThreads = 640;  // 18 consumer warps for 9 slots + combiner + producer
 
 template <int NCH>
 __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int nstages) {
@@ -200,6 +203,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const int cwarps = slots * kDownWarpsPerSlot;       // consumer warps in use
     const int producer_warp = (int)(blockDim.x >> 5) - 1;
+    const int combiner_warp = producer_warp - 1;
     const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
     const unsigned slot_bytes = kDownRows * (code_row + scale_row);
     const unsigned stage_bytes = max_slots * slot_bytes;
@@ -208,8 +212,10 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     PageEntry* tab = reinterpret_cast<PageEntry*>(stages + (size_t)nstages * stage_bytes);
     uint64_t* full = reinterpret_cast<uint64_t*>(tab + max_slots * a.P);
     uint64_t* empty = full + kMaxStages;
-    float* wts = reinterpret_cast<float*>(empty + kMaxStages);
-    float* ybuf = wts + kMaxSlots;  // [parity][row][kMaxSlots]
+    uint64_t* yfull = empty + kMaxStages;
+    uint64_t* yempty = yfull + kDownYStages;
+    float* wts = reinterpret_cast<float*>(yempty + kDownYStages);
+    float* ybuf = wts + kMaxSlots;  // [y stage][row][kMaxSlots]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_trigger();
@@ -217,6 +223,10 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, max(cwarps, 1));
+        }
+        for (int s = 0; s < kDownYStages; ++s) {
+            mbar_init(yfull + s, max(cwarps, 1));
+            mbar_init(yempty + s, 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -240,7 +250,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             for (int r = g0 + tid; r < g1; r += blockDim.x) a.out[r] = 0.f;
         return;
     }
-    if (warp != producer_warp && warp >= cwarps) return;  // warps of unused slots
+    if (warp < combiner_warp && warp >= cwarps) return;  // warps of unused slots
 
     if (warp == producer_warp) {
         // ── producer warp: the weights do not depend on the previous kernel, so streaming starts at
@@ -282,6 +292,32 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         return;
     }
 
+    if (warp == combiner_warp) {
+        // ── combiner warp: lane r adds row r of each tile over the slots, in plan order ──
+        TileWalk walk(g0, g1, a.H, a.rpp_dn, kDownRows);
+        Tile t;
+        int n = 0;
+        while (walk.next(t)) {
+            const int ys = n % kDownYStages;
+            if (!mbar_wait(yfull + ys, (n / kDownYStages) & 1)) {
+                if (lane == 0) flag(a.status, kStatusTimeout);
+                return;
+            }
+            if (lane < t.nrows) {
+                const float* yb = ybuf + ys * (kDownRows * kMaxSlots) + lane * kMaxSlots;
+                float out = 0.f;
+                for (int k = 0; k < slots; ++k) out = fmaf(wts[k], yb[k], out);
+                const int r = t.row + lane;
+                if (a.out_accumulate) a.out[r] += out;
+                else a.out[r] = out;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(yempty + ys);
+            ++n;
+        }
+        return;
+    }
+
     // ── consumers: warp (s, h) keeps slot s's activation chunks in registers ──
     const int s = warp / kDownWarpsPerSlot, h = warp % kDownWarpsPerSlot;
     pdl_wait();  // the activations are the gate/up kernel's output
@@ -306,10 +342,11 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         }
         const PageEntry e = tab[s * a.P + t.page];
         const bool present = e.ptr != 0 && t.rin + t.nrows <= e.row_count;
-        float* yb = ybuf + (n & 1) * (kDownRows * kMaxSlots);
         const uint32_t sb = stages_addr + st * stage_bytes;
+        float y[kDownRows / kDownWarpsPerSlot];
 #pragma unroll
-        for (int r = h; r < kDownRows; r += kDownWarpsPerSlot) {
+        for (int j = 0; j < kDownRows / kDownWarpsPerSlot; ++j) {
+            const int r = h + j * kDownWarpsPerSlot;
             float acc = 0.f;
             if (r < t.nrows && present) {
 #pragma unroll
@@ -319,20 +356,25 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
                     acc = MATH::chunk_r(q, sc, xv[i], sx[i], sq8[i], acc);
                 }
             }
-            const float y = warp_sum(acc);
-            // fp16 rounding of the down projection (its output buffer is fp16 in the reference)
-            if (lane == 0) yb[r * kMaxSlots + s] = __half2float(__float2half_rn(y));
+            y[j] = acc;
         }
-        if (!present && h == 0 && lane == 0) flag(a.status, kStatusMissingPage);
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + st);  // this warp has read everything it needs from the stage
-        asm volatile("bar.sync 1, %0;" ::"r"(cwarps * 32) : "memory");  // consumer warps only
-        if (warp == 0 && lane < t.nrows) {  // lane r adds row r's contributions
-            float out = 0.f;
-            for (int k = 0; k < slots; ++k) out = fmaf(wts[k], yb[lane * kMaxSlots + k], out);  // plan order
-            const int r = t.row + lane;
-            if (a.out_accumulate) a.out[r] += out;
-            else a.out[r] = out;
+#pragma unroll
+        for (int j = 0; j < kDownRows / kDownWarpsPerSlot; ++j) y[j] = warp_sum(y[j]);
+        if (!present && h == 0 && lane == 0) flag(a.status, kStatusMissingPage);
+        const int ys = n % kDownYStages;
+        if (n >= kDownYStages && !mbar_wait(yempty + ys, ((n / kDownYStages) - 1) & 1)) {
+            if (lane == 0) flag(a.status, kStatusTimeout);
+            return;
+        }
+        if (lane == 0) {
+            float* yb = ybuf + ys * (kDownRows * kMaxSlots);
+            // fp16 rounding of the down projection (its output buffer is fp16 in the reference)
+#pragma unroll
+            for (int j = 0; j < kDownRows / kDownWarpsPerSlot; ++j)
+                yb[(h + j * kDownWarpsPerSlot) * kMaxSlots + s] = __half2float(__float2half_rn(y[j]));
+            mbar_arrive(yfull + ys);
         }
         ++n;
     }
@@ -415,17 +457,17 @@ int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const int nchunks = a.I / kGroupSize;
-    // register-resident activations: at most two chunks per lane; two warps per slot plus the producer
+    // register-resident activations: at most two chunks per lane; two warps per slot, combiner, producer
     if (nchunks != 32 && nchunks != 64) return VIB3_ERR_UNSUPPORTED;
-    if ((slots * kDownWarpsPerSlot + 1) * 32 > kDownMaxThreads) return VIB3_ERR_UNSUPPORTED;
+    if ((slots * kDownWarpsPerSlot + 2) * 32 > kDownMaxThreads) return VIB3_ERR_UNSUPPORTED;
     const size_t stage_bytes = (size_t)slots * kDownRows * ((size_t)a.I / 2 + (size_t)a.I / 16);
-    const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + 2 * kMaxStages * sizeof(uint64_t) +
-                         kMaxSlots * sizeof(float) + 2 * kDownRows * kMaxSlots * sizeof(float) + 128;
+    const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + 2 * (kMaxStages + kDownYStages) * sizeof(uint64_t) +
+                         kMaxSlots * sizeof(float) + kDownYStages * kDownRows * kMaxSlots * sizeof(float) + 128;
     const int nstages = pick_stages(fixed, stage_bytes, 2);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
     const size_t smem = fixed + (size_t)nstages * stage_bytes;
     const int grid = min(sm_count(), (a.H + kDownRows - 1) / kDownRows);
-    const int threads = (slots * kDownWarpsPerSlot + 1) * 32;
+    const int threads = (slots * kDownWarpsPerSlot + 2) * 32;
     return nchunks == 64 ? launch_down_pipe_t<2>(a, st, nstages, smem, grid, threads)
                          : launch_down_pipe_t<1>(a, st, nstages, smem, grid, threads);
 }

@@ -137,14 +137,12 @@ __device__ __forceinline__ float sigmoid_ref(float z) {
     return __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_rn(-z)));
 }
 
-// Scoring + top-k by one CTA of 256 threads; every thread owns experts tid and tid+256.
-// smem: sel[E], sig[E], keys for the block reductions.
+// Scoring by one CTA of 256 threads, selection and weights by its first warp.
 struct __align__(16) TopKSmem {
     float prod[8][1024];   // per-warp products of the sequential-order recomputation (16-byte aligned: read as float4)
     float logit[kRouterMaxExperts];
     float sig[kRouterMaxExperts];
     float sel[kRouterMaxExperts];
-    unsigned long long wmax[2][8];
     int chosen[kRouterMaxTopK + 1];
     float wid[kRouterMaxExperts];
     int redo;
@@ -152,35 +150,36 @@ struct __align__(16) TopKSmem {
     int cand[kRouterMaxExperts];
 };
 
-__device__ void block_select(const RouterArgs& a, TopKSmem& sm, int nsel) {
-    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    unsigned long long key[2];
+// The best `nsel` entries of sm.sel[0 .. E) in descending order, ties towards the lower expert index,
+// found by ONE warp: lane l keeps the keys of experts l, l + 32, ... in registers; a round is two
+// warp-wide integer reductions (largest key, then lowest index holding it).  Lane i returns the
+// i-th selected expert (-1 when fewer exist).
+__device__ int warp_select(const RouterArgs& a, const TopKSmem& sm, int nsel) {
+    const int lane = threadIdx.x & 31;
+    constexpr int kPerLane = kRouterMaxExperts / 32;
+    unsigned key[kPerLane];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const int e = tid + 256 * j;
-        key[j] = e < a.E ? ((unsigned long long)orderable(sm.sel[e]) << 32) | (unsigned)(0xFFFFu - e) : 0ull;
+    for (int j = 0; j < kPerLane; ++j) {
+        const int e = lane + 32 * j;
+        key[j] = e < a.E ? orderable(sm.sel[e]) : 0u;
     }
+    int mine = -1;
     for (int round = 0; round < nsel; ++round) {
-        unsigned long long m = key[0] > key[1] ? key[0] : key[1];
+        unsigned m = key[0];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xffffffffu, m, o);
-            m = other > m ? other : m;
-        }
-        if (lane == 0) sm.wmax[round & 1][wid] = m;
-        __syncthreads();
-        unsigned long long best = sm.wmax[round & 1][0];
+        for (int j = 1; j < kPerLane; ++j) m = max(m, key[j]);
+        const unsigned best = __reduce_max_sync(0xffffffffu, m);
+        unsigned idx = 0xFFFFu;
 #pragma unroll
-        for (int w = 1; w < 8; ++w) {
-            const unsigned long long v = sm.wmax[round & 1][w];
-            best = v > best ? v : best;
-        }
-        const int e = 0xFFFF - (int)(best & 0xFFFFu);
-        if (key[0] == best) key[0] = 0ull;
-        if (key[1] == best) key[1] = 0ull;
-        if (tid == 0) sm.chosen[round] = best ? e : -1;
+        for (int j = kPerLane - 1; j >= 0; --j)
+            if (key[j] == best) idx = (unsigned)(lane + 32 * j);
+        const unsigned who = __reduce_min_sync(0xffffffffu, idx);
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j)
+            if ((unsigned)(lane + 32 * j) == who) key[j] = 0u;
+        if (lane == round) mine = best ? (int)who : -1;
     }
-    __syncthreads();
+    return mine;
 }
 
 __device__ void block_score(const RouterArgs& a, TopKSmem& sm) {
@@ -199,120 +198,142 @@ __device__ void block_score(const RouterArgs& a, TopKSmem& sm) {
 }
 
 __device__ void router_finish(const RouterArgs& a, TopKSmem& sm) {
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = min(a.top_k, a.E);
-    // one round trip: logits and (exact-order mode) the sums of |x w| together
-    for (int e = tid; e < a.E; e += blockDim.x) {
-        sm.logit[e] = __ldcg(a.scores + e);
-        if (a.exact_order) sm.wid[e] = __ldcg(a.scores + a.E + e);
+    const int nsel = min(k + 1, a.E);
+    const bool exact = a.exact_order && nsel > 1;
+    // one round trip: logits and (exact-order mode) the sums of |x w| together; then scoring and,
+    // in exact-order mode, the half-width of each expert's selection score under a change of
+    // summation order.  The logits of two fp32 summation orders of H products differ by less than
+    //     eps = 16 * 2^-24 * (sqrt(H) * |S| + sum |x w|)
+    // (the oracle's tests check this bound with a 4x margin); a selection score moves by at most eps
+    // times the local slope of the scoring function (1 for raw logits, s (1 - s) for the sigmoid,
+    // taken 1.25x for the curvature) plus a few ulps of rounding.
+    // (single-launch path, sigmoid mode: the GEMV CTAs have already stored the sigmoid of their logits)
+    const bool have_sig = a.counter != nullptr && a.mode != 0;
+    constexpr int kPerThread = kRouterMaxExperts / 256;
+    float z[kPerThread], ab[kPerThread], sg[kPerThread];
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {  // all loads first: one round trip
+        const int e = tid + 256 * j;
+        z[j] = e < a.E ? __ldcg(a.scores + e) : 0.f;
+        ab[j] = (exact && e < a.E) ? __ldcg(a.scores + a.E + e) : 0.f;
+        sg[j] = (have_sig && e < a.E) ? __ldcg(a.scores + 2 * a.E + e) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kPerThread; ++j) {
+        const int e = tid + 256 * j;
+        if (e >= a.E) continue;
+        float s = z[j], sel = z[j];
+        if (a.mode != 0) {
+            s = have_sig ? sg[j] : sigmoid_ref(z[j]);
+            sel = a.bias ? __fadd_rn(s, a.bias[e]) : s;
+        }
+        sm.logit[e] = z[j];
+        sm.sig[e] = s;
+        sm.sel[e] = sel;
+        if (exact) {
+            const float eps = 16.f * 5.9604645e-8f * (sqrtf((float)a.H) * fabsf(z[j]) + ab[j]);
+            const float slope = a.mode == 0 ? 1.f : 1.25f * s * (1.f - s);
+            sm.wid[e] = eps * slope + 2.f * 1.1920929e-7f * fmaxf(fabsf(sel), 1e-30f);
+        }
+    }
+    if (tid == 0) sm.redo = 0;
+    __syncthreads();
+
+    int mine = -1;  // warp 0: lane i holds the i-th selected expert
+    if (warp == 0) {
+        mine = warp_select(a, sm, nsel);
+        if (exact) {
+            // adjacent scores among the best k+1 closer than their widths: the order may differ
+            const int next = __shfl_down_sync(0xffffffffu, mine, 1);
+            bool close = false;
+            if (lane + 1 < nsel && mine >= 0 && next >= 0)
+                close = sm.sel[mine] - sm.sel[next] <= sm.wid[mine] + sm.wid[next];
+            if (__ballot_sync(0xffffffffu, close)) {
+                if (lane < nsel) sm.chosen[lane] = mine;
+                if (lane == 0) sm.redo = 1;
+            }
+        }
     }
     __syncthreads();
-    block_score(a, sm);
-    const int nsel = min(k + 1, a.E);
-    block_select(a, sm, nsel);
 
-    if (a.exact_order && nsel > 1) {
-        // Half-width of each expert's selection score under a change of summation order.  The
-        // logits of two fp32 summation orders of H products differ by less than
-        //     eps = 16 * 2^-24 * (sqrt(H) * |S| + sum |x w|)
-        // (the oracle's tests check this bound with a 4x margin); a selection score moves by at
-        // most eps times the local slope of the scoring function (1 for raw logits, s (1 - s) for
-        // the sigmoid, taken 1.25x for the curvature) plus a few ulps of rounding.
+    if (sm.redo) {
+        // candidates: every expert whose score interval overlaps that of one of the best k+1
+        const int last = sm.chosen[nsel - 1];
+        if (tid == 0) sm.ncand = 0;
+        __syncthreads();
         for (int e = tid; e < a.E; e += blockDim.x) {
-            const float ab = sm.wid[e];  // same thread wrote it above
-            const float eps = 16.f * 5.9604645e-8f * (sqrtf((float)a.H) * fabsf(sm.logit[e]) + ab);
-            const float slope = a.mode == 0 ? 1.f : 1.25f * sm.sig[e] * (1.f - sm.sig[e]);
-            sm.wid[e] = eps * slope + 2.f * 1.1920929e-7f * fmaxf(fabsf(sm.sel[e]), 1e-30f);
-        }
-        if (tid == 0) sm.redo = 0;
-        __syncthreads();
-        if (tid == 0) {
-            int redo = 0;
-            for (int i = 0; i + 1 < nsel; ++i) {
-                const int e0 = sm.chosen[i], e1 = sm.chosen[i + 1];
-                if (e0 < 0 || e1 < 0) break;
-                if (sm.sel[e0] - sm.sel[e1] <= sm.wid[e0] + sm.wid[e1]) redo = 1;
-            }
-            sm.redo = redo;
-        }
-        __syncthreads();
-        if (sm.redo) {
-            // candidates: every expert whose score interval overlaps that of one of the best k+1
-            const int last = sm.chosen[nsel - 1];
-            if (tid == 0) sm.ncand = 0;
-            __syncthreads();
-            for (int e = tid; e < a.E; e += blockDim.x) {
-                bool cand = false;
-                if (last < 0 || sm.sel[e] + sm.wid[e] >= sm.sel[last] - sm.wid[last])
-                    for (int i = 0; i < nsel; ++i) {
-                        const int c = sm.chosen[i];
-                        if (c >= 0 && c != e && fabsf(sm.sel[e] - sm.sel[c]) <= sm.wid[e] + sm.wid[c]) cand = true;
-                    }
-                if (cand) sm.cand[atomicAdd(&sm.ncand, 1)] = e;
-            }
-            __syncthreads();
-            // the CPU router's order: one chain per expert, multiply then add, d = 0 .. H-1
-            // (kernels.rs:2346-2350).  A warp forms 1024 rounded products at a time in parallel;
-            // lane 0 then adds them in order.
-            const int wid = tid >> 5, lane = tid & 31;
-            for (int ci = wid; ci < sm.ncand; ci += 8) {
-                const int e = sm.cand[ci];
-                const size_t base = (size_t)e * a.H;
-                float acc = 0.f;
-                for (int d0 = 0; d0 < a.H; d0 += 1024) {
-                    const int n = min(1024, a.H - d0);
-                    for (int i = lane; i < n; i += 32)
-                        sm.prod[wid][i] = __fmul_rn(load_x_as_f32(a.x, a.x_dtype, d0 + i), load_w(a.W, a.w_dtype, base + d0 + i));
-                    __syncwarp();
-                    if (lane == 0) {
-                        int i = 0;
-                        for (; i + 4 <= n; i += 4) {
-                            const float4 p = *reinterpret_cast<const float4*>(&sm.prod[wid][i]);
-                            acc = __fadd_rn(acc, p.x);
-                            acc = __fadd_rn(acc, p.y);
-                            acc = __fadd_rn(acc, p.z);
-                            acc = __fadd_rn(acc, p.w);
-                        }
-                        for (; i < n; ++i) acc = __fadd_rn(acc, sm.prod[wid][i]);
-                    }
-                    __syncwarp();
+            bool cand = false;
+            if (last < 0 || sm.sel[e] + sm.wid[e] >= sm.sel[last] - sm.wid[last])
+                for (int i = 0; i < nsel; ++i) {
+                    const int c = sm.chosen[i];
+                    if (c >= 0 && c != e && fabsf(sm.sel[e] - sm.sel[c]) <= sm.wid[e] + sm.wid[c]) cand = true;
                 }
+            if (cand) sm.cand[atomicAdd(&sm.ncand, 1)] = e;
+        }
+        __syncthreads();
+        // the CPU router's order: one chain per expert, multiply then add, d = 0 .. H-1
+        // (kernels.rs:2346-2350).  A warp forms 1024 rounded products at a time in parallel;
+        // lane 0 then adds them in order.
+        for (int ci = warp; ci < sm.ncand; ci += 8) {
+            const int e = sm.cand[ci];
+            const size_t base = (size_t)e * a.H;
+            float acc = 0.f;
+            for (int d0 = 0; d0 < a.H; d0 += 1024) {
+                const int n = min(1024, a.H - d0);
+                for (int i = lane; i < n; i += 32)
+                    sm.prod[warp][i] = __fmul_rn(load_x_as_f32(a.x, a.x_dtype, d0 + i), load_w(a.W, a.w_dtype, base + d0 + i));
+                __syncwarp();
                 if (lane == 0) {
-                    if (a.logit_offset) acc = __fadd_rn(acc, a.logit_offset[e]);
-                    sm.logit[e] = acc;
-                    a.scores[e] = acc;
+                    int i = 0;
+                    for (; i + 4 <= n; i += 4) {
+                        const float4 p = *reinterpret_cast<const float4*>(&sm.prod[warp][i]);
+                        acc = __fadd_rn(acc, p.x);
+                        acc = __fadd_rn(acc, p.y);
+                        acc = __fadd_rn(acc, p.z);
+                        acc = __fadd_rn(acc, p.w);
+                    }
+                    for (; i < n; ++i) acc = __fadd_rn(acc, sm.prod[warp][i]);
                 }
+                __syncwarp();
             }
-            __syncthreads();
-            if (tid == 0 && a.counter) a.counter[1] += 1u;  // diagnostics: near-tie recomputations so far
-            block_score(a, sm);
-            block_select(a, sm, k);
+            if (lane == 0) {
+                if (a.logit_offset) acc = __fadd_rn(acc, a.logit_offset[e]);
+                sm.logit[e] = acc;
+                a.scores[e] = acc;
+            }
         }
+        __syncthreads();
+        if (tid == 0 && a.counter) a.counter[1] += 1u;  // diagnostics: near-tie recomputations so far
+        block_score(a, sm);
+        if (warp == 0) mine = warp_select(a, sm, k);
     }
 
-    if (tid == 0) {
-        if (a.mode == 0) {
-            float mx = -INFINITY;
-            for (int i = 0; i < k; ++i) mx = fmaxf(mx, sm.logit[sm.chosen[i]]);
-            float sum = 0.f;
-            for (int i = 0; i < k; ++i) sum = __fadd_rn(sum, exp_rn(__fsub_rn(sm.logit[sm.chosen[i]], mx)));
-            for (int i = 0; i < k; ++i) {
-                a.out_ids[i] = (unsigned short)sm.chosen[i];
-                a.out_weights[i] = __fdiv_rn(exp_rn(__fsub_rn(sm.logit[sm.chosen[i]], mx)), sum);
-            }
-        } else {
-            float w[kRouterMaxTopK];
-            float total = 0.f;
-            for (int i = 0; i < k; ++i) {
-                w[i] = sm.sig[sm.chosen[i]];
-                total = __fadd_rn(total, w[i]);
-            }
-            const bool norm = a.normalize && total > 1e-20f;
-            for (int i = 0; i < k; ++i) {
-                float v = norm ? __fdiv_rn(w[i], total) : w[i];
-                a.out_ids[i] = (unsigned short)sm.chosen[i];
-                a.out_weights[i] = __fmul_rn(v, a.scaling);
-            }
+    if (warp != 0) return;
+    // weights, lane i for the i-th selected expert; sums run in selection order
+    const bool live = lane < k && mine >= 0;
+    if (a.mode == 0) {
+        const float z = live ? sm.logit[mine] : -INFINITY;
+        float mx = z;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float ex = live ? exp_rn(__fsub_rn(z, mx)) : 0.f;
+        float sum = 0.f;
+        for (int i = 0; i < k; ++i) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, i));
+        if (live) {
+            a.out_ids[lane] = (unsigned short)mine;
+            a.out_weights[lane] = __fdiv_rn(ex, sum);
+        }
+    } else {
+        const float w = live ? sm.sig[mine] : 0.f;
+        float total = 0.f;
+        for (int i = 0; i < k; ++i) total = __fadd_rn(total, __shfl_sync(0xffffffffu, w, i));
+        const bool norm = a.normalize && total > 1e-20f;
+        if (live) {
+            const float v = norm ? __fdiv_rn(w, total) : w;
+            a.out_ids[lane] = (unsigned short)mine;
+            a.out_weights[lane] = __fmul_rn(v, a.scaling);
         }
     }
 }
@@ -339,6 +360,9 @@ __global__ void __launch_bounds__(256) router_kernel(RouterArgs a) {
         if (a.logit_offset) logit = __fadd_rn(logit, a.logit_offset[expert]);
         a.scores[expert] = logit;
         if (a.exact_order) a.scores[a.E + expert] = absum;
+        // single launch, sigmoid scoring: the double-precision exponential runs here, in parallel over
+        // the CTAs, instead of in the last CTA's serial tail
+        if (a.counter != nullptr && a.mode != 0) a.scores[2 * a.E + expert] = sigmoid_ref(logit);
     }
     if (a.counter == nullptr) return;
     __syncthreads();
@@ -441,7 +465,7 @@ extern "C" int vib3_launch_router_topk(const void* x_f32, const void* W_f16, flo
     return (int)cudaGetLastError();
 }
 
-// Extended launcher: one launch.  scores_buf holds E floats (2E when exact_order != 0);
+// Extended launcher: one launch.  scores_buf holds 3E floats ([0, E) receives the logits, the rest is scratch);
 // workspace is two 32-bit words, zero before the first call: [0] is an arrival counter that every
 // call leaves at zero, [1] counts the near-tie recomputations done so far (diagnostics).
 extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,

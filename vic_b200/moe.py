@@ -21,13 +21,13 @@ class MoeDecoder:
     """Device buffers and launch sequence for batch-1 decode over a SyntheticMoe (or any pool with
     the same page-table layout)."""
 
-    def __init__(self, model: SyntheticMoe, exact_order: bool = True, single_kernel: bool = True):
+    def __init__(self, model: SyntheticMoe, exact_order: bool = True, single_kernel: bool = False):
         self.model = model
         self.single_kernel = single_kernel  # gate/up and down in one cooperative kernel where the shape allows
         sh = model.shape
         dev = model.router_w.device
         self.exact_order = exact_order
-        self.scores = torch.zeros(2 * sh.num_experts, dtype=torch.float32, device=dev)
+        self.scores = torch.zeros(3 * sh.num_experts, dtype=torch.float32, device=dev)
         self.ids = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
         self.weights = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
         self.workspace = torch.zeros(4, dtype=torch.int32, device=dev)  # words 0-1: router, 2-3: grid barrier
