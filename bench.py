@@ -264,11 +264,10 @@ def main():
     torch.cuda.set_device(dev)
     sh = KIMI
     model = build_synthetic_moe(sh, PHYS_LAYERS, dev, seed=SEED, slot_seed=99)
-    # A/B: VIB3_BENCH_SINGLE_KERNEL=1 runs gate/up and down as one cooperative kernel instead of two launches
-    dec = MoeDecoder(model, exact_order=True, single_kernel=os.environ.get("VIB3_BENCH_SINGLE_KERNEL") == "1")
-    if os.environ.get("VIB3_BENCH_SINGLE_KERNEL_MODE"):   # A/B: 1 cooperative launch only, 2 with programmatic dependent launch
+    dec = MoeDecoder(model, exact_order=True)
+    if os.environ.get("VIB3_BENCH_ROUTER_SMEM_KB"):   # A/B: shared memory the gate/up kernel leaves to a co-resident router CTA
         from vic_b200.lib import lib as _l
-        _l().vib3_config_set(3, int(os.environ["VIB3_BENCH_SINGLE_KERNEL_MODE"]))
+        _l().vib3_config_set(3, int(os.environ["VIB3_BENCH_ROUTER_SMEM_KB"]))
     gen = torch.Generator(device=dev).manual_seed(SEED)
     xs = synth_activation(sh, gen, dev, torch.bfloat16, N_TOKENS)
     outs = torch.zeros(N_TOKENS, sh.hidden, dtype=torch.float32, device=dev)
@@ -353,12 +352,6 @@ def main():
         # share of the timed router launches that recomputed near-tied logits in sequential order
         router_redo_share = (int(dec.workspace[1].item()) - redo0) / float(3 + n_k * (reps + 1))
 
-        def single_launch(i):
-            kernels.moe_layer_int4_paged_fused(xs[i], dec.tables[i % PHYS_LAYERS], sh.num_experts,
-                                               dec.shared_tables[i % PHYS_LAYERS], ids_all[i], w_all[i], sh.top_k, 1.0,
-                                               dec.act, dec.out, False, sh.hidden, sh.intermediate, sh.pages_per_segment,
-                                               sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.workspace[2:], dec.status)
-        single_us = time_kernel(single_launch)
         variants = {}
         if os.environ.get("VIB3_BENCH_VARIANTS") == "1":   # A/B of library options in one process
             from vic_b200.lib import lib as _lib
@@ -424,7 +417,7 @@ def main():
                      "traffic": 152.43e6, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same shape (profiles/moe_gateup_down_kimi_batch1.md)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sh.hidden * 2, "d2h_bytes_per_step": sh.hidden * 4,
                 "ms_per_step": e2e_ms / K},
-        "kernel_us": {"router": router_us, "gate_up": k_us, "down": down_us, "gate_up_and_down_single_kernel": single_us,
+        "kernel_us": {"router": router_us, "gate_up": k_us, "down": down_us,
                       "note": "each kernel alone, back to back in a CUDA graph over rotating layers/tokens"},
         "variants_us": variants,
         "gpu_launches": dec.launches_per_layer * K,

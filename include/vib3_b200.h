@@ -147,20 +147,6 @@ int vib3_launch_moe_layer_int4_paged_var(const void* x, int x_dtype, const void*
                                          int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
                                          int rows_per_page_down, int group_size, int* status, void* stream,
                                          const int* num_active_dev);
-/* vib3_launch_moe_layer_int4_paged as ONE cooperative kernel (gate/up, a grid-wide barrier, down) where
- * the shape allows it — hidden and expert dimensions multiples of 256 whose 32-wide chunk counts per
- * warp lane are 1, 2, 4 or 7 (gate/up) and 1 or 2 (down), at most 9 slots — and as the two-kernel
- * sequence otherwise; the results are bit-identical either way.  grid_workspace: two 32-bit words of
- * device memory, zero before the first launch and used by one stream at a time; every completed
- * launch leaves them zero.  A launch that set VIB3_STATUS_TIMEOUT may leave them non-zero: clear
- * them before the next launch. */
-int vib3_launch_moe_layer_int4_paged_fused(const void* x, int x_dtype, const void* page_table, int num_experts,
-                                           const void* shared_pages, const unsigned short* expert_ids,
-                                           const float* expert_weights, int top_k, float shared_weight,
-                                           void* act_scratch, float* out, int out_accumulate, int hidden_dim,
-                                           int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
-                                           int rows_per_page_down, int group_size, int* status, void* stream,
-                                           unsigned int* grid_workspace);
 /* Keep, in order, the (expert, weight) pairs with expert_lo <= expert < expert_hi; *count_out = how
  * many.  ids_out / weights_out have top_k entries (unused ones are filled with expert_lo / 0). */
 int vib3_launch_select_local_experts(const unsigned short* ids, const float* weights, int top_k, int expert_lo,
@@ -187,8 +173,6 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
  * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
  * launch so that their prologue overlaps the previous kernel's tail (default 1).  key 2: router
  * load-batching variant (0 default: 14 loads per batch, 1: whole row in one batch, 2: two batches).
- * key 3: how vib3_launch_moe_layer_int4_paged_fused launches its single kernel (0: never, use the two
- * kernels; 1: cooperative launch; 2 default: cooperative + programmatic dependent launch).
  * Returns the previous value. */
 int vib3_config_set(int key, int value);
 

@@ -16,9 +16,7 @@ def _shapes():
     # several ragged pages per segment at small size: gate/up 3640+360 rows, down 932+92 rows
     mid = MoeShape("mid", 1024, 4000, 6, 3, 1, SCORING_SIGMOID, 2.5, True)
     noshared = MoeShape("noshared", 256, 512, 8, 2, 0, SCORING_SOFTMAX, 1.0, True)
-    # smallest shape the single-kernel layer takes: one 32-chunk batch per lane in both phases
-    one = MoeShape("one", 1024, 1024, 8, 3, 1, SCORING_SIGMOID, 2.5, True)
-    return {"tiny": tiny, "mid": mid, "one": one, "noshared": noshared, "kimi": KIMI, "mixtral": MIXTRAL}
+    return {"tiny": tiny, "mid": mid, "noshared": noshared, "kimi": KIMI, "mixtral": MIXTRAL}
 
 
 _cache = {}
@@ -86,46 +84,6 @@ def test_staged_kernels_equal_direct_kernels_bit_for_bit(cuda_dev, name, xdt):
             assert torch.equal(a, b)
     finally:
         lib().vib3_config_set(0, 1)
-
-
-@pytest.mark.parametrize("name,xdt", [("one", torch.float16), ("kimi", torch.bfloat16), ("kimi", torch.float32)])
-def test_single_kernel_layer_equals_two_kernels_bit_for_bit(cuda_dev, oracle, name, xdt):
-    """Gate/up, grid barrier and down in one cooperative kernel: same bits as the two staged kernels,
-    with and without programmatic dependent launch, and the barrier words are left zero."""
-    from vic_b200.lib import lib
-    from vic_b200.moe import MoeDecoder
-    from vic_b200.synth import synth_activation
-    model = _model(name, cuda_dev)
-    sh = model.shape
-    two = MoeDecoder(model, single_kernel=False)
-    one = MoeDecoder(model, single_kernel=True)
-    g = torch.Generator(device=cuda_dev).manual_seed(78)
-    xs = synth_activation(sh, g, cuda_dev, xdt, 4)
-    try:
-        for t in range(4):
-            lib().vib3_config_set(3, 1 + t % 2)
-            want = two.forward_layer(0, xs[t]).clone()
-            got = one.forward_layer(0, xs[t]).clone()
-            torch.cuda.synchronize()
-            assert int(one.status.item()) == 0 and int(two.status.item()) == 0
-            assert torch.equal(one.act, two.act)
-            assert torch.equal(got, want)
-            assert one.workspace.tolist()[2:] == [0, 0]
-        # accumulate form, several launches back to back without a host sync in between
-        acc = torch.zeros(sh.hidden, dtype=torch.float32, device=cuda_dev)
-        for _ in range(3):
-            one.forward_layer(0, xs[0], out=acc, accumulate=True)
-        base = two.forward_layer(0, xs[0])
-        torch.cuda.synchronize()
-        assert torch.equal(acc, base + base + base)
-        assert int(one.status.item()) == 0
-    finally:
-        lib().vib3_config_set(3, 2)
-    x32 = xs[0].float().cpu().numpy()
-    ids, w = one.routing()
-    ref = oracle.moe_layer(x32, oracle_experts(oracle, model, 0, list(zip(ids.tolist(), w.tolist()))), sh.hidden,
-                           sh.intermediate, oracle.SCALE_FP16, order="gpu")
-    assert_close(base.cpu().numpy(), ref, f"{name} single-kernel layer")
 
 
 def test_accumulate_into_residual(cuda_dev):

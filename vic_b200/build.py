@@ -15,7 +15,6 @@ SOURCES = [
     "page_kernels.cu",
     "moe_layer.cu",
     "moe_pipe.cu",
-    "moe_fused.cu",
     "moe_noalloc.cu",
     "router.cu",
     "host/page_pool.cpp",

@@ -20,7 +20,7 @@ struct MoeLayerArgs {
     const int* num_active_dev;     // optional device int: use only the first min(top_k, *num_active_dev) routed slots
     int num_experts;
     float shared_weight;
-    __half* act;                   // [slots][I] scratch
+    __half* act;                   // [slots][I] scratch, in act_slot() order
     float* out;                    // [H]
     int out_accumulate;            // 0: out = layer output; 1: out += layer output (residual add)
     int H, I, P;
@@ -40,6 +40,14 @@ __device__ __forceinline__ void flag(int* status, int bit) {
     if (status) atomicOr(status, bit);
 }
 
+// Position of slot s's activations in the scratch buffer: the shared expert (slot top_k in plan
+// order) is stored FIRST, so that where it lives does not depend on the routing — the gate/up kernel
+// can then work on the shared expert before the router has finished.  `a.top_k` is the active count.
+__device__ __forceinline__ int act_slot(const MoeLayerArgs& a, int s) {
+    const int nsh = a.shared_pages ? 1 : 0;
+    return s < a.top_k ? s + nsh : 0;
+}
+
 // Resolve the page-table block ([3][P] entries) of slot s: routed expert or the shared expert.
 __device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, int s) {
     if (s < a.top_k) {
@@ -56,14 +64,13 @@ __device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, in
 // direct-load kernels.
 int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st);
 int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st);
-// both phases in one cooperative kernel (moe_fused.cu); `grid_ws` = two zeroed words for its grid barrier
-int launch_layer_fused(const MoeLayerArgs& a, unsigned* grid_ws, cudaStream_t st);
-extern int g_fused_mode;
 int sm_count();
 
 // Run-time switch: 1 (default) = staged kernels where the shape allows, 0 = direct-load kernels only.
 extern int g_use_pipeline;
 // 1 (default) = staged kernels are launched with programmatic dependent launch.
 extern int g_use_pdl;
+// Shared memory (KB) the gate/up kernel leaves free on an SM so that a router CTA fits beside it.
+extern int g_router_cta_smem_kb;
 
 }  // namespace vib3

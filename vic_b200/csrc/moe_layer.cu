@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(256, 2) moe_gateup_kernel(MoeLayerArgs a) {
             // the reference rounds each projection to fp16 before silu_mul, and its result again
             const float g16 = __half2float(__float2half_rn(gsum));
             const float u16 = __half2float(__float2half_rn(usum));
-            a.act[(size_t)s * a.I + row] = __float2half_rn(silu_mul_f32(g16, u16));
+            a.act[(size_t)act_slot(a, s) * a.I + row] = __float2half_rn(silu_mul_f32(g16, u16));
         }
     }
 }
@@ -120,7 +120,8 @@ __global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
         tab[i] = e;
     }
     for (int s = threadIdx.x; s < slots; s += blockDim.x) wts[s] = s < a.top_k ? a.expert_weights[s] : a.shared_weight;
-    // act is [slots][I] and the staged layout is [slots][chunks]: one vector of slots * I values
+    // act is [slots][I] and the staged layout is [slots][chunks]: one vector of slots * I values,
+    // both in act_slot() order
     stage_activation<MATH>(acts, a.act, X_F16, slots * a.I, threadIdx.x, blockDim.x);
     __syncthreads();
 
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(384, 1) moe_down_kernel(MoeLayerArgs a) {
                 }
 #pragma unroll
                 for (int ss = 0; ss < SB; ++ss) {
-                    const MATH::XS* xs = acts + (size_t)min(s0 + ss, slots - 1) * nchunks * MATH::kStride;
+                    const MATH::XS* xs = acts + (size_t)act_slot(a, min(s0 + ss, slots - 1)) * nchunks * MATH::kStride;
 #pragma unroll
                     for (int i = 0; i < B; ++i) {
                         const int c = min(c0 + 32 * i, nchunks - 1);
@@ -247,7 +248,7 @@ static int launch_down(const MoeLayerArgs& a, cudaStream_t st) {
 
 using namespace vib3;
 
-static int moe_layer_dispatch(int phases, const int* num_active_dev, unsigned* fused_ws, const void* x, int x_dtype, const void* page_table, int num_experts,
+static int moe_layer_dispatch(int phases, const int* num_active_dev, const void* x, int x_dtype, const void* page_table, int num_experts,
                               const void* shared_pages, const unsigned short* expert_ids, const float* expert_weights,
                               int top_k, float shared_weight, void* act_scratch, float* out, int out_accumulate,
                               int hidden_dim, int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
@@ -276,10 +277,6 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, unsigned* f
     cudaStream_t st = (cudaStream_t)stream;
 
     int err = 0;
-    if (phases == 3 && fused_ws && g_use_pipeline) {
-        err = launch_layer_fused(a, fused_ws, st);
-        if (err != VIB3_ERR_UNSUPPORTED) return err;
-    }
     if ((phases & 1) && g_use_pipeline) {
         err = launch_gateup_pipelined(a, st);
         if (err == 0) phases &= ~1;
@@ -319,8 +316,7 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, unsigned* f
         rows_per_page_down, group_size, status, stream
 
 // key 0: staged (bulk-copy) kernels on/off; key 1: programmatic dependent launch of the staged
-// kernels on/off; key 2: router load-batching variant (0 default, 1, 2); key 3: single-kernel layer
-// (0 off, 1 cooperative launch, 2 cooperative + programmatic dependent launch).  Returns the previous
+// kernels on/off; key 2: router load-batching variant (0 default, 1, 2).  Returns the previous
 // value, or VIB3_ERR_UNSUPPORTED.
 extern "C" int vib3_router_config_set(int value);  // router.cu
 
@@ -337,31 +333,22 @@ extern "C" int vib3_config_set(int key, int value) {
     }
     if (key == 2) return vib3_router_config_set(value);
     if (key == 3) {
-        const int old = g_fused_mode;
-        if (value < 0 || value > 2) return VIB3_ERR_UNSUPPORTED;
-        g_fused_mode = value;
+        const int old = g_router_cta_smem_kb;
+        if (value < 0 || value > 160) return VIB3_ERR_UNSUPPORTED;
+        g_router_cta_smem_kb = value;
         return old;
     }
     return VIB3_ERR_UNSUPPORTED;
 }
 
-extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, nullptr, nullptr, VIB3_MOE_PASS); }
-extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, nullptr, nullptr, VIB3_MOE_PASS); }
-extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(2, nullptr, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(2, nullptr, VIB3_MOE_PASS); }
 // Same as vib3_launch_moe_layer_int4_paged, but only the first min(top_k, *num_active_dev) routed slots
 // are used (a device-side count, e.g. the experts of a token that are resident on this GPU).
 extern "C" int vib3_launch_moe_layer_int4_paged_var(VIB3_MOE_ARGS, const int* num_active_dev) {
     if (!num_active_dev) return VIB3_ERR_NULL;
-    return moe_layer_dispatch(3, num_active_dev, nullptr, VIB3_MOE_PASS);
-}
-
-// Same results as vib3_launch_moe_layer_int4_paged from ONE cooperative kernel for both phases where the
-// shape allows it (else the two-kernel path).  `grid_workspace`: two 32-bit words of device memory, zero
-// before the first launch, owned by one stream at a time; every launch leaves them zero.
-extern "C" int vib3_launch_moe_layer_int4_paged_fused(VIB3_MOE_ARGS, unsigned int* grid_workspace) {
-    if (!grid_workspace) return VIB3_ERR_NULL;
-    if ((uintptr_t)grid_workspace & 3) return VIB3_ERR_ALIGN;
-    return moe_layer_dispatch(3, nullptr, grid_workspace, VIB3_MOE_PASS);
+    return moe_layer_dispatch(3, num_active_dev, VIB3_MOE_PASS);
 }
 
 // Keep, in order, the (expert, weight) pairs whose expert lies in [expert_lo, expert_hi): the slots of

@@ -28,74 +28,94 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nchunks = a.H / kGroupSize;
-    const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);  // shared-memory layout; the slots used may be fewer
+    const int cap_k = a.top_k;                                  // routed slots the launch was sized for
+    const int max_slots = cap_k + (a.shared_pages ? 1 : 0);     // shared-memory layout; the slots used may be fewer
     const unsigned code_row = (unsigned)a.H / 2, scale_row = (unsigned)a.H / 16;
     const unsigned stage_bytes = 2 * kTileRows * (code_row + scale_row);
 
     unsigned char* stages = smem_raw;
     unsigned char* xs = stages + (size_t)nstages * stage_bytes;
-    PageEntry* tab = reinterpret_cast<PageEntry*>(xs + (size_t)nchunks * MATH::kStride);
+    PageEntry* tab = reinterpret_cast<PageEntry*>(xs + (size_t)nchunks * MATH::kStride);  // [max_slots][2][P], shared expert at cap_k
     uint64_t* full = reinterpret_cast<uint64_t*>(tab + max_slots * 2 * a.P);
     uint64_t* empty = full + kMaxStages;
-    volatile unsigned* landed = reinterpret_cast<volatile unsigned*>(empty + kMaxStages);
+    uint64_t* tab_ready = empty + kMaxStages;
+    volatile unsigned* landed = reinterpret_cast<volatile unsigned*>(tab_ready + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, kGroupWarps);
             landed[s] = 0;
         }
+        mbar_init(tab_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // the activation vector does not come from the router: quantise it before waiting for the router
+    // Neither the activation vector nor the shared expert's pages come from the router: quantise the
+    // vector and run the whole shared expert (pass 0) BEFORE waiting for the router.  This kernel leaves
+    // enough shared memory free for a router CTA on the same SM, so its CTAs become resident while the
+    // router is still running and the shared expert streams under the router's serial tail.  Between the
+    // passes nobody waits for the whole CTA: the producer warp alone waits for the router, builds the
+    // routed slots' page table and goes on issuing copies while the consumers finish pass 0.
     if (warp < kConsumerWarps) stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
-    pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
-    a.top_k = active_top_k(a);
-    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-    for (int i = tid; i < slots * 2 * a.P; i += blockDim.x) {
-        const int s = i / (2 * a.P), rem = i % (2 * a.P);
-        const PageEntry* pg = slot_pages(a, s);
-        PageEntry e{0, 0, 0, 0};
-        if (pg) e = pg[rem];
-        else if (rem == 0) flag(a.status, kStatusBadExpert);
-        tab[i] = e;
-    }
+    if (a.shared_pages)
+        for (int i = tid; i < 2 * a.P; i += blockDim.x) tab[cap_k * 2 * a.P + i] = a.shared_pages[i];
     __syncthreads();
 
-    int g0, g1;
-    cta_share(slots * a.I, g0, g1);
+    int n = 0;  // tiles of this CTA so far, over both passes (producer and consumers count alike)
 
     if (warp == kConsumerWarps) {
-        // ── producer warp: every lane walks the tiles; lane 0 arms the stage's barrier, lanes 0..3
-        // each issue one of the tile's four copies, so a tile costs one lane's worth of latency ──
-        TileWalk walk(g0, g1, a.I, a.rpp_gu);
-        Tile t;
-        int n = 0;
+        // ── producer warp: every lane walks the tiles; lane 0 arms the stage's barrier, lanes 0..3 each
+        // issue one of the tile's four copies, so a tile costs one lane's worth of latency ──
         bool ok = true;
-        while (walk.next(t)) {
-            const int st = n % nstages;
-            if (n >= nstages) ok = mbar_wait(empty + st, ((n / nstages) - 1) & 1);
-            if (!ok) break;
-            const PageEntry eu = tab[(t.slot * 2 + kSegUp) * a.P + t.page];
-            const PageEntry eg = tab[(t.slot * 2 + kSegGate) * a.P + t.page];
-            unsigned char* sb = stages + (size_t)st * stage_bytes;
-            const bool present = eu.ptr != 0 && eg.ptr != 0 && t.rin + t.nrows <= eu.row_count && t.rin + t.nrows <= eg.row_count;
-            const unsigned cb = t.nrows * code_row, sbz = t.nrows * scale_row;
-            if (lane == 0) {
-                if (present) mbar_expect_tx(full + st, 2 * (cb + sbz));
-                else mbar_arrive(full + st);  // absent page: the stage completes empty, consumers write zeros
+        for (int pass = a.shared_pages ? 0 : 1; pass < 2 && ok; ++pass) {
+            int g0, g1, slot_base;
+            if (pass == 0) {
+                cta_share(a.I, g0, g1);
+                slot_base = cap_k;
+            } else {
+                pdl_trigger();
+                pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
+                a.top_k = active_top_k(a);
+                for (int i = lane; i < a.top_k * 2 * a.P; i += 32) {
+                    const int s = i / (2 * a.P), rem = i % (2 * a.P);
+                    const PageEntry* pg = slot_pages(a, s);
+                    PageEntry e{0, 0, 0, 0};
+                    if (pg) e = pg[rem];
+                    else if (rem == 0) flag(a.status, kStatusBadExpert);
+                    tab[i] = e;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tab_ready);  // release: the consumers acquire the table through this barrier
+                cta_share(a.top_k * a.I, g0, g1);
+                slot_base = 0;
             }
-            __syncwarp();
-            if (present && lane < 4) {
-                const PageEntry e = (lane & 1) ? eu : eg;            // lanes 0,2: gate; 1,3: up
-                const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
-                if (lane < 2) bulk_load(sb + lane * kTileRows * code_row, base + (size_t)t.rin * code_row, cb, full + st);
-                else bulk_load(sb + 2 * kTileRows * code_row + (lane - 2) * kTileRows * scale_row,
-                               base + (size_t)e.row_count * code_row + (size_t)t.rin * scale_row, sbz, full + st);
+            TileWalk walk(g0, g1, a.I, a.rpp_gu);
+            Tile t;
+            while (walk.next(t)) {
+                const int st = n % nstages;
+                if (n >= nstages) ok = mbar_wait(empty + st, ((n / nstages) - 1) & 1);
+                if (!ok) break;
+                const int ts = slot_base + t.slot;
+                const PageEntry eu = tab[(ts * 2 + kSegUp) * a.P + t.page];
+                const PageEntry eg = tab[(ts * 2 + kSegGate) * a.P + t.page];
+                unsigned char* sb = stages + (size_t)st * stage_bytes;
+                const bool present = eu.ptr != 0 && eg.ptr != 0 && t.rin + t.nrows <= eu.row_count && t.rin + t.nrows <= eg.row_count;
+                const unsigned cb = t.nrows * code_row, sbz = t.nrows * scale_row;
+                if (lane == 0) {
+                    if (present) mbar_expect_tx(full + st, 2 * (cb + sbz));
+                    else mbar_arrive(full + st);  // absent page: the stage completes empty, consumers write zeros
+                }
+                __syncwarp();
+                if (present && lane < 4) {
+                    const PageEntry e = (lane & 1) ? eu : eg;            // lanes 0,2: gate; 1,3: up
+                    const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
+                    if (lane < 2) bulk_load(sb + lane * kTileRows * code_row, base + (size_t)t.rin * code_row, cb, full + st);
+                    else bulk_load(sb + 2 * kTileRows * code_row + (lane - 2) * kTileRows * scale_row,
+                                   base + (size_t)e.row_count * code_row + (size_t)t.rin * scale_row, sbz, full + st);
+                }
+                ++n;
             }
-            ++n;
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
         // drain: every issued stage must have landed before the CTA's shared memory goes away
@@ -110,66 +130,87 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     Ring ring{full, empty, landed, nstages};
     const uint32_t stages_addr = smem_u32(stages);
     const uint32_t x_addr = smem_u32(xs) + lane * MATH::kStride;
-    TileWalk walk(g0, g1, a.I, a.rpp_gu);
-    Tile t;
-    int n = 0;
-    while (walk.next(t)) {
-        if (n % kGroups != group) { ++n; continue; }
-        const int st = n % nstages;
-        if (!ring.wait_full(n, wi == 0 && lane == 0)) {
-            if (lane == 0) flag(a.status, kStatusTimeout);
-            return;
+    for (int pass = a.shared_pages ? 0 : 1; pass < 2; ++pass) {
+        int g0, g1, slot_base;
+        if (pass == 0) {
+            cta_share(a.I, g0, g1);
+            slot_base = cap_k;
+        } else {
+            // From here on this thread writes nothing that a kernel launched after this one may touch
+            // before its own dependency wait: the shared expert's rows (pass 0) are done.
+            pdl_trigger();
+            pdl_wait();
+            a.top_k = active_top_k(a);
+            if (!mbar_wait(tab_ready, 0)) {
+                if (lane == 0) flag(a.status, kStatusTimeout);
+                return;
+            }
+            cta_share(a.top_k * a.I, g0, g1);
+            slot_base = 0;
         }
-        const int p0 = wi * kPairsPerWarp;  // this warp's row pairs: p0 and p0 + 1 of the tile
-        if (p0 < t.nrows) {
-            const PageEntry eu = tab[(t.slot * 2 + kSegUp) * a.P + t.page];
-            const PageEntry eg = tab[(t.slot * 2 + kSegGate) * a.P + t.page];
-            const bool present = eu.ptr != 0 && eg.ptr != 0 && t.rin + t.nrows <= eu.row_count && t.rin + t.nrows <= eg.row_count;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};  // gate p0, up p0, gate p0+1, up p0+1
-            if (present) {
-                const uint32_t sb = stages_addr + st * stage_bytes;
-                const uint32_t g_addr = sb + p0 * code_row + lane * 16;
-                const uint32_t u_addr = g_addr + kTileRows * code_row;
-                const uint32_t gs_addr = sb + 2 * kTileRows * code_row + p0 * scale_row + lane * 2;
-                const uint32_t us_addr = gs_addr + kTileRows * scale_row;
-                if (NCH > 0) {
+        TileWalk walk(g0, g1, a.I, a.rpp_gu);
+        Tile t;
+        while (walk.next(t)) {
+            if (n % kGroups != group) { ++n; continue; }
+            const int st = n % nstages;
+            if (!ring.wait_full(n, wi == 0 && lane == 0)) {
+                if (lane == 0) flag(a.status, kStatusTimeout);
+                return;
+            }
+            const int p0 = wi * kPairsPerWarp;  // this warp's row pairs: p0 and p0 + 1 of the tile
+            if (p0 < t.nrows) {
+                const int ts = slot_base + t.slot;
+                const PageEntry eu = tab[(ts * 2 + kSegUp) * a.P + t.page];
+                const PageEntry eg = tab[(ts * 2 + kSegGate) * a.P + t.page];
+                const bool present = eu.ptr != 0 && eg.ptr != 0 && t.rin + t.nrows <= eu.row_count && t.rin + t.nrows <= eg.row_count;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};  // gate p0, up p0, gate p0+1, up p0+1
+                if (present) {
+                    const uint32_t sb = stages_addr + st * stage_bytes;
+                    const uint32_t g_addr = sb + p0 * code_row + lane * 16;
+                    const uint32_t u_addr = g_addr + kTileRows * code_row;
+                    const uint32_t gs_addr = sb + 2 * kTileRows * code_row + p0 * scale_row + lane * 2;
+                    const uint32_t us_addr = gs_addr + kTileRows * scale_row;
+                    if (NCH > 0) {
 #pragma unroll
-                    for (int i = 0; i < NCH; ++i) {
-                        const uint4 q[4] = {lds128(g_addr + i * 512), lds128(u_addr + i * 512),
-                                            lds128(g_addr + code_row + i * 512), lds128(u_addr + code_row + i * 512)};
-                        const float s4[4] = {scale_to_f32(lds16(gs_addr + i * 64)), scale_to_f32(lds16(us_addr + i * 64)),
-                                             scale_to_f32(lds16(gs_addr + scale_row + i * 64)), scale_to_f32(lds16(us_addr + scale_row + i * 64))};
-                        MATH::template chunk_s<4>(q, s4, x_addr + i * (32 * MATH::kStride), acc);
+                        for (int i = 0; i < NCH; ++i) {
+                            const uint4 q[4] = {lds128(g_addr + i * 512), lds128(u_addr + i * 512),
+                                                lds128(g_addr + code_row + i * 512), lds128(u_addr + code_row + i * 512)};
+                            const float s4[4] = {scale_to_f32(lds16(gs_addr + i * 64)), scale_to_f32(lds16(us_addr + i * 64)),
+                                                 scale_to_f32(lds16(gs_addr + scale_row + i * 64)), scale_to_f32(lds16(us_addr + scale_row + i * 64))};
+                            MATH::template chunk_s<4>(q, s4, x_addr + i * (32 * MATH::kStride), acc);
+                        }
+                    } else {
+                        for (int c = lane; c < nchunks; c += 32) {
+                            const int o = c - lane;
+                            const uint4 q[4] = {lds128(g_addr + o * 16), lds128(u_addr + o * 16),
+                                                lds128(g_addr + code_row + o * 16), lds128(u_addr + code_row + o * 16)};
+                            const float s4[4] = {scale_to_f32(lds16(gs_addr + o * 2)), scale_to_f32(lds16(us_addr + o * 2)),
+                                                 scale_to_f32(lds16(gs_addr + scale_row + o * 2)), scale_to_f32(lds16(us_addr + scale_row + o * 2))};
+                            MATH::template chunk_s<4>(q, s4, x_addr + o * MATH::kStride, acc);
+                        }
                     }
-                } else {
-                    for (int c = lane; c < nchunks; c += 32) {
-                        const int o = c - lane;
-                        const uint4 q[4] = {lds128(g_addr + o * 16), lds128(u_addr + o * 16),
-                                            lds128(g_addr + code_row + o * 16), lds128(u_addr + code_row + o * 16)};
-                        const float s4[4] = {scale_to_f32(lds16(gs_addr + o * 2)), scale_to_f32(lds16(us_addr + o * 2)),
-                                             scale_to_f32(lds16(gs_addr + scale_row + o * 2)), scale_to_f32(lds16(us_addr + scale_row + o * 2))};
-                        MATH::template chunk_s<4>(q, s4, x_addr + o * MATH::kStride, acc);
+                } else if (lane == 0) {
+                    flag(a.status, kStatusMissingPage);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = warp_sum(acc[k]);
+                if (lane == 0) {
+                    // pass 0 writes the shared expert's rows at the front of the scratch buffer (act_slot order)
+                    __half* dst = a.act + (size_t)(pass == 0 ? 0 : t.slot + (a.shared_pages ? 1 : 0)) * a.I + t.row + p0;
+#pragma unroll
+                    for (int k = 0; k < kPairsPerWarp; ++k) {
+                        if (p0 + k < t.nrows) {
+                            const float g16 = __half2float(__float2half_rn(acc[2 * k]));
+                            const float u16 = __half2float(__float2half_rn(acc[2 * k + 1]));
+                            dst[k] = __float2half_rn(silu_mul_f32(g16, u16));
+                        }
                     }
                 }
-            } else if (lane == 0) {
-                flag(a.status, kStatusMissingPage);
             }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) acc[k] = warp_sum(acc[k]);
-            if (lane == 0) {
-#pragma unroll
-                for (int k = 0; k < kPairsPerWarp; ++k) {
-                    if (p0 + k < t.nrows) {
-                        const float g16 = __half2float(__float2half_rn(acc[2 * k]));
-                        const float u16 = __half2float(__float2half_rn(acc[2 * k + 1]));
-                        a.act[(size_t)t.slot * a.I + t.row + p0 + k] = __float2half_rn(silu_mul_f32(g16, u16));
-                    }
-                }
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + st);
+            ++n;
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + st);
-        ++n;
     }
 }
 
@@ -180,14 +221,20 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
 // the activations stay in REGISTERS: two warps per expert slot; each lane quantises the two
 // activation chunks it is responsible for (the gate/up kernel's fp16 output) once, straight from
 // global memory, and keeps them for the whole kernel.  All consumer warps work on the same tile
-// (4 output rows x all slots; warp (slot, h) takes rows h and h+2), so every ring stage ahead of it
-// is look-ahead.  Per-row results y[row][slot] (rounded to fp16 as the reference's down projection)
+// (6 output rows x all slots; warp (slot, h) takes rows h, h+2, h+4), so every ring stage ahead of it
+// is look-ahead.  Taller tiles mean larger bulk copies (6 KB of codes and 768 B of scales per slot):
+// the copy engine's rate drops with copy size, and with 4-row tiles the ring itself, not the
+// arithmetic, limited the kernel.  Per-row results y[row][slot] (rounded to fp16 as the reference's down projection)
 // go to a small ring in shared memory; a separate combiner warp adds each row in plan order and
 // writes the output.  The hand-over is by mbarriers (y-full: one arrival per consumer warp, y-empty:
 // one arrival by the combiner), so consumer warps never wait for one another: they drift apart by
 // up to the depth of the rings, and loads, integer math and shuffles of different warps overlap.
-// stage layout: per slot [codes R*I/2][scales R*I/16], R = 4.
-constexpr int kDownRows = 4;
+// stage layout: per slot [codes R*I/2][scales R*I/16], R = kDownRows.
+#ifndef VIB3_DOWN_ROWS
+#define VIB3_DOWN_ROWS 6
+#endif
+constexpr int kDownRows = VIB3_DOWN_ROWS;  // measured (Kimi shape, 9 slots): 4 rows 20.7 us, 6 rows 17.3 us, 8 rows 18.5 us
+constexpr int kDownRowsPerWarp = (kDownRows + 1) / 2;
 constexpr int kDownWarpsPerSlot = 2;
 constexpr int kDownYStages = 4;
 constexpr int kDownMaxThreads = 640;  // 18 consumer warps for 9 slots + combiner + producer
@@ -218,7 +265,10 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     float* ybuf = wts + kMaxSlots;  // [y stage][row][kMaxSlots]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    pdl_trigger();
+    // The next kernel in the stream may overwrite the activation scratch before its own dependency
+    // wait (the gate/up kernel does, for the shared expert).  Warps that never read the scratch let it
+    // go at once; consumer warps only after they have copied their chunks into registers.
+    if (warp >= cwarps) pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
@@ -326,7 +376,11 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     int sq8[NCH];
 #pragma unroll
     for (int i = 0; i < NCH; ++i)
-        MATH::quantize_chunk(a.act + (size_t)s * a.I + (size_t)(lane + 32 * i) * 32, xv[i], sx[i], sq8[i]);
+        MATH::quantize_chunk(a.act + (size_t)act_slot(a, s) * a.I + (size_t)(lane + 32 * i) * 32, xv[i], sx[i], sq8[i]);
+    // the scratch has been read: the sums below depend on every loaded value, so the loads have returned
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) asm volatile("" ::"r"(sq8[i]));
+    pdl_trigger();
 
     const uint32_t stages_addr = smem_u32(stages);
     const uint32_t code_base = s * slot_bytes + lane * 16;
@@ -343,9 +397,9 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         const PageEntry e = tab[s * a.P + t.page];
         const bool present = e.ptr != 0 && t.rin + t.nrows <= e.row_count;
         const uint32_t sb = stages_addr + st * stage_bytes;
-        float y[kDownRows / kDownWarpsPerSlot];
+        float y[kDownRowsPerWarp];
 #pragma unroll
-        for (int j = 0; j < kDownRows / kDownWarpsPerSlot; ++j) {
+        for (int j = 0; j < kDownRowsPerWarp; ++j) {
             const int r = h + j * kDownWarpsPerSlot;
             float acc = 0.f;
             if (r < t.nrows && present) {
@@ -361,7 +415,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + st);  // this warp has read everything it needs from the stage
 #pragma unroll
-        for (int j = 0; j < kDownRows / kDownWarpsPerSlot; ++j) y[j] = warp_sum(y[j]);
+        for (int j = 0; j < kDownRowsPerWarp; ++j) y[j] = warp_sum(y[j]);
         if (!present && h == 0 && lane == 0) flag(a.status, kStatusMissingPage);
         const int ys = n % kDownYStages;
         if (n >= kDownYStages && !mbar_wait(yempty + ys, ((n / kDownYStages) - 1) & 1)) {
@@ -372,8 +426,8 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             float* yb = ybuf + ys * (kDownRows * kMaxSlots);
             // fp16 rounding of the down projection (its output buffer is fp16 in the reference)
 #pragma unroll
-            for (int j = 0; j < kDownRows / kDownWarpsPerSlot; ++j)
-                yb[(h + j * kDownWarpsPerSlot) * kMaxSlots + s] = __half2float(__float2half_rn(y[j]));
+            for (int j = 0; j < kDownRowsPerWarp; ++j)
+                if (h + j * kDownWarpsPerSlot < kDownRows) yb[(h + j * kDownWarpsPerSlot) * kMaxSlots + s] = __half2float(__float2half_rn(y[j]));
             mbar_arrive(yfull + ys);
         }
         ++n;
@@ -381,6 +435,9 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
 }
 
 // ── host side ──────────────────────────────────────────────────────────────────────────────
+
+// static shared memory of a router CTA plus the per-CTA reservation, rounded up (vib3_config_set key 3, in KB)
+int g_router_cta_smem_kb = 46;
 
 static bool pipe_shape_ok(const MoeLayerArgs& a) {
     return a.H % 256 == 0 && a.I % 256 == 0;
@@ -428,8 +485,11 @@ int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const size_t stage_bytes = 2 * kTileRows * ((size_t)a.H / 2 + (size_t)a.H / 16);
     const size_t fixed = (size_t)(a.H / kGroupSize) * MathQ16::kStride + (size_t)slots * 2 * a.P * sizeof(PageEntry) +
-                         2 * kMaxStages * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + 128;
-    const int nstages = pick_stages(fixed, stage_bytes, 3);
+                         (2 * kMaxStages + 1) * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + 128;
+    // leave kRouterCtaSmem of the SM's shared memory to a router CTA, so that this kernel's CTAs become
+    // resident while the router still runs (see the kernel's first pass)
+    int nstages = pick_stages(fixed + (size_t)g_router_cta_smem_kb * 1024, stage_bytes, 3);
+    if (nstages == 0) nstages = pick_stages(fixed, stage_bytes, 3);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
     const size_t smem = fixed + (size_t)nstages * stage_bytes;
     const int total = slots * a.I;

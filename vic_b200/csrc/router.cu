@@ -389,8 +389,13 @@ int g_router_variant = 0;
 
 static int launch_router(const RouterArgs& a, cudaStream_t st) {
     const int grid = (a.E + 1) / 2;
+    // The default variant asks for the largest shared-memory carve-out: the gate/up kernel that follows
+    // sizes itself to fit beside one router CTA, which only works if both want the same SM configuration.
 #define VIB3_ROUTER_CASE(XD, WD)                                                      \
     if (a.x_dtype == XD && a.w_dtype == WD) {                                         \
+        static const cudaError_t carve = cudaFuncSetAttribute(router_kernel<14, XD, WD, false>,    \
+            cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);  \
+        (void)carve;                                                                  \
         if (g_router_variant == 0) router_kernel<14, XD, WD, false><<<grid, 256, 0, st>>>(a);      \
         else if (g_router_variant == 2) router_kernel<28, XD, WD, true><<<grid, 256, 0, st>>>(a);  \
         else if (g_router_variant == 3) router_kernel<56, XD, WD, false><<<grid, 256, 0, st>>>(a); \

@@ -158,19 +158,6 @@ def moe_layer_int4_paged_var(x: torch.Tensor, page_table: int, num_experts: int,
         _ptr(num_active_dev)))
 
 
-def moe_layer_int4_paged_fused(x: torch.Tensor, page_table: int, num_experts: int, shared_pages: int, expert_ids,
-                               expert_weights, top_k: int, shared_weight: float, act_scratch, out, out_accumulate: bool,
-                               hidden_dim: int, expert_hidden_dim: int, pages_per_segment: int,
-                               rows_per_page_gate_up: int, rows_per_page_down: int, grid_workspace, status=None,
-                               stream: Optional[int] = None) -> None:
-    """The sublayer as one cooperative kernel where the shape allows (else two kernels); same bits."""
-    check("moe_layer_int4_paged_fused", lib().vib3_launch_moe_layer_int4_paged_fused(
-        _ptr(x), x_dtype_code(x), page_table, num_experts, shared_pages or 0, _ptr(expert_ids), _ptr(expert_weights), top_k,
-        shared_weight, _ptr(act_scratch), _ptr(out), int(out_accumulate), hidden_dim, expert_hidden_dim,
-        pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status), _stream(stream),
-        _ptr(grid_workspace)))
-
-
 def select_local_experts(ids, weights, top_k: int, expert_lo: int, expert_hi: int, ids_out, weights_out, count_out,
                          stream: Optional[int] = None) -> None:
     check("select_local_experts", lib().vib3_launch_select_local_experts(

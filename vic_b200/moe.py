@@ -21,26 +21,21 @@ class MoeDecoder:
     """Device buffers and launch sequence for batch-1 decode over a SyntheticMoe (or any pool with
     the same page-table layout)."""
 
-    def __init__(self, model: SyntheticMoe, exact_order: bool = True, single_kernel: bool = False):
+    def __init__(self, model: SyntheticMoe, exact_order: bool = True):
         self.model = model
-        self.single_kernel = single_kernel  # gate/up and down in one cooperative kernel where the shape allows
         sh = model.shape
         dev = model.router_w.device
         self.exact_order = exact_order
         self.scores = torch.zeros(3 * sh.num_experts, dtype=torch.float32, device=dev)
         self.ids = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
         self.weights = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
-        self.workspace = torch.zeros(4, dtype=torch.int32, device=dev)  # words 0-1: router, 2-3: grid barrier
+        self.workspace = torch.zeros(4, dtype=torch.int32, device=dev)
         self.act = torch.zeros((sh.top_k + 1) * sh.intermediate, dtype=torch.float16, device=dev)
         self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.tables = [model.page_table(l) for l in range(model.n_layers)]
         self.shared_tables = [model.shared_table(l) for l in range(model.n_layers)]
-        # the single-kernel layer exists for 32-chunk counts per lane of 1, 2, 4 or 7 (gate/up) and 1 or 2 (down)
-        slots = sh.top_k + (1 if sh.shared_experts else 0)
-        self.single_kernel_shape = (sh.hidden % 1024 == 0 and sh.hidden // 1024 in (1, 2, 4, 7)
-                                    and sh.intermediate in (1024, 2048) and slots <= 9)
-        self.launches_per_layer = 2 if (single_kernel and self.single_kernel_shape) else 3
+        self.launches_per_layer = 3
 
     def route(self, layer: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
               logit_offset: Optional[torch.Tensor] = None) -> None:
@@ -53,13 +48,6 @@ class MoeDecoder:
                 phase: int = 3) -> torch.Tensor:
         sh = self.model.shape
         out = self.out if out is None else out
-        if phase == 3 and self.single_kernel:
-            kernels.moe_layer_int4_paged_fused(x, self.tables[layer], sh.num_experts, self.shared_tables[layer],
-                                               self.ids, self.weights, sh.top_k, 1.0, self.act, out, accumulate,
-                                               sh.hidden, sh.intermediate, sh.pages_per_segment,
-                                               sh.gate_up.rows_per_page, sh.down.rows_per_page, self.workspace[2:],
-                                               self.status)
-            return out
         kernels.moe_layer_int4_paged(x, self.tables[layer], sh.num_experts, self.shared_tables[layer], self.ids,
                                      self.weights, sh.top_k, 1.0, self.act, out, accumulate, sh.hidden,
                                      sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page,
