@@ -86,6 +86,25 @@ def test_staged_kernels_equal_direct_kernels_bit_for_bit(cuda_dev, name, xdt):
         lib().vib3_config_set(0, 1)
 
 
+def test_host_to_host_step_equals_device_step(cuda_dev):
+    """forward_host (one CUDA graph: copy in, three launches, copy out) returns the same bits as the
+    device-resident call, for pinned and ordinary host tensors, several tokens in a row."""
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import synth_activation
+    model = _model("mid", cuda_dev)
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(6)
+    xs = synth_activation(model.shape, g, cuda_dev, torch.bfloat16, 4)
+    for t in range(4):
+        want = dec.forward_layer(0, xs[t]).clone().cpu()
+        xh = xs[t].cpu()
+        if t % 2:
+            xh = xh.pin_memory()
+        got = dec.forward_host(0, xh)
+        assert got.is_pinned() and torch.equal(got, want)
+    assert int(dec.status.item()) == 0
+
+
 def test_accumulate_into_residual(cuda_dev):
     from vic_b200.moe import MoeDecoder
     from vic_b200.synth import synth_activation

@@ -20,8 +20,8 @@ def _ptr(t) -> int:
         return 0
     if isinstance(t, int):
         return t
-    if not t.is_cuda:
-        raise ValueError("device tensor expected")
+    if not t.is_cuda and not t.is_pinned():
+        raise ValueError("device tensor (or pinned, device-addressable host tensor) expected")
     return t.data_ptr()
 
 

@@ -61,6 +61,47 @@ class MoeDecoder:
         self.route(layer, x, bias, logit_offset)
         return self.experts(layer, x, out, accumulate)
 
+    def forward_host(self, layer: int, x_host: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """One token from and to HOST memory: x_host [H] (any of the activation dtypes, ordinary or pinned
+        memory) -> pinned fp32 [H] (valid until the next call).  The copy in and the three launches are one CUDA graph per (layer, dtype), built on first use — the first call for a
+        combination must therefore not happen inside somebody else's stream capture — so a step costs
+        one graph launch and one stream synchronisation on the host.  The copy out is not a separate
+        node: the last kernel writes its 4 H bytes into the pinned buffer directly."""
+        key = (layer, x_host.dtype)
+        stream = stream or torch.cuda.current_stream()
+        if not hasattr(self, "_host_graphs"):
+            self._host_graphs = {}
+        entry = self._host_graphs.get(key)
+        if entry is None:
+            sh = self.model.shape
+            dev = self.out.device
+            x_pin = torch.zeros(sh.hidden, dtype=x_host.dtype).pin_memory()
+            out_pin = torch.zeros(sh.hidden, dtype=torch.float32).pin_memory()
+            x_dev = torch.zeros(sh.hidden, dtype=x_host.dtype, device=dev)
+
+            def body():
+                x_dev.copy_(x_pin, non_blocking=True)
+                # the down kernel writes every output row once: it stores straight into the pinned host
+                # buffer (device-addressable under unified addressing), which saves the copy-out node
+                self.forward_layer(layer, x_dev, out=out_pin)
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                body()  # warm-up outside capture: one-time kernel attributes and lazy loading
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    body()
+            stream.wait_stream(side)
+            entry = (graph, x_pin, out_pin)
+            self._host_graphs[key] = entry
+        graph, x_pin, out_pin = entry
+        x_pin.copy_(x_host)          # host-to-host, a few microseconds for one activation vector
+        with torch.cuda.stream(stream):
+            graph.replay()
+        stream.synchronize()
+        return out_pin
+
     def forward_tokens(self, layer: int, xs: torch.Tensor, outs: Optional[torch.Tensor] = None,
                        logit_offset: Optional[torch.Tensor] = None, routing_out=None) -> torch.Tensor:
         """Multi-token decode, xs [T, H] -> [T, H] fp32: every token takes the batch-1 path in turn
