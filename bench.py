@@ -12,8 +12,9 @@ and every step has its own token, so no weight byte is re-read before 4 x 234 MB
 traffic went through the 126 MB L2.  Data is seeded synthetic (no checkpoint, no dataset).
 
 Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM (CUDA-graph
-replay, CUDA events); `e2e` = the same through host buffers (pinned H2D of the token, D2H of the
-fp32 layer output, every step); `roofline` = the dominant kernel (gate/up) timed alone with CUDA
+replay, CUDA events); `e2e` = the same through host buffers (MoeDecoder.forward_host: pinned H2D of
+the token and the three launches as one CUDA graph, the fp32 layer output written by the last kernel
+straight into pinned host memory, one stream synchronisation, every step); `roofline` = the dominant kernel (gate/up) timed alone with CUDA
 events against the measured HBM copy bandwidth; `cpu_baseline` = the CPU restatement of the
 reference's kernels (oracle/) on this host's cores over a bounded sample.
 """
@@ -410,7 +411,7 @@ def main():
         "roofline": {"bound": "hbm", "kernel": "moe_gateup_pipe_kernel (gate/up + SiLU, 9 experts)", "achieved": achieved,
                      "peak": peak, "peak_source": f"of {peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst)", "unit": "GB/s",
                      "frac": achieved / peak, "bytes_per_launch": b_gu, "us_per_launch": k_us,
-                     "traffic": 152.43e6, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same shape (profiles/moe_gateup_down_kimi_batch1.md)"},
+                     "traffic": 153.46e6, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same shape (profiles/moe_gateup_down_kimi_batch1.md)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sh.hidden * 2, "d2h_bytes_per_step": sh.hidden * 4,
                 "ms_per_step": e2e_ms / K},
         "kernel_us": {"router": router_us, "gate_up": k_us, "down": down_us,
