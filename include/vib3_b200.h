@@ -147,6 +147,32 @@ int vib3_launch_moe_layer_int4_paged_var(const void* x, int x_dtype, const void*
                                          int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
                                          int rows_per_page_down, int group_size, int* status, void* stream,
                                          const int* num_active_dev);
+/* Grouped form for expert parallelism: one launch pair for the (token, expert) pairs of SEVERAL tokens
+ * that this GPU owns.  pair_experts / pair_weights / pair_tokens: device lists in ascending token order
+ * (as vib3_launch_select_local_pairs writes them), *num_pairs_dev their length; this launch takes the
+ * pairs [pair_begin, pair_begin + pair_capacity) of them (pair_capacity <= 16; launches with
+ * pair_begin > 0 normally pass out_accumulate = 1 and no shared expert).  x: n_tokens activation vectors
+ * x_stride_bytes apart (16-byte multiples); out: n_tokens fp32 rows out_stride floats apart, every
+ * token's row is written (zero where the token has no pair here).  The shared expert, if given, belongs
+ * to token shared_token.  act_scratch: (pair_capacity + 1) * expert_hidden_dim fp16 values.  Only for
+ * shapes the staged kernels take (hidden and expert dimensions multiples of 256, expert dimension 1024
+ * or 2048); VIB3_ERR_UNSUPPORTED otherwise. */
+int vib3_launch_moe_layer_int4_paged_grouped(const void* x, int x_dtype, int x_stride_bytes, int n_tokens,
+                                             const void* page_table, int num_experts, const void* shared_pages,
+                                             int shared_token, const unsigned short* pair_experts,
+                                             const float* pair_weights, const unsigned short* pair_tokens,
+                                             int pair_capacity, int pair_begin, const int* num_pairs_dev,
+                                             float shared_weight, void* act_scratch, float* out, int out_stride,
+                                             int out_accumulate, int hidden_dim, int expert_hidden_dim,
+                                             int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down,
+                                             int group_size, int* status, void* stream);
+/* The (token, expert, weight) triples, token-major, whose expert lies in [expert_lo, expert_hi).
+ * ids / weights: n_tokens rows of top_k entries, row strides in bytes.  The lists hold `capacity`
+ * entries; *count_out receives the number found even if larger. */
+int vib3_launch_select_local_pairs(const unsigned short* ids, int ids_stride_bytes, const float* weights,
+                                   int weights_stride_bytes, int n_tokens, int top_k, int expert_lo, int expert_hi,
+                                   unsigned short* pair_experts, float* pair_weights, unsigned short* pair_tokens,
+                                   int capacity, int* count_out, void* stream);
 /* Keep, in order, the (expert, weight) pairs with expert_lo <= expert < expert_hi; *count_out = how
  * many.  ids_out / weights_out have top_k entries (unused ones are filled with expert_lo / 0). */
 int vib3_launch_select_local_experts(const unsigned short* ids, const float* weights, int top_k, int expert_lo,
@@ -173,7 +199,8 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
  * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
  * launch so that their prologue overlaps the previous kernel's tail (default 1).  key 2: router
  * load-batching variant (0 default: 14 loads per batch, 1: whole row in one batch, 2: two batches).
- * Returns the previous value. */
+ * key 3: KB of shared memory per SM that the gate/up kernel leaves to a co-resident router CTA
+ * (default 46; 0: largest ring, no overlap with the router).  Returns the previous value. */
 int vib3_config_set(int key, int value);
 
 /* ── Host side: VRAM page pool and query planner (C view of the C++ classes) ────────────── */

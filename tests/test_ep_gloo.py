@@ -43,9 +43,10 @@ def _worker(rank, world, port, ret):
         ws_t = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.float32)
         ids_t[:sh.top_k] = torch.from_numpy(ids.astype(np.int16))
         ws_t[:sh.top_k] = torch.from_numpy(ws)
-        words = H // 2 + 2 * MAX_ACTIVE_EXPERTS
-        send = torch.zeros(words, dtype=torch.int32)
-        recv = torch.zeros(world, words, dtype=torch.int32)
+        ids_off, w_off, nbytes = ep.message_layout(H)
+        assert nbytes % 16 == 0 and ids_off == 2 * H and w_off == ids_off + 2 * MAX_ACTIVE_EXPERTS
+        send = torch.zeros(nbytes, dtype=torch.uint8)
+        recv = torch.zeros(world, nbytes, dtype=torch.uint8)
         ep.pack_message(send, x, ids_t, ws_t)
         ep.gather_messages(send, recv, world)
         xs, gids, gws = ep.unpack_messages(recv, H)

@@ -43,7 +43,7 @@ def _worker(rank, world, port, ret):
             x = torch.randn(sh.hidden, generator=g, device=dev).to(torch.bfloat16)
             layer = step % 2
             out = epd.step(layer, x).clone()
-            ids_ep = epd.dec.routing()[0].tolist()
+            ids_ep = epd.routing()[0].tolist()
             want = ref.forward_layer(layer, x).clone()
             torch.cuda.synchronize()
             if ids_ep != ref.routing()[0].tolist():

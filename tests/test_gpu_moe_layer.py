@@ -260,6 +260,69 @@ def test_device_side_slot_count_and_local_selection(cuda_dev, oracle):
             assert_close(out_var.cpu().numpy(), want, f"{n} routed slot(s), shared={shared}")
 
 
+@pytest.mark.parametrize("name,T,lo_hi", [("grp", 3, (4, 12)), ("grp", 6, (0, 16)), ("kimi", 4, (96, 288)), ("kimi", 8, (0, 48))])
+def test_grouped_pairs_equal_per_token_launches_bit_for_bit(cuda_dev, name, T, lo_hi):
+    """The grouped launch (pairs of several tokens, as an expert-parallel rank sees them) writes, for
+    every token, the same bits as that token's own launch over its local experts; also with more than 9
+    slots (one warp per slot in the down kernel) and more than 16 pairs (a second, accumulating launch)."""
+    from vic_b200 import kernels
+    from vic_b200.core_types import KIMI, SCORING_SIGMOID, X_BF16, MoeShape
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import build_synthetic_moe, synth_activation
+    if name == "grp":
+        sh = MoeShape("grp", 1024, 1024, 16, 4, 1, SCORING_SIGMOID, 2.5, True)
+        _cache.clear()
+        model = build_synthetic_moe(sh, 1, cuda_dev, seed=21, slot_seed=5)
+    else:
+        model = _model("kimi", cuda_dev)
+        sh = model.shape
+    dec = MoeDecoder(model)
+    lo, hi = lo_hi
+    g = torch.Generator(device=cuda_dev).manual_seed(90 + T)
+    xs = synth_activation(sh, g, cuda_dev, torch.bfloat16, T)          # [T, H] contiguous: stride 2H bytes
+    ids_all = torch.zeros(T, 16, dtype=torch.int16, device=cuda_dev)
+    w_all = torch.zeros(T, 16, dtype=torch.float32, device=cuda_dev)
+    for t in range(T):
+        dec.route(0, xs[t])
+        ids_all[t].copy_(dec.ids)
+        w_all[t].copy_(dec.weights)
+    shared_token = T // 2
+    # per-token launches over the local experts
+    want = torch.zeros(T, sh.hidden, dtype=torch.float32, device=cuda_dev)
+    ids_loc = torch.zeros(16, dtype=torch.int16, device=cuda_dev)
+    w_loc = torch.zeros(16, dtype=torch.float32, device=cuda_dev)
+    n_loc = torch.zeros(1, dtype=torch.int32, device=cuda_dev)
+    total = 0
+    for t in range(T):
+        kernels.select_local_experts(ids_all[t], w_all[t], sh.top_k, lo, hi, ids_loc, w_loc, n_loc)
+        kernels.moe_layer_int4_paged_var(xs[t], dec.tables[0], sh.num_experts, dec.shared_tables[0] if t == shared_token else 0,
+                                         ids_loc, w_loc, sh.top_k, 1.0, dec.act, want[t], False, sh.hidden, sh.intermediate,
+                                         sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, n_loc, dec.status)
+        torch.cuda.synchronize()
+        total += int(n_loc.item())
+    # grouped
+    cap = T * sh.top_k
+    pe = torch.zeros(cap, dtype=torch.int16, device=cuda_dev)
+    pw = torch.zeros(cap, dtype=torch.float32, device=cuda_dev)
+    pt = torch.zeros(cap, dtype=torch.int16, device=cuda_dev)
+    cnt = torch.zeros(1, dtype=torch.int32, device=cuda_dev)
+    kernels.select_local_pairs(ids_all, 32, w_all, 64, T, sh.top_k, lo, hi, pe, pw, pt, cap, cnt)
+    torch.cuda.synchronize()
+    assert int(cnt.item()) == total
+    toks = pt[:total].cpu().tolist()
+    assert toks == sorted(toks)
+    act = torch.zeros(17 * sh.intermediate, dtype=torch.float16, device=cuda_dev)
+    got = torch.full((T, sh.hidden), 7.0, dtype=torch.float32, device=cuda_dev)
+    for j in range((cap + 15) // 16):
+        kernels.moe_layer_int4_paged_grouped(xs, X_BF16, sh.hidden * 2, T, dec.tables[0], sh.num_experts,
+                                             dec.shared_tables[0] if j == 0 else 0, shared_token, pe, pw, pt, 16, 16 * j, cnt, 1.0,
+                                             act, got, sh.hidden, j > 0, sh.hidden, sh.intermediate, sh.pages_per_segment,
+                                             sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status)
+    torch.cuda.synchronize()
+    assert int(dec.status.item()) == 0
+    assert torch.equal(got, want), (name, T, total)
+
+
 def test_fused_launcher_refusals(cuda_dev):
     from vic_b200.lib import lib
     L = lib()

@@ -26,6 +26,14 @@ struct MoeLayerArgs {
     int H, I, P;
     int rpp_gu, rpp_dn;            // rows per page of gate/up and of down
     int* status;                   // device status word, or null
+    // Grouped mode (slot_token != null): the routed slots are (token, expert) PAIRS of several tokens,
+    // listed in ascending token order; x and out have one row per token.
+    const unsigned short* slot_token;  // [top_k] token of each routed slot, or null
+    int n_tokens;                  // rows of x / out
+    int shared_token;              // the token the shared expert (if any) belongs to
+    int x_stride;                  // bytes between the tokens' activation vectors
+    int out_stride;                // floats between the tokens' output rows
+    int slot_begin;                // pairs of the device-side count that earlier launches have taken
 };
 
 enum StatusBits : int { kStatusMissingPage = 1, kStatusBadExpert = 2, kStatusTimeout = 4 };
@@ -33,7 +41,7 @@ enum StatusBits : int { kStatusMissingPage = 1, kStatusBadExpert = 2, kStatusTim
 // Routed slots actually used by this launch (see MoeLayerArgs::num_active_dev).
 __device__ __forceinline__ int active_top_k(const MoeLayerArgs& a) {
     if (a.num_active_dev == nullptr) return a.top_k;
-    return min(a.top_k, max(0, *a.num_active_dev));
+    return min(a.top_k, max(0, *a.num_active_dev - a.slot_begin));
 }
 
 __device__ __forceinline__ void flag(int* status, int bit) {

@@ -274,6 +274,7 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, const void*
     a.shared_weight = shared_weight; a.act = (__half*)act_scratch; a.out = out; a.out_accumulate = out_accumulate;
     a.H = hidden_dim; a.I = expert_hidden_dim; a.P = pages_per_segment;
     a.rpp_gu = rows_per_page_gate_up; a.rpp_dn = rows_per_page_down; a.status = status;
+    a.slot_token = nullptr; a.n_tokens = 1; a.shared_token = 0; a.x_stride = 0; a.out_stride = 0; a.slot_begin = 0;
     cudaStream_t st = (cudaStream_t)stream;
 
     int err = 0;
@@ -349,6 +350,96 @@ extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer
 extern "C" int vib3_launch_moe_layer_int4_paged_var(VIB3_MOE_ARGS, const int* num_active_dev) {
     if (!num_active_dev) return VIB3_ERR_NULL;
     return moe_layer_dispatch(3, num_active_dev, VIB3_MOE_PASS);
+}
+
+// Grouped form for expert parallelism: the routed slots are (token, expert) pairs of several tokens in
+// ascending token order (vib3_launch_select_local_pairs makes such a list); x has n_tokens rows
+// x_stride_bytes apart, out has n_tokens rows out_stride floats apart.  This launch takes the pairs
+// [pair_begin, pair_begin + pair_capacity) of the list whose length is *num_pairs_dev; the pointers
+// pair_experts / pair_weights / pair_tokens are the START of the lists.  The shared expert (if given)
+// belongs to token shared_token.  Staged kernels only: VIB3_ERR_UNSUPPORTED for other shapes.
+extern "C" int vib3_launch_moe_layer_int4_paged_grouped(
+    const void* x, int x_dtype, int x_stride_bytes, int n_tokens, const void* page_table, int num_experts,
+    const void* shared_pages, int shared_token, const unsigned short* pair_experts, const float* pair_weights,
+    const unsigned short* pair_tokens, int pair_capacity, int pair_begin, const int* num_pairs_dev, float shared_weight,
+    void* act_scratch, float* out, int out_stride, int out_accumulate, int hidden_dim, int expert_hidden_dim,
+    int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down, int group_size, int* status, void* stream) {
+    if (!x || !page_table || !pair_experts || !pair_weights || !pair_tokens || !num_pairs_dev || !act_scratch || !out) return VIB3_ERR_NULL;
+    if (group_size != kGroupSize) return VIB3_ERR_UNSUPPORTED;
+    if (x_dtype < X_F32 || x_dtype > X_BF16) return VIB3_ERR_UNSUPPORTED;
+    if (hidden_dim <= 0 || expert_hidden_dim <= 0 || hidden_dim % kGroupSize || expert_hidden_dim % kGroupSize) return VIB3_ERR_SHAPE;
+    if (pair_capacity <= 0 || pair_capacity > kMaxSlots - 1 || pair_begin < 0 || num_experts <= 0) return VIB3_ERR_COUNT;
+    if (n_tokens <= 0 || n_tokens > 65535 || shared_token < 0 || shared_token >= n_tokens) return VIB3_ERR_COUNT;
+    if (pages_per_segment <= 0 || pages_per_segment > kMaxPages) return VIB3_ERR_COUNT;
+    if (rows_per_page_gate_up <= 0 || rows_per_page_down <= 0) return VIB3_ERR_SHAPE;
+    if ((long long)rows_per_page_gate_up * pages_per_segment < expert_hidden_dim) return VIB3_ERR_SHAPE;
+    if ((long long)rows_per_page_down * pages_per_segment < hidden_dim) return VIB3_ERR_SHAPE;
+    if (out_stride < hidden_dim || x_stride_bytes <= 0) return VIB3_ERR_SHAPE;
+    if (((uintptr_t)x & 15) || (x_stride_bytes & 15) || ((uintptr_t)page_table & 15) || ((uintptr_t)shared_pages & 15) ||
+        ((uintptr_t)act_scratch & 15) || ((uintptr_t)out & 3)) return VIB3_ERR_ALIGN;
+    if (!g_use_pipeline) return VIB3_ERR_UNSUPPORTED;
+
+    MoeLayerArgs a;
+    a.x = x; a.x_dtype = x_dtype;
+    a.page_table = (const PageEntry*)page_table; a.shared_pages = (const PageEntry*)shared_pages;
+    a.expert_ids = pair_experts + pair_begin; a.expert_weights = pair_weights + pair_begin;
+    a.top_k = pair_capacity; a.num_experts = num_experts; a.num_active_dev = num_pairs_dev;
+    a.shared_weight = shared_weight; a.act = (__half*)act_scratch; a.out = out; a.out_accumulate = out_accumulate;
+    a.H = hidden_dim; a.I = expert_hidden_dim; a.P = pages_per_segment;
+    a.rpp_gu = rows_per_page_gate_up; a.rpp_dn = rows_per_page_down; a.status = status;
+    a.slot_token = pair_tokens + pair_begin; a.n_tokens = n_tokens; a.shared_token = shared_token;
+    a.x_stride = x_stride_bytes; a.out_stride = out_stride; a.slot_begin = pair_begin;
+    cudaStream_t st = (cudaStream_t)stream;
+    int err = launch_gateup_pipelined(a, st);
+    if (err) return err;
+    return launch_down_pipelined(a, st);
+}
+
+// The (token, expert, weight) triples, in token-major order, whose expert lies in [expert_lo, expert_hi):
+// the pairs of a step that an expert-parallel rank owns.  ids / weights: n_tokens rows of top_k entries,
+// row strides in bytes.  The lists have room for `capacity` entries (n_tokens * top_k suffices);
+// *count_out receives the number of pairs found, even if it exceeds the capacity.
+__global__ void select_local_pairs_kernel(const unsigned char* ids, int ids_stride, const unsigned char* w, int w_stride,
+                                          int n_tokens, int top_k, int lo, int hi, unsigned short* pe, float* pw,
+                                          unsigned short* pt, int capacity, int* count_out) {
+    const int lane = threadIdx.x;
+    const int total = n_tokens * top_k;
+    int n = 0;
+    for (int base = 0; base < total; base += 32) {
+        const int i = base + lane;
+        int e = -1, tk = 0;
+        float wv = 0.f;
+        if (i < total) {
+            tk = i / top_k;
+            const int j = i - tk * top_k;
+            e = reinterpret_cast<const unsigned short*>(ids + (size_t)tk * ids_stride)[j];
+            wv = reinterpret_cast<const float*>(w + (size_t)tk * w_stride)[j];
+        }
+        const bool keep = e >= lo && e < hi;
+        const unsigned m = __ballot_sync(0xffffffffu, keep);
+        const int pos = n + __popc(m & ((1u << lane) - 1u));
+        if (keep && pos < capacity) {
+            pe[pos] = (unsigned short)e;
+            pw[pos] = wv;
+            pt[pos] = (unsigned short)tk;
+        }
+        n += __popc(m);
+    }
+    if (lane == 0) *count_out = n;
+}
+
+extern "C" int vib3_launch_select_local_pairs(const unsigned short* ids, int ids_stride_bytes, const float* weights,
+                                              int weights_stride_bytes, int n_tokens, int top_k, int expert_lo,
+                                              int expert_hi, unsigned short* pair_experts, float* pair_weights,
+                                              unsigned short* pair_tokens, int capacity, int* count_out, void* stream) {
+    if (!ids || !weights || !pair_experts || !pair_weights || !pair_tokens || !count_out) return VIB3_ERR_NULL;
+    if (n_tokens <= 0 || n_tokens > 65535 || top_k <= 0 || top_k > kMaxSlots - 1 || capacity <= 0 || expert_lo < 0 ||
+        expert_hi < expert_lo) return VIB3_ERR_COUNT;
+    if ((ids_stride_bytes & 1) || (weights_stride_bytes & 3)) return VIB3_ERR_ALIGN;
+    select_local_pairs_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const unsigned char*>(ids), ids_stride_bytes, reinterpret_cast<const unsigned char*>(weights),
+        weights_stride_bytes, n_tokens, top_k, expert_lo, expert_hi, pair_experts, pair_weights, pair_tokens, capacity, count_out);
+    return (int)cudaGetLastError();
 }
 
 // Keep, in order, the (expert, weight) pairs whose expert lies in [expert_lo, expert_hi): the slots of

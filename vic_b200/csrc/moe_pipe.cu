@@ -33,9 +33,15 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     const unsigned code_row = (unsigned)a.H / 2, scale_row = (unsigned)a.H / 16;
     const unsigned stage_bytes = 2 * kTileRows * (code_row + scale_row);
 
+    // Grouped mode: the slots are (token, expert) pairs of several tokens.  A CTA's contiguous share of the
+    // row space touches at most two slots, so it keeps two quantised activation vectors; which tokens they
+    // belong to is known only after the wait, so there is no pass 0 (the shared expert is the last slot).
+    const bool grouped = a.slot_token != nullptr;
+    const unsigned xbytes = (unsigned)nchunks * MATH::kStride;
+
     unsigned char* stages = smem_raw;
     unsigned char* xs = stages + (size_t)nstages * stage_bytes;
-    PageEntry* tab = reinterpret_cast<PageEntry*>(xs + (size_t)nchunks * MATH::kStride);  // [max_slots][2][P], shared expert at cap_k
+    PageEntry* tab = reinterpret_cast<PageEntry*>(xs + (size_t)(grouped ? 2 : 1) * xbytes);  // [max_slots][2][P], shared expert at cap_k
     uint64_t* full = reinterpret_cast<uint64_t*>(tab + max_slots * 2 * a.P);
     uint64_t* empty = full + kMaxStages;
     uint64_t* tab_ready = empty + kMaxStages;
@@ -57,25 +63,28 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     // router is still running and the shared expert streams under the router's serial tail.  Between the
     // passes nobody waits for the whole CTA: the producer warp alone waits for the router, builds the
     // routed slots' page table and goes on issuing copies while the consumers finish pass 0.
-    if (warp < kConsumerWarps) stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
+    if (warp < kConsumerWarps && !grouped) stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
     if (a.shared_pages)
         for (int i = tid; i < 2 * a.P; i += blockDim.x) tab[cap_k * 2 * a.P + i] = a.shared_pages[i];
     __syncthreads();
 
     int n = 0;  // tiles of this CTA so far, over both passes (producer and consumers count alike)
+    const int first_pass = (a.shared_pages && !grouped) ? 0 : 1;
+    const int shared_in_pass1 = (grouped && a.shared_pages) ? 1 : 0;
 
     if (warp == kConsumerWarps) {
         // ── producer warp: every lane walks the tiles; lane 0 arms the stage's barrier, lanes 0..3 each
         // issue one of the tile's four copies, so a tile costs one lane's worth of latency ──
         bool ok = true;
-        for (int pass = a.shared_pages ? 0 : 1; pass < 2 && ok; ++pass) {
-            int g0, g1, slot_base;
+        for (int pass = first_pass; pass < 2 && ok; ++pass) {
+            int g0, g1;
             if (pass == 0) {
                 cta_share(a.I, g0, g1);
-                slot_base = cap_k;
             } else {
-                pdl_trigger();
                 pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
+                // Only now may the next kernel in the stream start: it reads the routing without waiting,
+                // and may overwrite nothing this kernel still reads.
+                pdl_trigger();
                 a.top_k = active_top_k(a);
                 for (int i = lane; i < a.top_k * 2 * a.P; i += 32) {
                     const int s = i / (2 * a.P), rem = i % (2 * a.P);
@@ -87,8 +96,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tab_ready);  // release: the consumers acquire the table through this barrier
-                cta_share(a.top_k * a.I, g0, g1);
-                slot_base = 0;
+                cta_share((a.top_k + shared_in_pass1) * a.I, g0, g1);
             }
             TileWalk walk(g0, g1, a.I, a.rpp_gu);
             Tile t;
@@ -96,7 +104,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
                 const int st = n % nstages;
                 if (n >= nstages) ok = mbar_wait(empty + st, ((n / nstages) - 1) & 1);
                 if (!ok) break;
-                const int ts = slot_base + t.slot;
+                const int ts = (pass == 0 || t.slot >= a.top_k) ? cap_k : t.slot;  // the shared expert's entries sit at cap_k
                 const PageEntry eu = tab[(ts * 2 + kSegUp) * a.P + t.page];
                 const PageEntry eg = tab[(ts * 2 + kSegGate) * a.P + t.page];
                 unsigned char* sb = stages + (size_t)st * stage_bytes;
@@ -129,24 +137,41 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     const int group = warp / kGroupWarps, wi = warp % kGroupWarps;
     Ring ring{full, empty, landed, nstages};
     const uint32_t stages_addr = smem_u32(stages);
-    const uint32_t x_addr = smem_u32(xs) + lane * MATH::kStride;
-    for (int pass = a.shared_pages ? 0 : 1; pass < 2; ++pass) {
-        int g0, g1, slot_base;
+    const uint32_t x_base = smem_u32(xs) + lane * MATH::kStride;
+    int slot_a = 0;  // grouped mode: the slot whose token's vector is in the first activation buffer
+    for (int pass = first_pass; pass < 2; ++pass) {
+        int g0, g1;
         if (pass == 0) {
             cta_share(a.I, g0, g1);
-            slot_base = cap_k;
         } else {
-            // From here on this thread writes nothing that a kernel launched after this one may touch
-            // before its own dependency wait: the shared expert's rows (pass 0) are done.
-            pdl_trigger();
+            // The next kernel in the stream (the down kernel) reads the routing without waiting, so it may
+            // start only when the router is known to have finished: after this thread's own wait.  By
+            // then this thread has also finished the shared expert's rows (pass 0).
             pdl_wait();
+            pdl_trigger();
             a.top_k = active_top_k(a);
-            if (!mbar_wait(tab_ready, 0)) {
+            const bool ready = mbar_wait(tab_ready, 0);
+            cta_share((a.top_k + shared_in_pass1) * a.I, g0, g1);
+            if (grouped) {
+                // quantise the activation vectors of the (at most two) slots this CTA's rows belong to
+                if (ready && g1 > g0) {
+                    slot_a = g0 / a.I;
+                    const int slot_b = (g1 - 1) / a.I;
+                    const int tok_a = slot_a < a.top_k ? a.slot_token[slot_a] : a.shared_token;
+                    stage_activation<MATH>(xs, reinterpret_cast<const unsigned char*>(a.x) + (size_t)tok_a * a.x_stride,
+                                           a.x_dtype, a.H, tid, kConsumerWarps * 32);
+                    if (slot_b != slot_a) {
+                        const int tok_b = slot_b < a.top_k ? a.slot_token[slot_b] : a.shared_token;
+                        stage_activation<MATH>(xs + xbytes, reinterpret_cast<const unsigned char*>(a.x) + (size_t)tok_b * a.x_stride,
+                                               a.x_dtype, a.H, tid, kConsumerWarps * 32);
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");  // consumer warps only
+            }
+            if (!ready) {  // (after the barrier: a named barrier counts threads, nobody may leave before it)
                 if (lane == 0) flag(a.status, kStatusTimeout);
                 return;
             }
-            cta_share(a.top_k * a.I, g0, g1);
-            slot_base = 0;
         }
         TileWalk walk(g0, g1, a.I, a.rpp_gu);
         Tile t;
@@ -159,12 +184,13 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
             }
             const int p0 = wi * kPairsPerWarp;  // this warp's row pairs: p0 and p0 + 1 of the tile
             if (p0 < t.nrows) {
-                const int ts = slot_base + t.slot;
+                const int ts = (pass == 0 || t.slot >= a.top_k) ? cap_k : t.slot;
                 const PageEntry eu = tab[(ts * 2 + kSegUp) * a.P + t.page];
                 const PageEntry eg = tab[(ts * 2 + kSegGate) * a.P + t.page];
                 const bool present = eu.ptr != 0 && eg.ptr != 0 && t.rin + t.nrows <= eu.row_count && t.rin + t.nrows <= eg.row_count;
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};  // gate p0, up p0, gate p0+1, up p0+1
                 if (present) {
+                    const uint32_t x_addr = x_base + ((grouped && t.slot != slot_a) ? xbytes : 0u);
                     const uint32_t sb = stages_addr + st * stage_bytes;
                     const uint32_t g_addr = sb + p0 * code_row + lane * 16;
                     const uint32_t u_addr = g_addr + kTileRows * code_row;
@@ -196,7 +222,8 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
                 for (int k = 0; k < 4; ++k) acc[k] = warp_sum(acc[k]);
                 if (lane == 0) {
                     // pass 0 writes the shared expert's rows at the front of the scratch buffer (act_slot order)
-                    __half* dst = a.act + (size_t)(pass == 0 ? 0 : t.slot + (a.shared_pages ? 1 : 0)) * a.I + t.row + p0;
+                    const int apos = (pass == 0 || t.slot >= a.top_k) ? 0 : t.slot + (a.shared_pages ? 1 : 0);
+                    __half* dst = a.act + (size_t)apos * a.I + t.row + p0;
 #pragma unroll
                     for (int k = 0; k < kPairsPerWarp; ++k) {
                         if (p0 + k < t.nrows) {
@@ -230,17 +257,17 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
 // one arrival by the combiner), so consumer warps never wait for one another: they drift apart by
 // up to the depth of the rings, and loads, integer math and shuffles of different warps overlap.
 // stage layout: per slot [codes R*I/2][scales R*I/16], R = kDownRows.
-#ifndef VIB3_DOWN_ROWS
-#define VIB3_DOWN_ROWS 6
-#endif
-constexpr int kDownRows = VIB3_DOWN_ROWS;  // measured (Kimi shape, 9 slots): 4 rows 20.7 us, 6 rows 17.3 us, 8 rows 18.5 us
-constexpr int kDownRowsPerWarp = (kDownRows + 1) / 2;
-constexpr int kDownWarpsPerSlot = 2;
+// Two shapes (template parameters R = rows per tile, WPS = warps per slot): up to 9 slots R = 6, WPS = 2
+// (measured on the Kimi shape with 9 slots: 4 rows 20.7 us, 6 rows 17.3 us, 8 rows 18.5 us); 10 to 17
+// slots — the grouped launches of expert parallelism — R = 4, WPS = 1, so that two stages still fit.
+// In grouped mode (MoeLayerArgs::slot_token) the slots are (token, expert) pairs in ascending token
+// order and the combiner writes one output row per token.
 constexpr int kDownYStages = 4;
 constexpr int kDownMaxThreads = 640;  // 18 consumer warps for 9 slots + combiner + producer
 
-template <int NCH>
+template <int NCH, int R, int WPS>
 __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int nstages) {
+    constexpr int kDownRows = R, kDownWarpsPerSlot = WPS, kDownRowsPerWarp = (R + WPS - 1) / WPS;
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);  // launch shape and shared-memory layout
@@ -262,7 +289,8 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     uint64_t* yfull = empty + kMaxStages;
     uint64_t* yempty = yfull + kDownYStages;
     float* wts = reinterpret_cast<float*>(yempty + kDownYStages);
-    float* ybuf = wts + kMaxSlots;  // [y stage][row][kMaxSlots]
+    int* toks = reinterpret_cast<int*>(wts + kMaxSlots);  // grouped mode: token of each routed slot
+    float* ybuf = reinterpret_cast<float*>(toks + kMaxSlots);  // [y stage][row][kMaxSlots]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // The next kernel in the stream may overwrite the activation scratch before its own dependency
@@ -280,8 +308,9 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // Expert ids and routing weights were written by the router, which had completed before the
-    // gate/up kernel passed its own dependency wait, so they are visible here without waiting.
+    // Expert ids and routing weights were written by the router.  This kernel is launched only after
+    // every thread of the gate/up kernel has passed its own wait for the router, so they are complete
+    // and visible here without waiting.
     for (int i = tid; i < slots * a.P; i += blockDim.x) {
         const int s = i / a.P, p = i - s * a.P;
         const PageEntry* pg = slot_pages(a, s);
@@ -289,7 +318,10 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         if (pg) e = pg[kSegDown * a.P + p];
         tab[i] = e;
     }
-    for (int s = tid; s < slots; s += blockDim.x) wts[s] = s < a.top_k ? a.expert_weights[s] : a.shared_weight;
+    for (int s = tid; s < slots; s += blockDim.x) {
+        wts[s] = s < a.top_k ? a.expert_weights[s] : a.shared_weight;
+        toks[s] = a.slot_token ? (s < a.top_k ? (int)a.slot_token[s] : a.shared_token) : 0;
+    }
     __syncthreads();
 
     int g0, g1;
@@ -297,7 +329,8 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
 
     if (slots == 0) {  // nothing selected: the layer output is zero
         if (!a.out_accumulate)
-            for (int r = g0 + tid; r < g1; r += blockDim.x) a.out[r] = 0.f;
+            for (int tk = 0; tk < (a.slot_token ? a.n_tokens : 1); ++tk)
+                for (int r = g0 + tid; r < g1; r += blockDim.x) a.out[(size_t)tk * a.out_stride + r] = 0.f;
         return;
     }
     if (warp < combiner_warp && warp >= cwarps) return;  // warps of unused slots
@@ -315,12 +348,19 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             if (n >= nstages) ok = mbar_wait(empty + st, ((n / nstages) - 1) & 1);
             if (!ok) break;
             unsigned char* sb = stages + (size_t)st * stage_bytes;
-            const int s = lane >> 1;
-            PageEntry e{0, 0, 0, 0};
-            if (s < slots) e = tab[s * a.P + t.page];
-            const bool mine = s < slots && e.ptr != 0 && t.rin + t.nrows <= e.row_count;
-            const unsigned bytes = mine ? ((lane & 1) ? t.nrows * scale_row : t.nrows * code_row) : 0u;
-            unsigned tx = bytes;
+            // slots lane / 2 and (the 17th slot) 16 + lane / 2
+            PageEntry e[2];
+            unsigned bytes[2];
+            unsigned tx = 0;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int s = u * 16 + (lane >> 1);
+                e[u] = PageEntry{0, 0, 0, 0};
+                if (s < slots) e[u] = tab[s * a.P + t.page];
+                const bool mine = s < slots && e[u].ptr != 0 && t.rin + t.nrows <= e[u].row_count;
+                bytes[u] = mine ? ((lane & 1) ? t.nrows * scale_row : t.nrows * code_row) : 0u;
+                tx += bytes[u];
+            }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
             if (lane == 0) {
@@ -328,10 +368,14 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
                 else mbar_arrive(full + st);
             }
             __syncwarp();
-            if (mine) {
-                const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
-                if (lane & 1) bulk_load(sb + s * slot_bytes + kDownRows * code_row, base + (size_t)e.row_count * code_row + (size_t)t.rin * scale_row, bytes, full + st);
-                else bulk_load(sb + s * slot_bytes, base + (size_t)t.rin * code_row, bytes, full + st);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (bytes[u]) {
+                    const int s = u * 16 + (lane >> 1);
+                    const unsigned char* base = reinterpret_cast<const unsigned char*>(e[u].ptr);
+                    if (lane & 1) bulk_load(sb + s * slot_bytes + kDownRows * code_row, base + (size_t)e[u].row_count * code_row + (size_t)t.rin * scale_row, bytes[u], full + st);
+                    else bulk_load(sb + s * slot_bytes, base + (size_t)t.rin * code_row, bytes[u], full + st);
+                }
             }
             ++n;
         }
@@ -355,11 +399,27 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             }
             if (lane < t.nrows) {
                 const float* yb = ybuf + ys * (kDownRows * kMaxSlots) + lane * kMaxSlots;
-                float out = 0.f;
-                for (int k = 0; k < slots; ++k) out = fmaf(wts[k], yb[k], out);
                 const int r = t.row + lane;
-                if (a.out_accumulate) a.out[r] += out;
-                else a.out[r] = out;
+                if (a.slot_token == nullptr) {
+                    float out = 0.f;
+                    for (int k = 0; k < slots; ++k) out = fmaf(wts[k], yb[k], out);
+                    if (a.out_accumulate) a.out[r] += out;
+                    else a.out[r] = out;
+                } else {
+                    // one output row per token: its routed pairs in list order, then the shared expert
+                    int k = 0;
+                    for (int tk = 0; tk < a.n_tokens; ++tk) {
+                        float out = 0.f;
+                        while (k < a.top_k && toks[k] == tk) {
+                            out = fmaf(wts[k], yb[k], out);
+                            ++k;
+                        }
+                        if (a.shared_pages && tk == a.shared_token) out = fmaf(wts[a.top_k], yb[a.top_k], out);
+                        float* o = a.out + (size_t)tk * a.out_stride + r;
+                        if (a.out_accumulate) *o += out;
+                        else *o = out;
+                    }
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(yempty + ys);
@@ -484,7 +544,8 @@ int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const size_t stage_bytes = 2 * kTileRows * ((size_t)a.H / 2 + (size_t)a.H / 16);
-    const size_t fixed = (size_t)(a.H / kGroupSize) * MathQ16::kStride + (size_t)slots * 2 * a.P * sizeof(PageEntry) +
+    const size_t fixed = (size_t)(a.slot_token ? 2 : 1) * (a.H / kGroupSize) * MathQ16::kStride +
+                         (size_t)slots * 2 * a.P * sizeof(PageEntry) +
                          (2 * kMaxStages + 1) * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + 128;
     // leave kRouterCtaSmem of the SM's shared memory to a router CTA, so that this kernel's CTAs become
     // resident while the router still runs (see the kernel's first pass)
@@ -506,30 +567,34 @@ int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     }
 }
 
-template <int NCH>
+template <int NCH, int R, int WPS>
 static int launch_down_pipe_t(const MoeLayerArgs& a, cudaStream_t st, int nstages, size_t smem, int grid, int threads) {
-    static int attr = set_max_smem(moe_down_pipe_kernel<NCH>);
+    static int attr = set_max_smem(moe_down_pipe_kernel<NCH, R, WPS>);
     if (attr) return attr;
-    return launch_pipe(moe_down_pipe_kernel<NCH>, grid, threads, smem, st, a, nstages);
+    return launch_pipe(moe_down_pipe_kernel<NCH, R, WPS>, grid, threads, smem, st, a, nstages);
 }
 
 int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const int nchunks = a.I / kGroupSize;
-    // register-resident activations: at most two chunks per lane; two warps per slot, combiner, producer
+    // register-resident activations: at most two chunks per lane
     if (nchunks != 32 && nchunks != 64) return VIB3_ERR_UNSUPPORTED;
-    if ((slots * kDownWarpsPerSlot + 2) * 32 > kDownMaxThreads) return VIB3_ERR_UNSUPPORTED;
-    const size_t stage_bytes = (size_t)slots * kDownRows * ((size_t)a.I / 2 + (size_t)a.I / 16);
+    const bool wide = slots > 9;               // more than 9 slots: one warp per slot, 4-row tiles
+    const int rows = wide ? 4 : 6, wps = wide ? 1 : 2;
+    if ((slots * wps + 2) * 32 > kDownMaxThreads) return VIB3_ERR_UNSUPPORTED;
+    const size_t stage_bytes = (size_t)slots * rows * ((size_t)a.I / 2 + (size_t)a.I / 16);
     const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + 2 * (kMaxStages + kDownYStages) * sizeof(uint64_t) +
-                         kMaxSlots * sizeof(float) + kDownYStages * kDownRows * kMaxSlots * sizeof(float) + 128;
+                         2 * kMaxSlots * sizeof(float) + kDownYStages * rows * kMaxSlots * sizeof(float) + 128;
     const int nstages = pick_stages(fixed, stage_bytes, 2);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
     const size_t smem = fixed + (size_t)nstages * stage_bytes;
-    const int grid = min(sm_count(), (a.H + kDownRows - 1) / kDownRows);
-    const int threads = (slots * kDownWarpsPerSlot + 2) * 32;
-    return nchunks == 64 ? launch_down_pipe_t<2>(a, st, nstages, smem, grid, threads)
-                         : launch_down_pipe_t<1>(a, st, nstages, smem, grid, threads);
+    const int grid = min(sm_count(), (a.H + rows - 1) / rows);
+    const int threads = (slots * wps + 2) * 32;
+    if (wide) return nchunks == 64 ? launch_down_pipe_t<2, 4, 1>(a, st, nstages, smem, grid, threads)
+                                   : launch_down_pipe_t<1, 4, 1>(a, st, nstages, smem, grid, threads);
+    return nchunks == 64 ? launch_down_pipe_t<2, 6, 2>(a, st, nstages, smem, grid, threads)
+                         : launch_down_pipe_t<1, 6, 2>(a, st, nstages, smem, grid, threads);
 }
 
 }  // namespace vib3

@@ -5,20 +5,20 @@ shared expert.  Each rank decodes its own token stream (batch 1 per rank: G toke
 scaling), which is how a data-parallel attention stage feeds an expert-parallel MoE stage:
 
   1. every rank routes its own token (router weights are replicated, so the top-k is the one a
-     single GPU would compute: bit-exact by construction);
-  2. all_gather of (token activation, expert ids, routing weights): 14.4 KB per rank for Kimi;
-  3. for every token of the step, each rank keeps the (expert, weight) pairs of the experts it owns
-     (a device-side selection, order preserved) and runs the fused expert kernels over exactly those
-     slots of ITS OWN page table; the shared expert runs only on the token's home rank;
+     single GPU would compute: bit-exact by construction); the router writes ids and weights straight
+     into the rank's message, next to the token;
+  2. all_gather of the messages (token activation, expert ids, routing weights): 14.4 KB per rank;
+  3. each rank lists, on the device, the (token, expert, weight) pairs of the step whose expert it owns
+     (token-major, order preserved) and runs ONE grouped launch pair of the expert kernels over them — on
+     average top_k pairs per rank, i.e. the work of a single-GPU token — plus the shared expert for its
+     own token; the kernels read the tokens in place from the gathered messages.  A launch takes up
+     to 16 pairs; further launches for pairs 16.., 32.. follow unconditionally (the count lives on the
+     device) and return at once when there is nothing for them;
   4. reduce_scatter of the per-token partial sums [G, H] fp32: each rank receives the full layer
      output of its own token.
 
 Peer data always lands in local HBM (NCCL receive buffers) before a kernel reads it.  The only
 difference from the single-GPU result is the fp32 association of the cross-rank sum.
-
-Step 3 costs one launch pair per (token, rank); with one local expert per pair on average the
-launches are mostly latency.  A grouped kernel that takes several (token, expert) pairs per launch
-removes that and is the next step of this path.
 """
 from __future__ import annotations
 
@@ -42,22 +42,40 @@ def local_experts(rank: int, num_experts: int, world: int) -> List[int]:
     return [e for e in range(num_experts) if expert_owner(e, num_experts, world) == rank]
 
 
+PAIRS_PER_LAUNCH = 16   # capacity of one grouped launch (kernel limit)
+
+
+def message_layout(hidden: int) -> Tuple[int, int, int]:
+    """Byte offsets of (expert ids u16[16], routing weights f32[16]) after the bf16 token, and the message
+    size: [token bf16 x H][ids][weights], a multiple of 16 bytes so that every token starts aligned."""
+    ids_off = hidden * 2
+    w_off = ids_off + MAX_ACTIVE_EXPERTS * 2
+    size = w_off + MAX_ACTIVE_EXPERTS * 4
+    return ids_off, w_off, (size + 15) // 16 * 16
+
+
+def message_views(buf: torch.Tensor, hidden: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Views into a message buffer ([bytes] or [G, bytes] uint8): token bf16 [.., H], ids int16 [.., 16],
+    weights fp32 [.., 16].  The router writes through the last two; the kernels read the first in place."""
+    ids_off, w_off, _ = message_layout(hidden)
+    x = buf[..., :ids_off].view(torch.bfloat16)
+    ids = buf[..., ids_off:w_off].view(torch.int16)
+    ws = buf[..., w_off:w_off + MAX_ACTIVE_EXPERTS * 4].view(torch.float32)
+    return x, ids, ws
+
+
 def pack_message(buf: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> None:
-    """One rank's per-step message as int32 words: the bf16 token (H/2 words), MAX_ACTIVE_EXPERTS expert
-    ids, MAX_ACTIVE_EXPERTS routing weights (fp32 bit patterns)."""
-    H2 = x.numel() // 2
-    buf[:H2].copy_(x.view(torch.int32))
-    buf[H2:H2 + MAX_ACTIVE_EXPERTS].copy_(ids.to(torch.int32))
-    buf[H2 + MAX_ACTIVE_EXPERTS:H2 + 2 * MAX_ACTIVE_EXPERTS].copy_(weights.view(torch.int32))
+    """Fill one rank's message from separate tensors (the GPU path lets the router write ids and weights
+    in place and only copies the token)."""
+    mx, mi, mw = message_views(buf, x.numel())
+    mx.copy_(x)
+    mi.copy_(ids)
+    mw.copy_(weights)
 
 
 def unpack_messages(recv: torch.Tensor, hidden: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """[G, words] gathered messages -> (tokens [G, H] bf16 view, ids [G, 16] int16, weights [G, 16] fp32)."""
-    H2 = hidden // 2
-    xs = recv[:, :H2].view(torch.bfloat16)
-    ids = recv[:, H2:H2 + MAX_ACTIVE_EXPERTS].to(torch.int16)
-    ws = recv[:, H2 + MAX_ACTIVE_EXPERTS:H2 + 2 * MAX_ACTIVE_EXPERTS].contiguous().view(torch.float32)
-    return xs, ids, ws
+    """[G, bytes] gathered messages -> (tokens [G, H] bf16, ids [G, 16] int16, weights [G, 16] fp32) views."""
+    return message_views(recv, hidden)
 
 
 def gather_messages(send: torch.Tensor, recv: torch.Tensor, world: int, group=None) -> None:
@@ -88,43 +106,51 @@ class ExpertParallelDecoder:
         self.dec = MoeDecoder(model, exact_order=True)
         sh = model.shape
         dev = model.router_w.device
-        words = sh.hidden // 2 + 2 * MAX_ACTIVE_EXPERTS
-        self.send = torch.zeros(words, dtype=torch.int32, device=dev)
-        self.recv = torch.zeros(world, words, dtype=torch.int32, device=dev)
+        self.ids_off, self.w_off, self.msg_bytes = message_layout(sh.hidden)
+        self.send = torch.zeros(self.msg_bytes, dtype=torch.uint8, device=dev)
+        self.recv = torch.zeros(world, self.msg_bytes, dtype=torch.uint8, device=dev)
+        self.send_x, self.send_ids, self.send_w = message_views(self.send, sh.hidden)
+        self.recv_x, self.recv_ids, self.recv_w = message_views(self.recv, sh.hidden)
         self.partial = torch.zeros(world, sh.hidden, dtype=torch.float32, device=dev)
         self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
-        self.ids_t = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
-        self.w_t = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
-        self.ids_loc = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
-        self.w_loc = torch.zeros(world, MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
-        self.n_loc = torch.zeros(world, dtype=torch.int32, device=dev)
+        cap = world * sh.top_k
+        self.pair_e = torch.zeros(cap, dtype=torch.int16, device=dev)
+        self.pair_w = torch.zeros(cap, dtype=torch.float32, device=dev)
+        self.pair_t = torch.zeros(cap, dtype=torch.int16, device=dev)
+        self.n_pairs = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.act = torch.zeros((PAIRS_PER_LAUNCH + 1) * sh.intermediate, dtype=torch.float16, device=dev)
         mine = local_experts(rank, sh.num_experts, world)
         self.expert_lo, self.expert_hi = (mine[0], mine[-1] + 1) if mine else (0, 0)
-        self.launches_per_step = 1 + 3 * world
+        self.grouped_launches = (cap + PAIRS_PER_LAUNCH - 1) // PAIRS_PER_LAUNCH
+        self.launches_per_step = 2 + 2 * self.grouped_launches   # router, pair selection, (gate/up, down) per grouped launch
 
     def step(self, layer: int, x: torch.Tensor) -> torch.Tensor:
         """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
         from . import kernels
+        from .core_types import X_BF16
         sh, dec = self.model.shape, self.dec
         H = sh.hidden
-        dec.route(layer, x)
-        pack_message(self.send, x, dec.ids, dec.weights)
+        self.send_x.copy_(x)
+        # the router writes the expert ids and routing weights into the message
+        kernels.router_topk_ex(self.send_x, self.model.router_w[layer], dec.scores, None, self.send_ids, self.send_w,
+                               sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, dec.exact_order, dec.workspace)
         gather_messages(self.send, self.recv, self.world, self.group)
-        xs, ids, ws = unpack_messages(self.recv, H)
-        self.ids_t.copy_(ids)
-        self.w_t.copy_(ws)
-        for t in range(self.world):
-            # the token's experts that live here, compacted on the device; the kernels then balance
-            # their work over exactly those slots (plus the shared expert on the token's home rank)
-            kernels.select_local_experts(self.ids_t[t], self.w_t[t], sh.top_k, self.expert_lo, self.expert_hi,
-                                         self.ids_loc[t], self.w_loc[t], self.n_loc[t:t + 1])
-            shared = dec.shared_tables[layer] if t == self.rank else 0
-            kernels.moe_layer_int4_paged_var(xs[t], dec.tables[layer], sh.num_experts, shared, self.ids_loc[t],
-                                             self.w_loc[t], sh.top_k, 1.0, dec.act, self.partial[t], False, H,
-                                             sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page,
-                                             sh.down.rows_per_page, self.n_loc[t:t + 1], dec.status)
+        kernels.select_local_pairs(self.recv_ids, self.msg_bytes, self.recv_w, self.msg_bytes, self.world, sh.top_k,
+                                   self.expert_lo, self.expert_hi, self.pair_e, self.pair_w, self.pair_t,
+                                   self.pair_e.numel(), self.n_pairs)
+        for j in range(self.grouped_launches):
+            kernels.moe_layer_int4_paged_grouped(
+                self.recv_x, X_BF16, self.msg_bytes, self.world, dec.tables[layer], sh.num_experts,
+                dec.shared_tables[layer] if j == 0 else 0, self.rank, self.pair_e, self.pair_w, self.pair_t,
+                PAIRS_PER_LAUNCH, j * PAIRS_PER_LAUNCH, self.n_pairs, 1.0, self.act, self.partial, H, j > 0, H,
+                sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status)
         combine_partials(self.out, self.partial, self.rank, self.world, self.group)
         return self.out
+
+    def routing(self):
+        """This rank's token's routing of the last step (host copies)."""
+        k = self.model.shape.top_k
+        return (self.send_ids[:k].cpu().view(torch.int16).numpy().view("uint16"), self.send_w[:k].cpu().numpy())
 
 
 def build_rank_model(shape: MoeShape, n_layers: int, device, seed: int, rank: int, world: int, per_page_content=False):

@@ -158,6 +158,28 @@ def moe_layer_int4_paged_var(x: torch.Tensor, page_table: int, num_experts: int,
         _ptr(num_active_dev)))
 
 
+def moe_layer_int4_paged_grouped(x, x_dtype: int, x_stride_bytes: int, n_tokens: int, page_table: int, num_experts: int,
+                                 shared_pages: int, shared_token: int, pair_experts, pair_weights, pair_tokens,
+                                 pair_capacity: int, pair_begin: int, num_pairs_dev, shared_weight: float, act_scratch, out,
+                                 out_stride: int, out_accumulate: bool, hidden_dim: int, expert_hidden_dim: int,
+                                 pages_per_segment: int, rows_per_page_gate_up: int, rows_per_page_down: int, status=None,
+                                 stream: Optional[int] = None) -> None:
+    """One launch pair over the (token, expert) pairs of several tokens (expert parallelism)."""
+    check("moe_layer_int4_paged_grouped", lib().vib3_launch_moe_layer_int4_paged_grouped(
+        _ptr(x), x_dtype, x_stride_bytes, n_tokens, page_table, num_experts, shared_pages or 0, shared_token,
+        _ptr(pair_experts), _ptr(pair_weights), _ptr(pair_tokens), pair_capacity, pair_begin, _ptr(num_pairs_dev),
+        shared_weight, _ptr(act_scratch), _ptr(out), out_stride, int(out_accumulate), hidden_dim, expert_hidden_dim,
+        pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status), _stream(stream)))
+
+
+def select_local_pairs(ids, ids_stride_bytes: int, weights, weights_stride_bytes: int, n_tokens: int, top_k: int,
+                       expert_lo: int, expert_hi: int, pair_experts, pair_weights, pair_tokens, capacity: int, count_out,
+                       stream: Optional[int] = None) -> None:
+    check("select_local_pairs", lib().vib3_launch_select_local_pairs(
+        _ptr(ids), ids_stride_bytes, _ptr(weights), weights_stride_bytes, n_tokens, top_k, expert_lo, expert_hi,
+        _ptr(pair_experts), _ptr(pair_weights), _ptr(pair_tokens), capacity, _ptr(count_out), _stream(stream)))
+
+
 def select_local_experts(ids, weights, top_k: int, expert_lo: int, expert_hi: int, ids_out, weights_out, count_out,
                          stream: Optional[int] = None) -> None:
     check("select_local_experts", lib().vib3_launch_select_local_experts(
