@@ -265,9 +265,15 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
 constexpr int kDownYStages = 4;
 constexpr int kDownMaxThreads = 640;  // 18 consumer warps for 9 slots + combiner + producer
 
+// R = 0: tile height and warps per slot are chosen in the kernel from the number of ACTIVE slots (which
+// may live in device memory): up to 9 slots 6 rows and 2 warps per slot, otherwise one warp per slot and
+// 6 rows if two stages of that size fit, else 4 rows.  `ring` = bytes of the ring (R = 0) or its number
+// of stages (R > 0).
 template <int NCH, int R, int WPS>
-__global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int nstages) {
-    constexpr int kDownRows = R, kDownWarpsPerSlot = WPS, kDownRowsPerWarp = (R + WPS - 1) / WPS;
+__global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int ring) {
+    constexpr bool kDyn = R == 0;
+    constexpr int kRowsMax = kDyn ? 6 : R;
+    constexpr int kDownRowsPerWarp = kDyn ? 6 : (R + (kDyn ? 1 : WPS) - 1) / (kDyn ? 1 : WPS);
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);  // launch shape and shared-memory layout
@@ -275,15 +281,23 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     // gate/up kernel passed its dependency wait, like the expert ids (see below).
     a.top_k = active_top_k(a);
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+    const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
+    int rows_v = R, wps_v = WPS, nstages_v = ring;
+    if (kDyn) {
+        const unsigned row_bytes = code_row + scale_row;
+        wps_v = slots <= 9 ? 2 : 1;
+        rows_v = (slots <= 9 || 2u * slots * 6u * row_bytes <= (unsigned)ring) ? 6 : 4;
+        nstages_v = min(kMaxStages, ring / max(1, (int)(slots * rows_v * row_bytes)));
+    }
+    const int kDownRows = rows_v, kDownWarpsPerSlot = wps_v, nstages = nstages_v;
     const int cwarps = slots * kDownWarpsPerSlot;       // consumer warps in use
     const int producer_warp = (int)(blockDim.x >> 5) - 1;
     const int combiner_warp = producer_warp - 1;
-    const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
     const unsigned slot_bytes = kDownRows * (code_row + scale_row);
-    const unsigned stage_bytes = max_slots * slot_bytes;
+    const unsigned stage_bytes = (kDyn ? slots : max_slots) * slot_bytes;
 
-    unsigned char* stages = smem_raw;
-    PageEntry* tab = reinterpret_cast<PageEntry*>(stages + (size_t)nstages * stage_bytes);
+    // fixed-size parts first, the ring (whose stage size may depend on the active slots) last
+    PageEntry* tab = reinterpret_cast<PageEntry*>(smem_raw);
     uint64_t* full = reinterpret_cast<uint64_t*>(tab + max_slots * a.P);
     uint64_t* empty = full + kMaxStages;
     uint64_t* yfull = empty + kMaxStages;
@@ -291,6 +305,8 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     float* wts = reinterpret_cast<float*>(yempty + kDownYStages);
     int* toks = reinterpret_cast<int*>(wts + kMaxSlots);  // grouped mode: token of each routed slot
     float* ybuf = reinterpret_cast<float*>(toks + kMaxSlots);  // [y stage][row][kMaxSlots]
+    unsigned char* stages = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(ybuf + kDownYStages * kRowsMax * kMaxSlots) + 127) & ~(uintptr_t)127);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // The next kernel in the stream may overwrite the activation scratch before its own dependency
@@ -350,10 +366,11 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             unsigned char* sb = stages + (size_t)st * stage_bytes;
             // slots lane / 2 and (the 17th slot) 16 + lane / 2
             PageEntry e[2];
-            unsigned bytes[2];
+            unsigned bytes[2] = {0u, 0u};
             unsigned tx = 0;
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
+                if (u == 1 && slots <= 16) break;  // (the same for every lane)
                 const int s = u * 16 + (lane >> 1);
                 e[u] = PageEntry{0, 0, 0, 0};
                 if (s < slots) e[u] = tab[s * a.P + t.page];
@@ -398,7 +415,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
                 return;
             }
             if (lane < t.nrows) {
-                const float* yb = ybuf + ys * (kDownRows * kMaxSlots) + lane * kMaxSlots;
+                const float* yb = ybuf + ys * (kRowsMax * kMaxSlots) + lane * kMaxSlots;
                 const int r = t.row + lane;
                 if (a.slot_token == nullptr) {
                     float out = 0.f;
@@ -462,7 +479,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         for (int j = 0; j < kDownRowsPerWarp; ++j) {
             const int r = h + j * kDownWarpsPerSlot;
             float acc = 0.f;
-            if (r < t.nrows && present) {
+            if (r < kDownRows && r < t.nrows && present) {
 #pragma unroll
                 for (int i = 0; i < NCH; ++i) {
                     const uint4 q = lds128(sb + code_base + r * code_row + i * 512);
@@ -475,7 +492,8 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + st);  // this warp has read everything it needs from the stage
 #pragma unroll
-        for (int j = 0; j < kDownRowsPerWarp; ++j) y[j] = warp_sum(y[j]);
+        for (int j = 0; j < kDownRowsPerWarp; ++j)
+            if (h + j * kDownWarpsPerSlot < kDownRows) y[j] = warp_sum(y[j]);
         if (!present && h == 0 && lane == 0) flag(a.status, kStatusMissingPage);
         const int ys = n % kDownYStages;
         if (n >= kDownYStages && !mbar_wait(yempty + ys, ((n / kDownYStages) - 1) & 1)) {
@@ -483,7 +501,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             return;
         }
         if (lane == 0) {
-            float* yb = ybuf + ys * (kDownRows * kMaxSlots);
+            float* yb = ybuf + ys * (kRowsMax * kMaxSlots);
             // fp16 rounding of the down projection (its output buffer is fp16 in the reference)
 #pragma unroll
             for (int j = 0; j < kDownRowsPerWarp; ++j)
@@ -580,19 +598,25 @@ int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     const int nchunks = a.I / kGroupSize;
     // register-resident activations: at most two chunks per lane
     if (nchunks != 32 && nchunks != 64) return VIB3_ERR_UNSUPPORTED;
-    const bool wide = slots > 9;               // more than 9 slots: one warp per slot, 4-row tiles
-    const int rows = wide ? 4 : 6, wps = wide ? 1 : 2;
-    if ((slots * wps + 2) * 32 > kDownMaxThreads) return VIB3_ERR_UNSUPPORTED;
-    const size_t stage_bytes = (size_t)slots * rows * ((size_t)a.I / 2 + (size_t)a.I / 16);
+    const size_t row_bytes = (size_t)a.I / 2 + (size_t)a.I / 16;
     const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + 2 * (kMaxStages + kDownYStages) * sizeof(uint64_t) +
-                         2 * kMaxSlots * sizeof(float) + kDownYStages * rows * kMaxSlots * sizeof(float) + 128;
+                         2 * kMaxSlots * sizeof(float) + kDownYStages * 6 * kMaxSlots * sizeof(float) + 256;
+    if (slots > 9) {
+        // Launch sized for up to 17 slots; how many are active is known only on the device, and the kernel
+        // picks tile height, warps per slot and ring depth from that number.
+        if (slots > kMaxSlots || fixed + 2 * (size_t)slots * 4 * row_bytes > kSmemBudget) return VIB3_ERR_UNSUPPORTED;
+        const int ring = (int)(kSmemBudget - fixed);
+        const int grid = min(sm_count(), (a.H + 3) / 4);
+        return nchunks == 64 ? launch_down_pipe_t<2, 0, 0>(a, st, ring, kSmemBudget, grid, kDownMaxThreads)
+                             : launch_down_pipe_t<1, 0, 0>(a, st, ring, kSmemBudget, grid, kDownMaxThreads);
+    }
+    const int rows = 6, wps = 2;
+    const size_t stage_bytes = (size_t)slots * rows * row_bytes;
     const int nstages = pick_stages(fixed, stage_bytes, 2);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
     const size_t smem = fixed + (size_t)nstages * stage_bytes;
     const int grid = min(sm_count(), (a.H + rows - 1) / rows);
     const int threads = (slots * wps + 2) * 32;
-    if (wide) return nchunks == 64 ? launch_down_pipe_t<2, 4, 1>(a, st, nstages, smem, grid, threads)
-                                   : launch_down_pipe_t<1, 4, 1>(a, st, nstages, smem, grid, threads);
     return nchunks == 64 ? launch_down_pipe_t<2, 6, 2>(a, st, nstages, smem, grid, threads)
                          : launch_down_pipe_t<1, 6, 2>(a, st, nstages, smem, grid, threads);
 }

@@ -126,15 +126,27 @@ class ExpertParallelDecoder:
 
     def step(self, layer: int, x: torch.Tensor) -> torch.Tensor:
         """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
+        self.route(layer, x)
+        self.gather()
+        self.experts(layer)
+        return self.combine()
+
+    def route(self, layer: int, x: torch.Tensor) -> None:
         from . import kernels
-        from .core_types import X_BF16
         sh, dec = self.model.shape, self.dec
-        H = sh.hidden
         self.send_x.copy_(x)
         # the router writes the expert ids and routing weights into the message
         kernels.router_topk_ex(self.send_x, self.model.router_w[layer], dec.scores, None, self.send_ids, self.send_w,
                                sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, dec.exact_order, dec.workspace)
+
+    def gather(self) -> None:
         gather_messages(self.send, self.recv, self.world, self.group)
+
+    def experts(self, layer: int) -> None:
+        from . import kernels
+        from .core_types import X_BF16
+        sh, dec = self.model.shape, self.dec
+        H = sh.hidden
         kernels.select_local_pairs(self.recv_ids, self.msg_bytes, self.recv_w, self.msg_bytes, self.world, sh.top_k,
                                    self.expert_lo, self.expert_hi, self.pair_e, self.pair_w, self.pair_t,
                                    self.pair_e.numel(), self.n_pairs)
@@ -144,6 +156,8 @@ class ExpertParallelDecoder:
                 dec.shared_tables[layer] if j == 0 else 0, self.rank, self.pair_e, self.pair_w, self.pair_t,
                 PAIRS_PER_LAUNCH, j * PAIRS_PER_LAUNCH, self.n_pairs, 1.0, self.act, self.partial, H, j > 0, H,
                 sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status)
+
+    def combine(self) -> torch.Tensor:
         combine_partials(self.out, self.partial, self.rank, self.world, self.group)
         return self.out
 
@@ -252,6 +266,34 @@ def bench_main(args) -> None:
     torch.cuda.synchronize()
     e2e_local = e0.elapsed_time(e1)
 
+    # where the step's time goes: each phase alone, 16 times back to back in a CUDA graph of its own
+    # (CUDA events on this rank; every rank replays the same graphs, so the collectives match up)
+    phases = {}
+    if graph is not None:
+        def time_phase(fn, reps=16):
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                gp = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gp, stream=side):
+                    for i in range(reps):
+                        fn(i)
+                gp.replay()
+                side.synchronize()
+                dist.barrier()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record(side)
+                for _ in range(4):
+                    gp.replay()
+                a1.record(side)
+                side.synchronize()
+            return a0.elapsed_time(a1) * 1e3 / (4 * reps)
+        phases["route"] = time_phase(lambda i: ep.route(i % layers, xs[i % B.N_TOKENS]))
+        phases["all_gather"] = time_phase(lambda i: ep.gather())
+        phases["experts"] = time_phase(lambda i: ep.experts(i % layers))
+        phases["reduce_scatter"] = time_phase(lambda i: ep.combine())
+    dist.barrier()
+
     t = torch.tensor([ms_local, e2e_local], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
@@ -269,6 +311,7 @@ def bench_main(args) -> None:
             "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": world * sh.hidden * 2,
                     "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms / K},
             "gpu_launches": K * ep.launches_per_step * world,
+            "phase_us_rank0": {k: round(v, 1) for k, v in phases.items()},
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": world * (b_gu + b_dn + b_r) / (ms * 1e-3 / K) / 1e9,
                          "peak": world * B.measured_peaks()[0], "unit": "GB/s",
