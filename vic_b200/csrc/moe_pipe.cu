@@ -33,6 +33,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLay
     const unsigned code_row = (unsigned)a.H / 2, scale_row = (unsigned)a.H / 16;
     const unsigned stage_bytes = 2 * kTileRows * (code_row + scale_row);
 
+    // A launch for a later window of a device-side pair list (slot_begin > 0) with nothing in its window:
+    // leave at once.  The count was written by a kernel that had completed before the first launch of
+    // the chain started, so it can be read without waiting.
+    if (a.slot_begin > 0 && a.num_active_dev && !a.shared_pages && *a.num_active_dev <= a.slot_begin) return;
     // Grouped mode: the slots are (token, expert) pairs of several tokens.  A CTA's contiguous share of the
     // row space touches at most two slots, so it keeps two quantised activation vectors; which tokens they
     // belong to is known only after the wait, so there is no pass 0 (the shared expert is the last slot).
@@ -279,6 +283,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);  // launch shape and shared-memory layout
     // The slot count may come from device memory; the kernel that wrote it had completed before the
     // gate/up kernel passed its dependency wait, like the expert ids (see below).
+    if (a.slot_begin > 0 && a.num_active_dev && !a.shared_pages && a.out_accumulate && *a.num_active_dev <= a.slot_begin) return;
     a.top_k = active_top_k(a);
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
