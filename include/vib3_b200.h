@@ -173,6 +173,9 @@ int vib3_launch_select_local_pairs(const unsigned short* ids, int ids_stride_byt
                                    int weights_stride_bytes, int n_tokens, int top_k, int expert_lo, int expert_hi,
                                    unsigned short* pair_experts, float* pair_weights, unsigned short* pair_tokens,
                                    int capacity, int* count_out, void* stream);
+/* out[c] = sum over r of in[r * row_stride + c], rows added in order (fp32; 16-byte aligned pointers,
+ * row_stride a multiple of 4): combines the partial sums an expert-parallel rank has received. */
+int vib3_launch_sum_rows_f32(const float* in, int rows, int cols, int row_stride, float* out, void* stream);
 /* Keep, in order, the (expert, weight) pairs with expert_lo <= expert < expert_hi; *count_out = how
  * many.  ids_out / weights_out have top_k entries (unused ones are filled with expert_lo / 0). */
 int vib3_launch_select_local_experts(const unsigned short* ids, const float* weights, int top_k, int expert_lo,

@@ -442,6 +442,35 @@ extern "C" int vib3_launch_select_local_pairs(const unsigned short* ids, int ids
     return (int)cudaGetLastError();
 }
 
+// out[c] = in[0][c] + in[1][c] + ... in row order (fp32): the last step of an expert-parallel layer when
+// every rank has received the other ranks' partial sums for its token.
+__global__ void sum_rows_kernel(const float* in, int rows, int cols, int row_stride, float* out) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c + 3 < cols) {
+        float4 acc = *reinterpret_cast<const float4*>(in + c);
+        for (int r = 1; r < rows; ++r) {
+            const float4 v = *reinterpret_cast<const float4*>(in + (size_t)r * row_stride + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *reinterpret_cast<float4*>(out + c) = acc;
+    } else {
+        for (int k = c; k < cols; ++k) {
+            float acc = in[k];
+            for (int r = 1; r < rows; ++r) acc += in[(size_t)r * row_stride + k];
+            out[k] = acc;
+        }
+    }
+}
+
+extern "C" int vib3_launch_sum_rows_f32(const float* in, int rows, int cols, int row_stride, float* out, void* stream) {
+    if (!in || !out) return VIB3_ERR_NULL;
+    if (rows <= 0 || cols <= 0 || row_stride < cols) return VIB3_ERR_SHAPE;
+    if (((uintptr_t)in & 15) || ((uintptr_t)out & 15) || (row_stride & 3)) return VIB3_ERR_ALIGN;
+    const int threads = 128, per_block = threads * 4;
+    sum_rows_kernel<<<(cols + per_block - 1) / per_block, threads, 0, (cudaStream_t)stream>>>(in, rows, cols, row_stride, out);
+    return (int)cudaGetLastError();
+}
+
 // Keep, in order, the (expert, weight) pairs whose expert lies in [expert_lo, expert_hi): the slots of
 // a token that an expert-parallel rank owns.  ids_out/weights_out have room for top_k entries; the
 // rest is filled with expert_lo / 0; *count_out receives the number kept.

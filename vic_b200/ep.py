@@ -78,23 +78,35 @@ def unpack_messages(recv: torch.Tensor, hidden: int) -> Tuple[torch.Tensor, torc
     return message_views(recv, hidden)
 
 
-def gather_messages(send: torch.Tensor, recv: torch.Tensor, world: int, group=None) -> None:
-    if world > 1:
-        dist.all_gather_into_tensor(recv.view(-1), send, group=group)
-    else:
+def gather_messages(send: torch.Tensor, recv: torch.Tensor, world: int, group=None, scratch: Optional[torch.Tensor] = None) -> None:
+    """Every rank's message to every rank.  With `scratch` ([G, bytes]) the exchange is one all-to-all of
+    point-to-point transfers (one hop whatever G is) instead of the ring all-gather (G-1 hops)."""
+    if world == 1:
         recv[0].copy_(send)
+    elif scratch is not None:
+        scratch.copy_(send.expand(world, -1))
+        dist.all_to_all_single(recv.view(-1), scratch.view(-1), group=group)
+    else:
+        dist.all_gather_into_tensor(recv.view(-1), send, group=group)
 
 
-def combine_partials(out: torch.Tensor, partial: torch.Tensor, rank: int, world: int, group=None) -> None:
-    """Sum the per-token partial layer outputs [G, H] over ranks; rank r keeps row r."""
+def combine_partials(out: torch.Tensor, partial: torch.Tensor, rank: int, world: int, group=None,
+                     scratch: Optional[torch.Tensor] = None) -> None:
+    """Sum the per-token partial layer outputs [G, H] over ranks; rank r keeps row r.  With `scratch`
+    ([G, H] fp32, device) row t of every rank goes to rank t in one all-to-all and the rank adds the G rows
+    it received in rank order; otherwise NCCL's ring reduce-scatter does both."""
     if world == 1:
         out.copy_(partial[0])
-    elif dist.get_backend(group) == "nccl":
-        dist.reduce_scatter_tensor(out, partial.view(-1), op=dist.ReduceOp.SUM, group=group)
-    else:  # gloo (CPU tests) has no reduce_scatter
+    elif dist.get_backend(group) != "nccl":  # gloo (CPU tests) has no reduce_scatter
         tmp = partial.clone()
         dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=group)
         out.copy_(tmp[rank])
+    elif scratch is not None:
+        from . import kernels
+        dist.all_to_all_single(scratch.view(-1), partial.view(-1), group=group)
+        kernels.sum_rows_f32(scratch, out)
+    else:
+        dist.reduce_scatter_tensor(out, partial.view(-1), op=dist.ReduceOp.SUM, group=group)
 
 
 class ExpertParallelDecoder:
@@ -113,6 +125,10 @@ class ExpertParallelDecoder:
         self.recv_x, self.recv_ids, self.recv_w = message_views(self.recv, sh.hidden)
         self.partial = torch.zeros(world, sh.hidden, dtype=torch.float32, device=dev)
         self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
+        # "a2a": both exchanges as one-hop all-to-alls (plus a row sum); "ring": NCCL all-gather / reduce-scatter
+        self.collectives = os.environ.get("VIB3_EP_COLLECTIVES", "a2a" if world > 2 else "ring")
+        self.send_rep = torch.zeros(world, self.msg_bytes, dtype=torch.uint8, device=dev) if self.collectives == "a2a" else None
+        self.partial_in = torch.zeros(world, sh.hidden, dtype=torch.float32, device=dev) if self.collectives == "a2a" else None
         cap = world * sh.top_k
         self.pair_e = torch.zeros(cap, dtype=torch.int16, device=dev)
         self.pair_w = torch.zeros(cap, dtype=torch.float32, device=dev)
@@ -122,7 +138,8 @@ class ExpertParallelDecoder:
         mine = local_experts(rank, sh.num_experts, world)
         self.expert_lo, self.expert_hi = (mine[0], mine[-1] + 1) if mine else (0, 0)
         self.grouped_launches = (cap + PAIRS_PER_LAUNCH - 1) // PAIRS_PER_LAUNCH
-        self.launches_per_step = 2 + 2 * self.grouped_launches   # router, pair selection, (gate/up, down) per grouped launch
+        # router, pair selection, (gate/up, down) per grouped launch, the row sum of the all-to-all form
+        self.launches_per_step = 2 + 2 * self.grouped_launches + (1 if self.collectives == "a2a" else 0)
 
     def step(self, layer: int, x: torch.Tensor) -> torch.Tensor:
         """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
@@ -140,7 +157,7 @@ class ExpertParallelDecoder:
                                sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, dec.exact_order, dec.workspace)
 
     def gather(self) -> None:
-        gather_messages(self.send, self.recv, self.world, self.group)
+        gather_messages(self.send, self.recv, self.world, self.group, self.send_rep)
 
     def experts(self, layer: int) -> None:
         from . import kernels
@@ -158,7 +175,7 @@ class ExpertParallelDecoder:
                 sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status)
 
     def combine(self) -> torch.Tensor:
-        combine_partials(self.out, self.partial, self.rank, self.world, self.group)
+        combine_partials(self.out, self.partial, self.rank, self.world, self.group, self.partial_in)
         return self.out
 
     def routing(self):
@@ -307,7 +324,7 @@ def bench_main(args) -> None:
                        "hidden": sh.hidden, "experts": sh.num_experts, "experts_per_gpu": sh.num_experts // world,
                        "top_k": sh.top_k, "shared_experts": 1, "intermediate": sh.intermediate, "tokens_per_step": world,
                        "physical_layers": layers, "launch_mode": mode, "l2_policy": "inputs larger than L2: layers and tokens rotate",
-                       "parallelism": f"ep{world}: all_gather(token, routing) + reduce_scatter(partial sums), NCCL"},
+                       "parallelism": f"ep{world}: exchange of (token, routing) + exchange and sum of partial sums, NCCL ({ep.collectives})"},
             "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": world * sh.hidden * 2,
                     "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms / K},
             "gpu_launches": K * ep.launches_per_step * world,

@@ -180,6 +180,12 @@ def select_local_pairs(ids, ids_stride_bytes: int, weights, weights_stride_bytes
         _ptr(pair_experts), _ptr(pair_weights), _ptr(pair_tokens), capacity, _ptr(count_out), _stream(stream)))
 
 
+def sum_rows_f32(rows_in: torch.Tensor, out: torch.Tensor, stream: Optional[int] = None) -> None:
+    """out[c] = sum_r rows_in[r, c], rows added in order."""
+    check("sum_rows_f32", lib().vib3_launch_sum_rows_f32(_ptr(rows_in), rows_in.shape[0], rows_in.shape[1], rows_in.stride(0),
+                                                         _ptr(out), _stream(stream)))
+
+
 def select_local_experts(ids, weights, top_k: int, expert_lo: int, expert_hi: int, ids_out, weights_out, count_out,
                          stream: Optional[int] = None) -> None:
     check("select_local_experts", lib().vib3_launch_select_local_experts(
