@@ -147,6 +147,21 @@ int vib3_launch_moe_layer_int4_paged_var(const void* x, int x_dtype, const void*
                                          int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
                                          int rows_per_page_down, int group_size, int* status, void* stream,
                                          const int* num_active_dev);
+/* One token through one MoE sublayer from and to HOST memory: copies the token in, launches the router
+ * and the two expert kernels and waits for the stream — the only entry point here that copies or
+ * synchronises (the reference's engine does the same around its launches, src/runtime/engine.rs:
+ * 5052-5360).  x_host: ordinary or pinned host memory.  If out_dev is null, out_host must be
+ * device-addressable (pinned) memory and the last kernel stores the result into it directly;
+ * otherwise the kernels write out_dev and a device-to-host copy follows.  x_dev: device scratch for
+ * the token.  Other arguments as for vib3_launch_router_topk_ex / vib3_launch_moe_layer_int4_paged. */
+int vib3_moe_layer_step_host(const void* x_host, int x_dtype, void* x_dev, const void* router_w, int w_dtype,
+                             float* scores_buf, const float* bias_or_null, unsigned short* ids_dev, float* weights_dev,
+                             int num_experts, int top_k, int scoring_mode, float scaling_factor, int normalize,
+                             int exact_order, unsigned int* workspace, const void* page_table,
+                             const void* shared_pages, float shared_weight, void* act_scratch, float* out_dev_or_null,
+                             float* out_host, int hidden_dim, int expert_hidden_dim, int pages_per_segment,
+                             int rows_per_page_gate_up, int rows_per_page_down, int group_size, int* status,
+                             void* stream);
 /* Grouped form for expert parallelism: one launch pair for the (token, expert) pairs of SEVERAL tokens
  * that this GPU owns.  pair_experts / pair_weights / pair_tokens: device lists in ascending token order
  * (as vib3_launch_select_local_pairs writes them), *num_pairs_dev their length; this launch takes the

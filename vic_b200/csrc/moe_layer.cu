@@ -352,6 +352,49 @@ extern "C" int vib3_launch_moe_layer_int4_paged_var(VIB3_MOE_ARGS, const int* nu
     return moe_layer_dispatch(3, num_active_dev, VIB3_MOE_PASS);
 }
 
+extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
+                                          const float* bias, const float* logit_offset, unsigned short* out_ids,
+                                          float* out_weights, int hidden_dim, int num_experts, int top_k, int scoring_mode,
+                                          float scaling_factor, int normalize, int exact_order, unsigned int* workspace,
+                                          void* stream);  // router.cu
+
+// One token through one MoE sublayer FROM AND TO HOST MEMORY: copies the token to the device, launches
+// the router and the two expert kernels, and waits for the stream.  The only entry point of this library
+// that copies or synchronises.  x_host: hidden_dim values of x_dtype in ordinary or pinned host memory.
+// The result goes to out_host: if out_dev is null, out_host must be device-addressable (pinned) memory
+// and the last kernel stores into it directly; otherwise the kernels write out_dev and a copy follows.
+// All other arguments as for vib3_launch_router_topk_ex and vib3_launch_moe_layer_int4_paged.
+extern "C" int vib3_moe_layer_step_host(const void* x_host, int x_dtype, void* x_dev, const void* router_w, int w_dtype,
+                                        float* scores_buf, const float* bias, unsigned short* ids_dev, float* weights_dev,
+                                        int num_experts, int top_k, int scoring_mode, float scaling_factor, int normalize,
+                                        int exact_order, unsigned int* workspace, const void* page_table,
+                                        const void* shared_pages, float shared_weight, void* act_scratch, float* out_dev,
+                                        float* out_host, int hidden_dim, int expert_hidden_dim, int pages_per_segment,
+                                        int rows_per_page_gate_up, int rows_per_page_down, int group_size, int* status,
+                                        void* stream) {
+    if (!x_host || !x_dev || !out_host) return VIB3_ERR_NULL;
+    if (x_dtype < X_F32 || x_dtype > X_BF16 || hidden_dim <= 0) return VIB3_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t xbytes = (size_t)hidden_dim * (x_dtype == X_F32 ? 4 : 2);
+    cudaError_t ce = cudaMemcpyAsync(x_dev, x_host, xbytes, cudaMemcpyHostToDevice, st);
+    if (ce != cudaSuccess) return (int)ce;
+    int err = vib3_launch_router_topk_ex(x_dev, x_dtype, router_w, w_dtype, scores_buf, bias, nullptr, ids_dev, weights_dev,
+                                         hidden_dim, num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order,
+                                         workspace, stream);
+    if (err) return err;
+    float* out = out_dev ? out_dev : out_host;
+    err = moe_layer_dispatch(3, nullptr, x_dev, x_dtype, page_table, num_experts, shared_pages, ids_dev, weights_dev, top_k,
+                             shared_weight, act_scratch, out, 0, hidden_dim, expert_hidden_dim, pages_per_segment,
+                             rows_per_page_gate_up, rows_per_page_down, group_size, status, stream);
+    if (err) return err;
+    if (out_dev) {
+        ce = cudaMemcpyAsync(out_host, out_dev, (size_t)hidden_dim * sizeof(float), cudaMemcpyDeviceToHost, st);
+        if (ce != cudaSuccess) return (int)ce;
+    }
+    ce = cudaStreamSynchronize(st);
+    return ce == cudaSuccess ? 0 : (int)ce;
+}
+
 // Grouped form for expert parallelism: the routed slots are (token, expert) pairs of several tokens in
 // ascending token order (vib3_launch_select_local_pairs makes such a list); x has n_tokens rows
 // x_stride_bytes apart, out has n_tokens rows out_stride floats apart.  This launch takes the pairs

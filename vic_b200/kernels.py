@@ -180,6 +180,25 @@ def select_local_pairs(ids, ids_stride_bytes: int, weights, weights_stride_bytes
         _ptr(pair_experts), _ptr(pair_weights), _ptr(pair_tokens), capacity, _ptr(count_out), _stream(stream)))
 
 
+def moe_layer_step_host(x_host: torch.Tensor, x_dev: torch.Tensor, router_w: torch.Tensor, scores_buf, bias, ids_dev, weights_dev,
+                        num_experts: int, top_k: int, scoring_mode: int, scaling_factor: float, normalize: bool,
+                        exact_order: bool, workspace, page_table: int, shared_pages: int, shared_weight: float, act_scratch,
+                        out_dev, out_host: torch.Tensor, hidden_dim: int, expert_hidden_dim: int, pages_per_segment: int,
+                        rows_per_page_gate_up: int, rows_per_page_down: int, status=None, stream: Optional[int] = None) -> None:
+    """One token from and to host memory through one C call (copy in, router, experts, synchronise)."""
+    w_dtype = {torch.float16: W_F16, torch.float32: W_F32}[router_w.dtype]
+    if x_host.is_cuda or out_host.is_cuda:
+        raise ValueError("host tensors expected")
+    if out_dev is None and not out_host.is_pinned():
+        raise ValueError("out_host must be pinned when no device output buffer is given")
+    check("moe_layer_step_host", lib().vib3_moe_layer_step_host(
+        x_host.data_ptr(), x_dtype_code(x_host), _ptr(x_dev), _ptr(router_w), w_dtype, _ptr(scores_buf), _ptr(bias), _ptr(ids_dev),
+        _ptr(weights_dev), num_experts, top_k, scoring_mode, scaling_factor, int(normalize), int(exact_order), _ptr(workspace),
+        page_table, shared_pages or 0, shared_weight, _ptr(act_scratch), _ptr(out_dev), out_host.data_ptr(), hidden_dim,
+        expert_hidden_dim, pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status),
+        _stream(stream)))
+
+
 def sum_rows_f32(rows_in: torch.Tensor, out: torch.Tensor, stream: Optional[int] = None) -> None:
     """out[c] = sum_r rows_in[r, c], rows added in order."""
     check("sum_rows_f32", lib().vib3_launch_sum_rows_f32(_ptr(rows_in), rows_in.shape[0], rows_in.shape[1], rows_in.stride(0),

@@ -63,6 +63,8 @@ SIGNATURES = {
     "vib3_launch_moe_layer_int4_paged_grouped": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _f, _vp,
                                                       _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "vib3_launch_select_local_pairs": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
+    "vib3_moe_layer_step_host": (_i, [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _f, _vp,
+                                      _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "vib3_launch_sum_rows_f32": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "vib3_launch_select_local_experts": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "vib3_config_set": (_i, [_i, _i]),
