@@ -12,9 +12,9 @@ and every step has its own token, so no weight byte is re-read before 4 x 234 MB
 traffic went through the 126 MB L2.  Data is seeded synthetic (no checkpoint, no dataset).
 
 Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM (CUDA-graph
-replay, CUDA events); `e2e` = the same through host buffers (MoeDecoder.forward_host = the C call
-vib3_moe_layer_step_host: H2D of the token, the three launches, the fp32 layer output written by the
-last kernel straight into pinned host memory, one stream synchronisation, every step); `roofline` = the dominant kernel (gate/up) timed alone with CUDA
+replay, CUDA events); `e2e` = the same through host buffers (MoeDecoder.forward_host: pinned H2D of
+the token and the three launches as one CUDA graph, the fp32 layer output written by the last kernel
+straight into pinned host memory, one stream synchronisation, every step); `roofline` = the dominant kernel (gate/up) timed alone with CUDA
 events against the measured HBM copy bandwidth; `cpu_baseline` = the CPU restatement of the
 reference's kernels (oracle/) on this host's cores over a bounded sample.
 """
@@ -375,8 +375,10 @@ def main():
             variants["down_direct"] = time_kernel(lambda i: phase_launch(i, 2))
             _lib().vib3_config_set(0, 1)
 
-        # ── e2e: host buffers every step, through the host-to-host C call (copy in from pinned memory,
-        # router, gate/up, down storing into pinned host memory, one synchronisation) ──
+        # ── e2e: host buffers every step, through the public host-to-host call (one CUDA graph per
+        # layer: copy in from pinned memory, router, gate/up, down storing into pinned host memory; one
+        # synchronisation).  The single C call vib3_moe_layer_step_host does the same without a graph
+        # and measures about 4 us slower per token. ──
         x_host = [xs[i].cpu().pin_memory() for i in range(N_TOKENS)]
         checksum = 0.0
 

@@ -102,6 +102,8 @@ def test_host_to_host_step_equals_device_step(cuda_dev):
             xh = xh.pin_memory()
         got = dec.forward_host(0, xh)
         assert got.is_pinned() and torch.equal(got, want)
+        got2 = dec.forward_host_call(0, xh)      # the single C call with host pointers
+        assert got2.is_pinned() and torch.equal(got2, want)
     assert int(dec.status.item()) == 0
 
 
