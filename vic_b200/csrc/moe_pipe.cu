@@ -23,8 +23,11 @@ namespace vib3 {
 // ── gate/up + SiLU, staged ─────────────────────────────────────────────────────────────────
 // stage layout: [gate codes R*K/2][up codes R*K/2][gate scales R*K/16][up scales R*K/16]
 // NCH = chunks per lane when K/32 is a multiple of 32 (fully unrolled, constant offsets), 0 = any K.
+// At most 80 registers per thread: with more, a CTA of this kernel (17 warps) and a router CTA (8 warps
+// of 48 registers) no longer fit in an SM's register file together, and the first pass cannot run beside
+// the router (measured: 59 us per step instead of 56).
 template <int NCH>
-__global__ void __launch_bounds__(kPipeThreads, 1) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstages) {
+__global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstages) {
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nchunks = a.H / kGroupSize;
