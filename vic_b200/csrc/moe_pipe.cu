@@ -373,11 +373,13 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             if (!ok) break;
             unsigned char* sb = stages + (size_t)st * stage_bytes;
             // slots lane / 2 and (the 17th slot) 16 + lane / 2
-            PageEntry e[2];
-            unsigned bytes[2] = {0u, 0u};
+            constexpr int kHalves = kDyn ? 2 : 1;  // a launch of fixed shape has at most 9 slots
+            PageEntry e[kHalves];
+            unsigned bytes[kHalves];
             unsigned tx = 0;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < kHalves; ++u) {
+                bytes[u] = 0u;
                 if (u == 1 && slots <= 16) break;  // (the same for every lane)
                 const int s = u * 16 + (lane >> 1);
                 e[u] = PageEntry{0, 0, 0, 0};
@@ -394,7 +396,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             }
             __syncwarp();
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < kHalves; ++u) {
                 if (bytes[u]) {
                     const int s = u * 16 + (lane >> 1);
                     const unsigned char* base = reinterpret_cast<const unsigned char*>(e[u].ptr);
