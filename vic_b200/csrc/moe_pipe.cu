@@ -265,7 +265,8 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
 // up to the depth of the rings, and loads, integer math and shuffles of different warps overlap.
 // stage layout: per slot [codes R*I/2][scales R*I/16], R = kDownRows.
 // Two shapes (template parameters R = rows per tile, WPS = warps per slot): up to 9 slots R = 6, WPS = 2
-// (measured on the Kimi shape with 9 slots: 4 rows 20.7 us, 6 rows 17.3 us, 8 rows 18.5 us); 10 to 17
+// (measured on the Kimi shape with 9 slots: 4 rows 20.7 us, 5 rows 18.2 us, 6 rows 17.3-18.0 us, 8 rows
+// 18.5 us; VIB3_DOWN_ROWS rebuilds the fixed shape with another height); 10 to 17
 // slots — the grouped launches of expert parallelism — R = 4, WPS = 1, so that two stages still fit.
 // In grouped mode (MoeLayerArgs::slot_token) the slots are (token, expert) pairs in ascending token
 // order and the combiner writes one output row per token.
@@ -620,15 +621,18 @@ int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
         return nchunks == 64 ? launch_down_pipe_t<2, 0, 0>(a, st, ring, kSmemBudget, grid, kDownMaxThreads)
                              : launch_down_pipe_t<1, 0, 0>(a, st, ring, kSmemBudget, grid, kDownMaxThreads);
     }
-    const int rows = 6, wps = 2;
+#ifndef VIB3_DOWN_ROWS
+#define VIB3_DOWN_ROWS 6
+#endif
+    constexpr int rows = VIB3_DOWN_ROWS, wps = 2;
     const size_t stage_bytes = (size_t)slots * rows * row_bytes;
     const int nstages = pick_stages(fixed, stage_bytes, 2);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
     const size_t smem = fixed + (size_t)nstages * stage_bytes;
     const int grid = min(sm_count(), (a.H + rows - 1) / rows);
     const int threads = (slots * wps + 2) * 32;
-    return nchunks == 64 ? launch_down_pipe_t<2, 6, 2>(a, st, nstages, smem, grid, threads)
-                         : launch_down_pipe_t<1, 6, 2>(a, st, nstages, smem, grid, threads);
+    return nchunks == 64 ? launch_down_pipe_t<2, rows, wps>(a, st, nstages, smem, grid, threads)
+                         : launch_down_pipe_t<1, rows, wps>(a, st, nstages, smem, grid, threads);
 }
 
 }  // namespace vib3
