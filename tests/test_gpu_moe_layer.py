@@ -325,6 +325,32 @@ def test_grouped_pairs_equal_per_token_launches_bit_for_bit(cuda_dev, name, T, l
     assert torch.equal(got, want), (name, T, total)
 
 
+def test_sum_rows_and_pair_list_overflow(cuda_dev):
+    """Helpers of the expert-parallel step: the row sum adds in row order (bit-exact against the same
+    additions in torch); the pair selection reports the full count even when the lists are too short."""
+    from vic_b200 import kernels
+    g = torch.Generator(device=cuda_dev).manual_seed(3)
+    rows = torch.randn(5, 1000, generator=g, device=cuda_dev)[:, :996]      # stride 1000, 996 columns
+    out = torch.zeros(996, device=cuda_dev)
+    kernels.sum_rows_f32(rows, out)
+    want = rows[0].clone()
+    for r in range(1, 5):
+        want = want + rows[r]
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    ids = torch.arange(32, dtype=torch.int16, device=cuda_dev).view(4, 8).contiguous()
+    ws = torch.arange(32, dtype=torch.float32, device=cuda_dev).view(4, 8).contiguous()
+    pe = torch.full((6,), -1, dtype=torch.int16, device=cuda_dev)
+    pw = torch.zeros(6, dtype=torch.float32, device=cuda_dev)
+    pt = torch.zeros(6, dtype=torch.int16, device=cuda_dev)
+    cnt = torch.zeros(1, dtype=torch.int32, device=cuda_dev)
+    kernels.select_local_pairs(ids, 16, ws, 32, 4, 8, 4, 28, pe, pw, pt, 6, cnt)   # experts 4..27 are local: 24 pairs
+    torch.cuda.synchronize()
+    assert int(cnt.item()) == 24
+    assert pe.cpu().tolist() == [4, 5, 6, 7, 8, 9] and pt.cpu().tolist() == [0, 0, 0, 0, 1, 1]
+    assert pw.cpu().tolist() == [4.0, 5.0, 6.0, 7.0, 8.0, 9.0]
+
+
 def test_fused_launcher_refusals(cuda_dev):
     from vic_b200.lib import lib
     L = lib()
