@@ -413,7 +413,7 @@ def main():
         "roofline": {"bound": "hbm", "kernel": "moe_gateup_pipe_kernel (gate/up + SiLU, 9 experts)", "achieved": achieved,
                      "peak": peak, "peak_source": f"of {peak_kind} (MEASURED_PEAKS.json hbm_gbs, burst)", "unit": "GB/s",
                      "frac": achieved / peak, "bytes_per_launch": b_gu, "us_per_launch": k_us,
-                     "traffic": 153.46e6, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same shape (profiles/moe_gateup_down_kimi_batch1.md)"},
+                     "traffic": 153.06e6, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same shape (profiles/moe_gateup_down_kimi_batch1.md)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": sh.hidden * 2, "d2h_bytes_per_step": sh.hidden * 4,
                 "ms_per_step": e2e_ms / K},
         "kernel_us": {"router": router_us, "gate_up": k_us, "down": down_us,
