@@ -85,9 +85,9 @@ int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_
  * logit_offset: added to the logit before scoring.  scores_buf: 3 * num_experts floats; the first
  * num_experts receive the logits, the rest is scratch.
  * exact_order != 0 makes the selected indices equal to those of the reference's CPU router
- * (sequential fp32 summation) even for near-tied experts.  workspace: two uint32, zero before
- * the first call; [0] is left zero by every call, [1] counts near-tie recomputations; calls
- * sharing a workspace must not overlap. */
+ * (sequential fp32 summation) even for near-tied experts.  workspace: four uint32, zero before
+ * the first call; [0] is left zero by every call, [1] counts near-tie recomputations, [2] and [3] are
+ * used by vib3_launch_moe_layer_routed_int4_paged; calls sharing a workspace must not overlap. */
 int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
                                const float* bias_or_null, const float* logit_offset_or_null,
                                unsigned short* out_ids, float* out_weights,
@@ -120,6 +120,27 @@ int vib3_launch_moe_layer_int4_paged(const void* x, int x_dtype, const void* pag
                                      void* act_scratch, float* out, int out_accumulate, int hidden_dim,
                                      int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
                                      int rows_per_page_down, int group_size, int* status, void* stream);
+
+/* Router and experts of one token in one call; the routing (ids_out u16[top_k], weights_out f32[top_k],
+ * device) is an OUTPUT, written for the caller and for the kernels that follow.  Replaces
+ * run_router_gpu_topk_nosync (src/compute/kernels.rs:1890-1953) followed by the per-page expert sequence
+ * (src/runtime/engine.rs:6094-6107, :6215-6223, :6290-6296).  Where the shapes allow (hidden and expert
+ * dimensions multiples of 256, a router row no larger than a ring stage) the gate/up kernel streams the
+ * router's rows through its own ring and selects in its prologue — two launches for the layer and no idle
+ * memory pipe while the router's serial tail runs; otherwise the router is launched first.  Router
+ * arguments as for vib3_launch_router_topk_ex (workspace: four uint32, zero before the first call; [0]
+ * and [2] are left zero), layer arguments as for vib3_launch_moe_layer_int4_paged.  The launch may
+ * follow the kernel that produces x with programmatic dependent launch. */
+int vib3_launch_moe_layer_routed_int4_paged(const void* x, int x_dtype, const void* router_w, int w_dtype,
+                                            float* scores_buf, const float* bias_or_null,
+                                            const float* logit_offset_or_null, unsigned short* ids_out,
+                                            float* weights_out, int num_experts, int top_k, int scoring_mode,
+                                            float scaling_factor, int normalize, int exact_order,
+                                            unsigned int* workspace, const void* page_table,
+                                            const void* shared_pages, float shared_weight, void* act_scratch,
+                                            float* out, int out_accumulate, int hidden_dim, int expert_hidden_dim,
+                                            int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down,
+                                            int group_size, int* status, void* stream);
 
 /* The two halves of vib3_launch_moe_layer_int4_paged as separate launches, same arguments: the
  * first writes act_scratch (out is not touched), the second reads it and writes out. */
@@ -202,9 +223,11 @@ int vib3_launch_select_local_experts(const unsigned short* ids, const float* wei
  * after warm-up, no allocator in the binding).  This entry point has no counterpart in the
  * reference.  The intermediate lives in a 544 KiB array inside the library image, held by every GPU
  * the library is loaded on.  Limit: (top_k + 1 if shared_pages) * expert_hidden_dim <= 278,528, else
- * VIB3_ERR_CAPACITY and nothing is launched.  The first call on a device resolves the array's
- * address: issue it before any stream capture.  All calls on a device share the array; calls whose
- * kernels may overlap on the GPU race on it.  Nothing is allocated or freed. */
+ * VIB3_ERR_CAPACITY and nothing is launched.  The first call on a device loads the array onto that
+ * device (lazy module loading: 544 KiB are reserved then, and the call fails with the runtime's
+ * out-of-memory code if they are not free) and resolves its address: issue it before any stream
+ * capture and before free VRAM is handed to a pool.  All calls on a device share the array; calls whose
+ * kernels may overlap on the GPU race on it.  Nothing is allocated or freed by this entry point. */
 int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const void* page_table, int num_experts,
                                              const void* shared_pages, const unsigned short* expert_ids,
                                              const float* expert_weights, int top_k, float shared_weight,
@@ -215,10 +238,9 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
 
 /* Library options.  key 0: use the bulk-copy staged MoE kernels where the shape allows (default 1);
  * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
- * launch so that their prologue overlaps the previous kernel's tail (default 1).  key 2: router
- * load-batching variant (0 default: 14 loads per batch, 1: whole row in one batch, 2: two batches).
- * key 3: KB of shared memory per SM that the gate/up kernel leaves to a co-resident router CTA
- * (default 46; 0: largest ring, no overlap with the router).  Returns the previous value. */
+ * launch so that their prologue overlaps the previous kernel's tail (default 1).  The switches are
+ * atomics: a launch running concurrently on another thread sees the old or the new value.  Returns
+ * the previous value, or VIB3_ERR_UNSUPPORTED for an unknown key. */
 int vib3_config_set(int key, int value);
 
 /* ── Host side: VRAM page pool and query planner (C view of the C++ classes) ────────────── */

@@ -58,7 +58,19 @@ def lib() -> ctypes.CDLL:
         _lib.vo_page_key.argtypes = [ctypes.c_uint16] * 4
         _lib.vo_router_select.restype = ctypes.c_int
         _lib.vo_router.restype = ctypes.c_int
+        _lib.vo_set_num_threads.restype = ctypes.c_int
+        _lib.vo_set_num_threads.argtypes = [ctypes.c_int]
+        _lib.vo_build_flags.restype = ctypes.c_char_p
     return _lib
+
+
+def set_num_threads(n: int = 0) -> int:
+    """Use n OpenMP threads for the row loops (0: leave as is); returns the count in force."""
+    return int(lib().vo_set_num_threads(int(n)))
+
+
+def build_flags() -> str:
+    return lib().vo_build_flags().decode()
 
 
 def _p(a: Optional[np.ndarray]):

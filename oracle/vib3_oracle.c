@@ -23,7 +23,30 @@
 #include <stdlib.h>
 #include <string.h>
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
 #define VO_API __attribute__((visibility("default")))
+
+/* Row parallelism of the timed CPU baseline: the number of OpenMP threads the row loops use (the
+ * reference's rayon pool takes every core).  A launcher that exports OMP_NUM_THREADS=1 to its children
+ * would otherwise pin the baseline to one core.  Returns the thread count now in force. */
+VO_API int vo_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
+/* The compiler flags this file was built with (recorded beside the timed baseline). */
+#ifndef VO_CFLAGS
+#define VO_CFLAGS "unknown"
+#endif
+VO_API const char* vo_build_flags(void) { return VO_CFLAGS; }
 
 /* ── 16-bit float helpers (crate `half` 2.7.1 semantics: IEEE round-to-nearest-even) ── */
 

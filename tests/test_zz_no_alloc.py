@@ -58,5 +58,34 @@ def test_noalloc_rejects_oversized_request_without_launching(cuda_dev):
     rc = lib().vib3_launch_moe_layer_int4_paged_noalloc(p, 2, p, 8, p, p, p, 16, 1.0, p, 0, 256, 32768, 1, 32768, 256, 32, None, None)
     assert rc == -8
     rc = lib().vib3_launch_moe_layer_int4_paged_noalloc(p, 2, p, 8, None, p, p, -1, 1.0, p, 0, 256, 512, 1, 512, 256, 32, None, None)
-    assert rc == -5
+    assert rc == -2      # the code vib3_launch_moe_layer_int4_paged gives for a negative count
+    # the limit itself: 17 slots of 16384 values are exactly the array (accepted as far as the capacity check
+    # goes: the call is then refused for its null output, -3, before anything is launched); one value more is not
+    rc = lib().vib3_launch_moe_layer_int4_paged_noalloc(p, 2, p, 8, p, p, p, 16, 1.0, None, 0, 256, 16384, 1, 16384, 256, 32, None, None)
+    assert rc == -3
+    rc = lib().vib3_launch_moe_layer_int4_paged_noalloc(p, 2, p, 8, None, p, p, 1, 1.0, p, 0, 256, 278529, 1, 278529, 256, 32, None, None)
+    assert rc == -8
     torch.cuda.synchronize()
+
+
+def test_noalloc_without_shared_expert(cuda_dev):
+    """No shared expert: the slots are the routed experts alone (a different layout of the built-in array)."""
+    from vic_b200.core_types import SCORING_SOFTMAX, MoeShape
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import build_synthetic_moe, synth_activation
+    sh = MoeShape("noalloc-noshared", 512, 1024, 8, 2, 0, SCORING_SOFTMAX, 1.0, True)
+    model = build_synthetic_moe(sh, 1, cuda_dev, seed=22, slot_seed=6)
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(4)
+    xs = synth_activation(sh, g, cuda_dev, torch.float16, 2)
+    out_a = torch.zeros(sh.hidden, dtype=torch.float32, device=cuda_dev)
+    out_b = torch.full((sh.hidden,), -3.0, dtype=torch.float32, device=cuda_dev)
+    for t in range(2):
+        dec.route(0, xs[t])
+        dec.experts(0, xs[t], out=out_a)
+        assert _call_noalloc(dec, 0, xs[t], out_b) == 0
+        torch.cuda.synchronize()
+        assert int(dec.status.item()) == 0
+        a, b = out_a.cpu().numpy(), out_b.cpu().numpy()
+        assert np.max(np.abs(a - b)) <= 2e-2 and np.linalg.norm(a - b) <= 1e-3 * np.linalg.norm(a)
+        assert torch.equal(out_a, out_b)

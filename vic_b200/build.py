@@ -29,11 +29,7 @@ NVCC_FLAGS = [
 
 
 def _sources():
-    out = [os.path.join(CSRC, s) for s in SOURCES]
-    extra = os.path.join(CSRC, "extra_sources.txt")
-    if os.path.exists(extra):
-        out += [os.path.join(CSRC, l.strip()) for l in open(extra) if l.strip() and not l.startswith("#")]
-    return out
+    return [os.path.join(CSRC, s) for s in SOURCES]
 
 
 def needs_build() -> bool:

@@ -2,6 +2,7 @@
 #pragma once
 #include "int4_math.cuh"
 #include "launch_common.h"
+#include <atomic>
 
 namespace vib3 {
 
@@ -59,7 +60,7 @@ __device__ __forceinline__ int act_slot(const MoeLayerArgs& a, int s) {
 // Resolve the page-table block ([3][P] entries) of slot s: routed expert or the shared expert.
 __device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, int s) {
     if (s < a.top_k) {
-        unsigned e = a.expert_ids[s];
+        unsigned e = __ldcg(a.expert_ids + s);  // (from L2: the router may have stored it moments ago)
         if (e >= (unsigned)a.num_experts) return nullptr;
         return a.page_table + (size_t)e * 3 * a.P;
     }
@@ -70,15 +71,17 @@ __device__ __forceinline__ const PageEntry* slot_pages(const MoeLayerArgs& a, in
 // Pipelined (bulk-copy staged) variants, defined in moe_pipe.cu.  They return VIB3_ERR_UNSUPPORTED
 // without launching when the shape does not meet their alignment rules; the caller then uses the
 // direct-load kernels.
-int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st);
+struct RouterArgs;
+int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st, const RouterArgs* router = nullptr);
 int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st);
 int sm_count();
 
 // Run-time switch: 1 (default) = staged kernels where the shape allows, 0 = direct-load kernels only.
-extern int g_use_pipeline;
+extern std::atomic<int> g_use_pipeline;
 // 1 (default) = staged kernels are launched with programmatic dependent launch.
-extern int g_use_pdl;
-// Shared memory (KB) the gate/up kernel leaves free on an SM so that a router CTA fits beside it.
-extern int g_router_cta_smem_kb;
+extern std::atomic<int> g_use_pdl;
+// Shared memory the gate/up kernel leaves free on an SM so that a router CTA (43 KB static plus the
+// per-CTA reservation) fits beside it.
+constexpr size_t kRouterCtaSmem = 46 * 1024;
 
 }  // namespace vib3

@@ -14,6 +14,7 @@
 // src/core/types.rs:204).  The experts of the token are read from device memory (router
 // output), so no host synchronisation sits between the router and the experts.
 #include "moe_common.cuh"
+#include "router_core.cuh"
 
 namespace vib3 {
 
@@ -211,8 +212,8 @@ int sm_count() {
     return n;
 }
 
-int g_use_pipeline = 1;
-int g_use_pdl = 1;
+std::atomic<int> g_use_pipeline{1};
+std::atomic<int> g_use_pdl{1};
 
 template <class K>
 static int ensure_smem(K kernel, size_t bytes) {
@@ -246,9 +247,17 @@ static int launch_down(const MoeLayerArgs& a, cudaStream_t st) {
 
 }  // namespace vib3
 
+namespace vib3 {
+int make_router_args(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf, const float* bias,
+                     const float* logit_offset, unsigned short* out_ids, float* out_weights, int hidden_dim, int num_experts,
+                     int top_k, int scoring_mode, float scaling_factor, int normalize, int exact_order,
+                     unsigned int* workspace, RouterArgs& a);  // router.cu
+int launch_router_args(const RouterArgs& a, cudaStream_t st);  // router.cu
+}  // namespace vib3
+
 using namespace vib3;
 
-static int moe_layer_dispatch(int phases, const int* num_active_dev, const void* x, int x_dtype, const void* page_table, int num_experts,
+static int moe_layer_dispatch(int phases, const int* num_active_dev, const RouterArgs* router, const void* x, int x_dtype, const void* page_table, int num_experts,
                               const void* shared_pages, const unsigned short* expert_ids, const float* expert_weights,
                               int top_k, float shared_weight, void* act_scratch, float* out, int out_accumulate,
                               int hidden_dim, int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up,
@@ -277,13 +286,21 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, const void*
     a.slot_token = nullptr; a.n_tokens = 1; a.shared_token = 0; a.x_stride = 0; a.out_stride = 0; a.slot_begin = 0;
     cudaStream_t st = (cudaStream_t)stream;
 
+    const bool use_pipe = g_use_pipeline.load(std::memory_order_relaxed) != 0;
     int err = 0;
-    if ((phases & 1) && g_use_pipeline) {
+    if (router) {
+        // the gate/up kernel routes the token itself where the shapes allow; otherwise the router is a launch of its own
+        err = ((phases & 1) && use_pipe) ? launch_gateup_pipelined(a, st, router) : VIB3_ERR_UNSUPPORTED;
+        if (err == 0) phases &= ~1;
+        else if (err != VIB3_ERR_UNSUPPORTED) return err;
+        else if ((err = launch_router_args(*router, st)) != 0) return err;
+    }
+    if ((phases & 1) && use_pipe) {
         err = launch_gateup_pipelined(a, st);
         if (err == 0) phases &= ~1;
         else if (err != VIB3_ERR_UNSUPPORTED) return err;
     }
-    if ((phases & 2) && !(phases & 1) && g_use_pipeline) {
+    if ((phases & 2) && !(phases & 1) && use_pipe) {
         err = launch_down_pipelined(a, st);
         if (err == 0) phases &= ~2;
         else if (err != VIB3_ERR_UNSUPPORTED) return err;
@@ -317,46 +334,42 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, const void*
         rows_per_page_down, group_size, status, stream
 
 // key 0: staged (bulk-copy) kernels on/off; key 1: programmatic dependent launch of the staged
-// kernels on/off; key 2: router load-batching variant (0 default, 1, 2).  Returns the previous
-// value, or VIB3_ERR_UNSUPPORTED.
-extern "C" int vib3_router_config_set(int value);  // router.cu
-
+// kernels on/off.  Atomic exchanges: safe against concurrent launches from other threads (a launch
+// sees the old or the new value).  Returns the previous value, or VIB3_ERR_UNSUPPORTED.
 extern "C" int vib3_config_set(int key, int value) {
-    if (key == 0) {
-        const int old = g_use_pipeline;
-        g_use_pipeline = value ? 1 : 0;
-        return old;
-    }
-    if (key == 1) {
-        const int old = g_use_pdl;
-        g_use_pdl = value ? 1 : 0;
-        return old;
-    }
-    if (key == 2) return vib3_router_config_set(value);
-    if (key == 3) {
-        const int old = g_router_cta_smem_kb;
-        if (value < 0 || value > 160) return VIB3_ERR_UNSUPPORTED;
-        g_router_cta_smem_kb = value;
-        return old;
-    }
+    if (key == 0) return g_use_pipeline.exchange(value ? 1 : 0);
+    if (key == 1) return g_use_pdl.exchange(value ? 1 : 0);
     return VIB3_ERR_UNSUPPORTED;
 }
 
-extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, nullptr, VIB3_MOE_PASS); }
-extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, nullptr, VIB3_MOE_PASS); }
-extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(2, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_layer_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(3, nullptr, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_gate_up_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(1, nullptr, nullptr, VIB3_MOE_PASS); }
+extern "C" int vib3_launch_moe_down_int4_paged(VIB3_MOE_ARGS) { return moe_layer_dispatch(2, nullptr, nullptr, VIB3_MOE_PASS); }
 // Same as vib3_launch_moe_layer_int4_paged, but only the first min(top_k, *num_active_dev) routed slots
 // are used (a device-side count, e.g. the experts of a token that are resident on this GPU).
 extern "C" int vib3_launch_moe_layer_int4_paged_var(VIB3_MOE_ARGS, const int* num_active_dev) {
     if (!num_active_dev) return VIB3_ERR_NULL;
-    return moe_layer_dispatch(3, num_active_dev, VIB3_MOE_PASS);
+    return moe_layer_dispatch(3, num_active_dev, nullptr, VIB3_MOE_PASS);
 }
 
-extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
-                                          const float* bias, const float* logit_offset, unsigned short* out_ids,
-                                          float* out_weights, int hidden_dim, int num_experts, int top_k, int scoring_mode,
-                                          float scaling_factor, int normalize, int exact_order, unsigned int* workspace,
-                                          void* stream);  // router.cu
+// Router and experts of one token: the routing (ids, weights; device) is an OUTPUT.  Where the shapes allow,
+// the gate/up kernel routes the token in its own prologue (two launches for the layer); otherwise the router
+// is launched first (three).  workspace: four 32-bit words, zero before the first call and left zero at
+// [0] and [2]; calls that share one must not overlap on the GPU.  scores_buf: 3 * num_experts floats.
+extern "C" int vib3_launch_moe_layer_routed_int4_paged(
+    const void* x, int x_dtype, const void* router_w, int w_dtype, float* scores_buf, const float* bias,
+    const float* logit_offset, unsigned short* ids_out, float* weights_out, int num_experts, int top_k, int scoring_mode,
+    float scaling_factor, int normalize, int exact_order, unsigned int* workspace, const void* page_table,
+    const void* shared_pages, float shared_weight, void* act_scratch, float* out, int out_accumulate, int hidden_dim,
+    int expert_hidden_dim, int pages_per_segment, int rows_per_page_gate_up, int rows_per_page_down, int group_size,
+    int* status, void* stream) {
+    RouterArgs r;
+    if (int e = make_router_args(x, x_dtype, router_w, w_dtype, scores_buf, bias, logit_offset, ids_out, weights_out, hidden_dim,
+                                 num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order, workspace, r)) return e;
+    return moe_layer_dispatch(3, nullptr, &r, x, x_dtype, page_table, num_experts, shared_pages, ids_out, weights_out, top_k,
+                              shared_weight, act_scratch, out, out_accumulate, hidden_dim, expert_hidden_dim, pages_per_segment,
+                              rows_per_page_gate_up, rows_per_page_down, group_size, status, stream);
+}
 
 // One token through one MoE sublayer FROM AND TO HOST MEMORY: copies the token to the device, launches
 // the router and the two expert kernels, and waits for the stream.  The only entry point of this library
@@ -378,14 +391,12 @@ extern "C" int vib3_moe_layer_step_host(const void* x_host, int x_dtype, void* x
     const size_t xbytes = (size_t)hidden_dim * (x_dtype == X_F32 ? 4 : 2);
     cudaError_t ce = cudaMemcpyAsync(x_dev, x_host, xbytes, cudaMemcpyHostToDevice, st);
     if (ce != cudaSuccess) return (int)ce;
-    int err = vib3_launch_router_topk_ex(x_dev, x_dtype, router_w, w_dtype, scores_buf, bias, nullptr, ids_dev, weights_dev,
-                                         hidden_dim, num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order,
-                                         workspace, stream);
-    if (err) return err;
     float* out = out_dev ? out_dev : out_host;
-    err = moe_layer_dispatch(3, nullptr, x_dev, x_dtype, page_table, num_experts, shared_pages, ids_dev, weights_dev, top_k,
-                             shared_weight, act_scratch, out, 0, hidden_dim, expert_hidden_dim, pages_per_segment,
-                             rows_per_page_gate_up, rows_per_page_down, group_size, status, stream);
+    int err = vib3_launch_moe_layer_routed_int4_paged(x_dev, x_dtype, router_w, w_dtype, scores_buf, bias, nullptr, ids_dev, weights_dev,
+                                                      num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order, workspace,
+                                                      page_table, shared_pages, shared_weight, act_scratch, out, 0, hidden_dim,
+                                                      expert_hidden_dim, pages_per_segment, rows_per_page_gate_up, rows_per_page_down,
+                                                      group_size, status, stream);
     if (err) return err;
     if (out_dev) {
         ce = cudaMemcpyAsync(out_host, out_dev, (size_t)hidden_dim * sizeof(float), cudaMemcpyDeviceToHost, st);
@@ -420,7 +431,7 @@ extern "C" int vib3_launch_moe_layer_int4_paged_grouped(
     if (out_stride < hidden_dim || x_stride_bytes <= 0) return VIB3_ERR_SHAPE;
     if (((uintptr_t)x & 15) || (x_stride_bytes & 15) || ((uintptr_t)page_table & 15) || ((uintptr_t)shared_pages & 15) ||
         ((uintptr_t)act_scratch & 15) || ((uintptr_t)out & 3)) return VIB3_ERR_ALIGN;
-    if (!g_use_pipeline) return VIB3_ERR_UNSUPPORTED;
+    if (!g_use_pipeline.load(std::memory_order_relaxed)) return VIB3_ERR_UNSUPPORTED;
 
     MoeLayerArgs a;
     a.x = x; a.x_dtype = x_dtype;

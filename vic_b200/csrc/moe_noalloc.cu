@@ -8,15 +8,20 @@
 // caller still passes its inputs and its output; only the fp16 intermediate that travels from the
 // gate/up kernel to the down kernel comes from an array that is part of this library's image.
 //
-// The array is a file-scope __device__ array: every GPU on which the library is loaded keeps
-// kNoAllocMaxHalves * 2 bytes (544 KiB) for it until the process exits.  In host code its name is
-// only a handle, not a device address, so the address is asked for once per device with
-// cudaGetSymbolAddress (with that device current) and then passed to the kernels like any buffer.
+// The array is a file-scope __device__ array: every GPU on which this part of the library gets loaded
+// keeps kNoAllocMaxHalves * 2 bytes (544 KiB) for it until the process exits.  With the CUDA runtime's
+// lazy module loading that happens at the first call on a device, not when the library is opened: the
+// first call may therefore synchronise the device and, on a device without 544 KiB free, fails with
+// the runtime's out-of-memory error.  A caller that hands all free VRAM to a pool makes one call
+// (any valid arguments) BEFORE it sizes the pool.  In host code the array's name is only a handle, not
+// a device address, so the address is asked for once per device with cudaGetSymbolAddress (with that
+// device current) and then passed to the kernels like any buffer.
 //
 // Rules for callers:
 //   * (top_k + 1 if a shared expert is given) * expert_hidden_dim must not exceed 278,528 values;
 //     larger requests return VIB3_ERR_CAPACITY and launch nothing.
-//   * The first call on a device looks the address up.  Make that call outside any stream capture.
+//   * The first call on a device loads the array and looks its address up.  Make that call outside any
+//     stream capture and before free VRAM is given away.
 //   * All calls on a device share the one array and each call overwrites what the previous one left
 //     (nothing has to be cleared: the second kernel reads only what the first kernel of the same call
 //     wrote).  Two calls whose kernels can overlap on the GPU — different streams without an ordering
@@ -73,7 +78,8 @@ extern "C" int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dty
                                                         int hidden_dim, int expert_hidden_dim, int pages_per_segment,
                                                         int rows_per_page_gate_up, int rows_per_page_down,
                                                         int group_size, int* status, void* stream) {
-    if (top_k < 0 || expert_hidden_dim <= 0) return VIB3_ERR_SHAPE;
+    if (top_k < 0) return VIB3_ERR_COUNT;   // (the codes of vib3_launch_moe_layer_int4_paged)
+    if (expert_hidden_dim <= 0) return VIB3_ERR_SHAPE;
     const size_t slots = (size_t)top_k + (shared_pages ? 1u : 0u);
     if (slots * (size_t)expert_hidden_dim > kNoAllocMaxHalves) return VIB3_ERR_CAPACITY;
     void* scratch = nullptr;

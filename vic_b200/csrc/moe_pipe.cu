@@ -17,6 +17,7 @@
 // VIB3_STATUS_TIMEOUT in the status word and leaves; the producer additionally drains the copies
 // it has issued (bounded as well) before it returns.
 #include "pipe_common.cuh"
+#include "router_core.cuh"
 
 namespace vib3 {
 
@@ -26,8 +27,36 @@ namespace vib3 {
 // At most 80 registers per thread: with more, a CTA of this kernel (17 warps) and a router CTA (8 warps
 // of 48 registers) no longer fit in an SM's register file together, and the first pass cannot run beside
 // the router (measured: 59 us per step instead of 56).
-template <int NCH>
-__global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstages) {
+// ROUTED: the kernel also ROUTES the token.  Its CTAs first stream the router's weight rows through the same
+// ring (one row per stage; CTA b takes rows [E b / G, E (b+1) / G)), one consumer warp per row forms the
+// logit in the reference kernel's summation order (router_core.cuh) and stores it; the CTAs then meet at a
+// counter in global memory (all of them are resident: one per SM), and in every CTA a pair of extra warps
+// (a selecting warp and a helper) repeats the same scoring and selection over the E logits, so that every
+// CTA knows the routing without another launch or a broadcast; CTA 0 also stores it for the kernels that
+// follow.  While the counter fills and the selection runs, the ring already streams the shared expert
+// (pass 0): the memory pipe never waits for the router.  Every wait is bounded.
+constexpr int kRoutedThreads = kPipeThreads + 64;   // + selecting warp + helper warp
+
+// slot_pages() with the routing taken from shared memory
+__device__ __forceinline__ const PageEntry* routed_slot_pages(const MoeLayerArgs& a, const unsigned short* ids, int s) {
+    if (s < a.top_k) {
+        const unsigned e = ids[s];
+        if (e >= (unsigned)a.num_experts) return nullptr;
+        return a.page_table + (size_t)e * 3 * a.P;
+    }
+    return a.shared_pages;
+}
+
+struct RoutedSmem {
+    TopKSmem topk;
+    unsigned long long rows_done;      // one arrival per router row of this CTA
+    unsigned long long routing_ready;  // the selecting warp arrives once the routing is in r_ids / r_w
+    unsigned short r_ids[kRouterMaxTopK];
+    float r_w[kRouterMaxTopK];
+};
+
+template <int NCH, bool ROUTED>
+__global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerArgs a, RouterArgs r, int nstages) {
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nchunks = a.H / kGroupSize;
@@ -36,14 +65,19 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
     const unsigned code_row = (unsigned)a.H / 2, scale_row = (unsigned)a.H / 16;
     const unsigned stage_bytes = 2 * kTileRows * (code_row + scale_row);
 
-    // A launch for a later window of a device-side pair list (slot_begin > 0) with nothing in its window:
-    // leave at once.  The count was written by a kernel that had completed before the first launch of
-    // the chain started, so it can be read without waiting.
-    if (a.slot_begin > 0 && a.num_active_dev && !a.shared_pages && *a.num_active_dev <= a.slot_begin) return;
+    // A launch for a later window of a device-side pair list (slot_begin > 0) with nothing in its window has
+    // no work.  The count was written by a kernel that had completed before the first launch of the chain
+    // started, so it can be read without waiting; but the kernel may only END after its predecessor has:
+    // a kernel that leaves before its dependency wait counts as complete, and the kernel after it would no
+    // longer be ordered behind the predecessor.
+    if (!ROUTED && a.slot_begin > 0 && a.num_active_dev && !a.shared_pages && *a.num_active_dev <= a.slot_begin) {
+        pdl_wait();
+        return;
+    }
     // Grouped mode: the slots are (token, expert) pairs of several tokens.  A CTA's contiguous share of the
     // row space touches at most two slots, so it keeps two quantised activation vectors; which tokens they
     // belong to is known only after the wait, so there is no pass 0 (the shared expert is the last slot).
-    const bool grouped = a.slot_token != nullptr;
+    const bool grouped = !ROUTED && a.slot_token != nullptr;
     const unsigned xbytes = (unsigned)nchunks * MATH::kStride;
 
     unsigned char* stages = smem_raw;
@@ -53,8 +87,15 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
     uint64_t* empty = full + kMaxStages;
     uint64_t* tab_ready = empty + kMaxStages;
     volatile unsigned* landed = reinterpret_cast<volatile unsigned*>(tab_ready + 1);
+    // routed launches only: the token as given (later the ring of a near-tie recomputation), selection scratch
+    unsigned char* xraw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(landed + kMaxStages) + 15) & ~(uintptr_t)15);
+    const unsigned xraw_bytes = ROUTED ? max((unsigned)a.H * (a.x_dtype == X_F32 ? 4u : 2u), (unsigned)(kSeqRingFloats * sizeof(float))) : 0u;
+    RoutedSmem& rs = *reinterpret_cast<RoutedSmem*>(xraw + ((xraw_bytes + 15) & ~15u));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int e0 = 0, e1 = 0;  // this CTA's router rows
+    if (ROUTED) cta_share(r.E, e0, e1);
+    const int nrows = e1 - e0;
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
@@ -62,15 +103,29 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
             landed[s] = 0;
         }
         mbar_init(tab_ready, 1);
+        if (ROUTED) {
+            mbar_init(reinterpret_cast<uint64_t*>(&rs.rows_done), max(nrows, 1));
+            mbar_init(reinterpret_cast<uint64_t*>(&rs.routing_ready), 1);
+            topk_smem_init(rs.topk, 1);
+            if (nrows == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&rs.rows_done));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Neither the activation vector nor the shared expert's pages come from the router: quantise the
-    // vector and run the whole shared expert (pass 0) BEFORE waiting for the router.  This kernel leaves
-    // enough shared memory free for a router CTA on the same SM, so its CTAs become resident while the
-    // router is still running and the shared expert streams under the router's serial tail.  Between the
-    // passes nobody waits for the whole CTA: the producer warp alone waits for the router, builds the
-    // routed slots' page table and goes on issuing copies while the consumers finish pass 0.
+    // vector and run the whole shared expert (pass 0) BEFORE the routing is known.  A launch that does not
+    // route itself leaves enough shared memory free for a router CTA on the same SM, so its CTAs become
+    // resident while the router is still running and the shared expert streams under the router's serial
+    // tail.  Between the passes nobody waits for the whole CTA: the producer warp alone waits for the
+    // routing, builds the routed slots' page table and goes on issuing copies while the consumers finish
+    // pass 0.  A routed launch may follow the producer of its token with programmatic dependent launch:
+    // everything that reads the token waits for that kernel first; the weights do not depend on it, so the
+    // producer warp fills the ring meanwhile.
+    if (ROUTED && warp != kConsumerWarps) pdl_wait();
     if (warp < kConsumerWarps && !grouped) stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
+    if (ROUTED && warp < kConsumerWarps) {
+        const int n16 = (a.H * (a.x_dtype == X_F32 ? 4 : 2)) >> 4;
+        for (int i = tid; i < n16; i += kConsumerWarps * 32) reinterpret_cast<uint4*>(xraw)[i] = __ldg(reinterpret_cast<const uint4*>(a.x) + i);
+    }
     if (a.shared_pages)
         for (int i = tid; i < 2 * a.P; i += blockDim.x) tab[cap_k * 2 * a.P + i] = a.shared_pages[i];
     __syncthreads();
@@ -83,19 +138,35 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
         // ── producer warp: every lane walks the tiles; lane 0 arms the stage's barrier, lanes 0..3 each
         // issue one of the tile's four copies, so a tile costs one lane's worth of latency ──
         bool ok = true;
+        if (ROUTED) {
+            // the router's rows of this CTA, one row per stage (the launcher checked that they fit)
+            const unsigned row_bytes = (unsigned)r.H * (r.w_dtype == W_F32 ? 4u : 2u);
+            for (int i = 0; i < nrows; ++i, ++n) {
+                if (lane == 0) {
+                    mbar_expect_tx(full + n, row_bytes);
+                    bulk_load(stages + (size_t)n * stage_bytes, reinterpret_cast<const unsigned char*>(r.W) + (size_t)(e0 + i) * row_bytes, row_bytes, full + n);
+                }
+            }
+            __syncwarp();
+        }
         for (int pass = first_pass; pass < 2 && ok; ++pass) {
             int g0, g1;
             if (pass == 0) {
                 cta_share(a.I, g0, g1);
             } else {
-                pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
-                // Only now may the next kernel in the stream start: it reads the routing without waiting,
-                // and may overwrite nothing this kernel still reads.
-                pdl_trigger();
+                if (ROUTED) {
+                    ok = mbar_wait(reinterpret_cast<uint64_t*>(&rs.routing_ready), 0);
+                    if (!ok) break;
+                } else {
+                    pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
+                    // Only now may the next kernel in the stream start: it reads the routing without waiting,
+                    // and may overwrite nothing this kernel still reads.
+                    pdl_trigger();
+                }
                 a.top_k = active_top_k(a);
                 for (int i = lane; i < a.top_k * 2 * a.P; i += 32) {
                     const int s = i / (2 * a.P), rem = i % (2 * a.P);
-                    const PageEntry* pg = slot_pages(a, s);
+                    const PageEntry* pg = ROUTED ? routed_slot_pages(a, rs.r_ids, s) : slot_pages(a, s);
                     PageEntry e{0, 0, 0, 0};
                     if (pg) e = pg[rem];
                     else if (rem == 0) flag(a.status, kStatusBadExpert);
@@ -140,9 +211,75 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
         return;
     }
 
+    Ring ring{full, empty, landed, nstages};
+    if (ROUTED && warp > kConsumerWarps) {
+        // ── selecting warp and helper warp ──
+        const int gt = tid - (kConsumerWarps + 1) * 32;  // index in the group of 64
+        bool ok = true;
+        if (gt == 0) {
+            ok = mbar_wait(reinterpret_cast<uint64_t*>(&rs.rows_done), 0);
+            // arrive at the grid-wide counter (release this CTA's logits), then wait for everybody's
+            unsigned int seen = 0;
+            asm volatile("atom.add.acq_rel.gpu.u32 %0, [%1], 1;" : "=r"(seen) : "l"(r.counter) : "memory");
+            ++seen;
+            for (unsigned it = 0; seen < gridDim.x && it < kRouterSpinLimit; ++it)
+                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(seen) : "l"(r.counter) : "memory");
+            if (seen < gridDim.x) ok = false;
+            if (!ok) flag(a.status, kStatusTimeout);
+        }
+        group_sync(64);
+        router_finish(r, rs.topk, reinterpret_cast<float*>(xraw), gt, 64, r.mode != 0, blockIdx.x == 0, rs.r_ids, rs.r_w);
+        if (gt == 0) {
+            if (rs.topk.failed) flag(a.status, kStatusTimeout);
+            __threadfence();  // CTA 0: ids and weights are in global memory before the next kernel may start
+            mbar_arrive(reinterpret_cast<uint64_t*>(&rs.routing_ready));
+            pdl_trigger();
+            // the last CTA to leave the counter resets it for the next launch
+            unsigned int left;
+            asm volatile("atom.add.acq_rel.gpu.u32 %0, [%1], 1;" : "=r"(left) : "l"(r.counter + 2) : "memory");
+            if (left == gridDim.x - 1) {
+                r.counter[0] = 0u;
+                r.counter[2] = 0u;
+            }
+        }
+        return;
+    }
+
     // ── consumers ──
     const int group = warp / kGroupWarps, wi = warp % kGroupWarps;
-    Ring ring{full, empty, landed, nstages};
+    if (ROUTED) {
+        // router rows: row i of this CTA sits in stage i and belongs to warp i % 16
+        for (int i = 0; i < nrows; ++i) {
+            if (i % kConsumerWarps != warp) continue;
+            if (!ring.wait_full(i, lane == 0)) {
+                if (lane == 0) flag(a.status, kStatusTimeout);
+                return;
+            }
+            const unsigned char* wrow = stages + (size_t)i * stage_bytes;
+            float logit = 0.f, absum = 0.f;
+            if (r.w_dtype == W_F32) {
+                if (r.x_dtype == X_F32) row_logit_smem<X_F32, W_F32>(wrow, xraw, r.H, lane, logit, absum);
+                else if (r.x_dtype == X_F16) row_logit_smem<X_F16, W_F32>(wrow, xraw, r.H, lane, logit, absum);
+                else row_logit_smem<X_BF16, W_F32>(wrow, xraw, r.H, lane, logit, absum);
+            } else {
+                if (r.x_dtype == X_F32) row_logit_smem<X_F32, W_F16>(wrow, xraw, r.H, lane, logit, absum);
+                else if (r.x_dtype == X_F16) row_logit_smem<X_F16, W_F16>(wrow, xraw, r.H, lane, logit, absum);
+                else row_logit_smem<X_BF16, W_F16>(wrow, xraw, r.H, lane, logit, absum);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                const int e = e0 + i;
+                if (r.logit_offset) logit = __fadd_rn(logit, r.logit_offset[e]);
+                r.scores[e] = logit;
+                if (r.exact_order) r.scores[r.E + e] = absum;
+                if (r.mode != 0) r.scores[2 * r.E + e] = sigmoid_ref(logit);
+                __threadfence();
+                for (int k = 0; k < kGroupWarps; ++k) mbar_arrive(empty + i);   // the stage had one reader
+                mbar_arrive(reinterpret_cast<uint64_t*>(&rs.rows_done));
+            }
+        }
+        n = nrows;
+    }
     const uint32_t stages_addr = smem_u32(stages);
     const uint32_t x_base = smem_u32(xs) + lane * MATH::kStride;
     int slot_a = 0;  // grouped mode: the slot whose token's vector is in the first activation buffer
@@ -153,9 +290,12 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
         } else {
             // The next kernel in the stream (the down kernel) reads the routing without waiting, so it may
             // start only when the router is known to have finished: after this thread's own wait.  By
-            // then this thread has also finished the shared expert's rows (pass 0).
-            pdl_wait();
-            pdl_trigger();
+            // then this thread has also finished the shared expert's rows (pass 0).  (A routed launch lets
+            // it go from its selecting warp, once CTA 0 has stored the routing.)
+            if (!ROUTED) {
+                pdl_wait();
+                pdl_trigger();
+            }
             a.top_k = active_top_k(a);
             const bool ready = mbar_wait(tab_ready, 0);
             cta_share((a.top_k + shared_in_pass1) * a.I, g0, g1);
@@ -266,11 +406,13 @@ __global__ void __maxnreg__(80) moe_gateup_pipe_kernel(MoeLayerArgs a, int nstag
 // stage layout: per slot [codes R*I/2][scales R*I/16], R = kDownRows.
 // Two shapes (template parameters R = rows per tile, WPS = warps per slot): up to 9 slots R = 6, WPS = 2
 // (measured on the Kimi shape with 9 slots: 4 rows 20.7 us, 5 rows 18.2 us, 6 rows 17.3-18.0 us, 8 rows
-// 18.5 us; VIB3_DOWN_ROWS rebuilds the fixed shape with another height); 10 to 17
+// 18.5 us); 10 to 17
 // slots — the grouped launches of expert parallelism — R = 4, WPS = 1, so that two stages still fit.
 // In grouped mode (MoeLayerArgs::slot_token) the slots are (token, expert) pairs in ascending token
 // order and the combiner writes one output row per token.
 constexpr int kDownYStages = 4;
+constexpr int kDownTileRows = 6;      // rows of a tile in the fixed and (at most) in the run-time chosen shape
+static_assert(kDownTileRows <= 32, "the combiner uses one lane per row of a tile");
 constexpr int kDownMaxThreads = 640;  // 18 consumer warps for 9 slots + combiner + producer
 
 // R = 0: tile height and warps per slot are chosen in the kernel from the number of ACTIVE slots (which
@@ -280,14 +422,19 @@ constexpr int kDownMaxThreads = 640;  // 18 consumer warps for 9 slots + combine
 template <int NCH, int R, int WPS>
 __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLayerArgs a, int ring) {
     constexpr bool kDyn = R == 0;
-    constexpr int kRowsMax = kDyn ? 6 : R;
-    constexpr int kDownRowsPerWarp = kDyn ? 6 : (R + (kDyn ? 1 : WPS) - 1) / (kDyn ? 1 : WPS);
+    constexpr int kRowsMax = kDyn ? kDownTileRows : R;
+    constexpr int kDownRowsPerWarp = kDyn ? kDownTileRows : (R + (kDyn ? 1 : WPS) - 1) / (kDyn ? 1 : WPS);
+    static_assert(kRowsMax <= kDownTileRows, "the host sizes the row ring for kDownTileRows rows");
     using MATH = MathQ16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);  // launch shape and shared-memory layout
     // The slot count may come from device memory; the kernel that wrote it had completed before the
     // gate/up kernel passed its dependency wait, like the expert ids (see below).
-    if (a.slot_begin > 0 && a.num_active_dev && !a.shared_pages && a.out_accumulate && *a.num_active_dev <= a.slot_begin) return;
+    // (An empty later window leaves only after its predecessor has completed, see the gate/up kernel.)
+    if (a.slot_begin > 0 && a.num_active_dev && !a.shared_pages && a.out_accumulate && *a.num_active_dev <= a.slot_begin) {
+        pdl_wait();
+        return;
+    }
     a.top_k = active_top_k(a);
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
@@ -295,7 +442,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     if (kDyn) {
         const unsigned row_bytes = code_row + scale_row;
         wps_v = slots <= 9 ? 2 : 1;
-        rows_v = (slots <= 9 || 2u * slots * 6u * row_bytes <= (unsigned)ring) ? 6 : 4;
+        rows_v = (slots <= 9 || 2u * slots * kDownTileRows * row_bytes <= (unsigned)ring) ? kDownTileRows : 4;
         nstages_v = min(kMaxStages, ring / max(1, (int)(slots * rows_v * row_bytes)));
     }
     const int kDownRows = rows_v, kDownWarpsPerSlot = wps_v, nstages = nstages_v;
@@ -311,7 +458,8 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     uint64_t* empty = full + kMaxStages;
     uint64_t* yfull = empty + kMaxStages;
     uint64_t* yempty = yfull + kDownYStages;
-    float* wts = reinterpret_cast<float*>(yempty + kDownYStages);
+    uint64_t* act_read = yempty + kDownYStages;  // one arrival per consumer warp once its activations are in registers
+    float* wts = reinterpret_cast<float*>(act_read + 1);
     int* toks = reinterpret_cast<int*>(wts + kMaxSlots);  // grouped mode: token of each routed slot
     float* ybuf = reinterpret_cast<float*>(toks + kMaxSlots);  // [y stage][row][kMaxSlots]
     unsigned char* stages = reinterpret_cast<unsigned char*>(
@@ -319,9 +467,9 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // The next kernel in the stream may overwrite the activation scratch before its own dependency
-    // wait (the gate/up kernel does, for the shared expert).  Warps that never read the scratch let it
-    // go at once; consumer warps only after they have copied their chunks into registers.
-    if (warp >= cwarps) pdl_trigger();
+    // wait (the gate/up kernel does, for the shared expert).  It may therefore be let go only when every
+    // consumer warp of this CTA has copied its chunks into registers: the warps arrive on `act_read` and
+    // ONE thread, the combiner's first lane, issues the trigger for the CTA.
     if (tid == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
@@ -331,6 +479,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
             mbar_init(yfull + s, max(cwarps, 1));
             mbar_init(yempty + s, 1);
         }
+        mbar_init(act_read, max(cwarps, 1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // Expert ids and routing weights were written by the router.  This kernel is launched only after
@@ -344,7 +493,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
         tab[i] = e;
     }
     for (int s = tid; s < slots; s += blockDim.x) {
-        wts[s] = s < a.top_k ? a.expert_weights[s] : a.shared_weight;
+        wts[s] = s < a.top_k ? __ldcg(a.expert_weights + s) : a.shared_weight;
         toks[s] = a.slot_token ? (s < a.top_k ? (int)a.slot_token[s] : a.shared_token) : 0;
     }
     __syncthreads();
@@ -353,6 +502,7 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     cta_share(a.H, g0, g1);
 
     if (slots == 0) {  // nothing selected: the layer output is zero
+        pdl_wait();  // (end only after the predecessor)
         if (!a.out_accumulate)
             for (int tk = 0; tk < (a.slot_token ? a.n_tokens : 1); ++tk)
                 for (int r = g0 + tid; r < g1; r += blockDim.x) a.out[(size_t)tk * a.out_stride + r] = 0.f;
@@ -416,6 +566,11 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
 
     if (warp == combiner_warp) {
         // ── combiner warp: lane r adds row r of each tile over the slots, in plan order ──
+        if (lane == 0) {
+            if (!mbar_wait(act_read, 0)) flag(a.status, kStatusTimeout);
+            pdl_trigger();
+        }
+        __syncwarp();
         TileWalk walk(g0, g1, a.H, a.rpp_dn, kDownRows);
         Tile t;
         int n = 0;
@@ -468,7 +623,8 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     // the scratch has been read: the sums below depend on every loaded value, so the loads have returned
 #pragma unroll
     for (int i = 0; i < NCH; ++i) asm volatile("" ::"r"(sq8[i]));
-    pdl_trigger();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(act_read);
 
     const uint32_t stages_addr = smem_u32(stages);
     const uint32_t code_base = s * slot_bytes + lane * 16;
@@ -525,9 +681,6 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
 
 // ── host side ──────────────────────────────────────────────────────────────────────────────
 
-// static shared memory of a router CTA plus the per-CTA reservation, rounded up (vib3_config_set key 3, in KB)
-int g_router_cta_smem_kb = 46;
-
 static bool pipe_shape_ok(const MoeLayerArgs& a) {
     return a.H % 256 == 0 && a.I % 256 == 0;
 }
@@ -541,8 +694,8 @@ static int pick_stages(size_t fixed, size_t stage_bytes, int min_stages) {
 }
 
 // Launch with the programmatic-stream-serialization attribute (g_use_pdl) or plainly.
-template <class K>
-static int launch_pipe(K kernel, int grid, int threads, size_t smem, cudaStream_t st, const MoeLayerArgs& a, int nstages) {
+template <class K, class... Args>
+static int launch_pipe(K kernel, int grid, int threads, size_t smem, cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)threads);
@@ -552,8 +705,8 @@ static int launch_pipe(K kernel, int grid, int threads, size_t smem, cudaStream_
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_use_pdl ? 1 : 0;
-    return (int)cudaLaunchKernelEx(&cfg, kernel, a, nstages);
+    cfg.numAttrs = g_use_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 template <class K>
@@ -562,38 +715,57 @@ static int set_max_smem(K kernel) {
     return e == cudaSuccess ? 0 : (int)e;
 }
 
-template <int NCH>
-static int launch_gateup_pipe_t(const MoeLayerArgs& a, cudaStream_t st, int nstages, size_t smem, int grid) {
-    static int attr = set_max_smem(moe_gateup_pipe_kernel<NCH>);
+template <int NCH, bool ROUTED>
+static int launch_gateup_pipe_t(const MoeLayerArgs& a, const RouterArgs& r, cudaStream_t st, int nstages, size_t smem, int grid) {
+    static int attr = set_max_smem(moe_gateup_pipe_kernel<NCH, ROUTED>);
     if (attr) return attr;
-    return launch_pipe(moe_gateup_pipe_kernel<NCH>, grid, kPipeThreads, smem, st, a, nstages);
+    return launch_pipe(moe_gateup_pipe_kernel<NCH, ROUTED>, grid, ROUTED ? kRoutedThreads : kPipeThreads, smem, st, a, r, nstages);
 }
 
-int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
-    if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
-    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-    const size_t stage_bytes = 2 * kTileRows * ((size_t)a.H / 2 + (size_t)a.H / 16);
-    const size_t fixed = (size_t)(a.slot_token ? 2 : 1) * (a.H / kGroupSize) * MathQ16::kStride +
-                         (size_t)slots * 2 * a.P * sizeof(PageEntry) +
-                         (2 * kMaxStages + 1) * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + 128;
-    // leave kRouterCtaSmem of the SM's shared memory to a router CTA, so that this kernel's CTAs become
-    // resident while the router still runs (see the kernel's first pass)
-    int nstages = pick_stages(fixed + (size_t)g_router_cta_smem_kb * 1024, stage_bytes, 3);
-    if (nstages == 0) nstages = pick_stages(fixed, stage_bytes, 3);
-    if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
-    const size_t smem = fixed + (size_t)nstages * stage_bytes;
-    const int total = slots * a.I;
-    const int grid = min(sm_count(), (total + kTileRows - 1) / kTileRows);
+template <bool ROUTED>
+static int launch_gateup_nch(const MoeLayerArgs& a, const RouterArgs& r, cudaStream_t st, int nstages, size_t smem, int grid) {
     const int nchunks = a.H / kGroupSize;
     const int nch = nchunks % 32 == 0 ? nchunks / 32 : 0;
     switch (nch) {
-        case 1: return launch_gateup_pipe_t<1>(a, st, nstages, smem, grid);
-        case 2: return launch_gateup_pipe_t<2>(a, st, nstages, smem, grid);
-        case 4: return launch_gateup_pipe_t<4>(a, st, nstages, smem, grid);
-        case 7: return launch_gateup_pipe_t<7>(a, st, nstages, smem, grid);
-        case 8: return launch_gateup_pipe_t<8>(a, st, nstages, smem, grid);
-        default: return launch_gateup_pipe_t<0>(a, st, nstages, smem, grid);
+        case 1: return launch_gateup_pipe_t<1, ROUTED>(a, r, st, nstages, smem, grid);
+        case 2: return launch_gateup_pipe_t<2, ROUTED>(a, r, st, nstages, smem, grid);
+        case 4: return launch_gateup_pipe_t<4, ROUTED>(a, r, st, nstages, smem, grid);
+        case 7: return launch_gateup_pipe_t<7, ROUTED>(a, r, st, nstages, smem, grid);
+        case 8: return launch_gateup_pipe_t<8, ROUTED>(a, r, st, nstages, smem, grid);
+        default: return launch_gateup_pipe_t<0, ROUTED>(a, r, st, nstages, smem, grid);
     }
+}
+
+// router == nullptr: the routing (a.expert_ids / a.expert_weights) comes from an earlier kernel.
+// Otherwise the kernel routes the token itself and CTA 0 stores the routing there; VIB3_ERR_UNSUPPORTED
+// (nothing launched) when the router's rows do not fit the ring — the caller then launches the router separately.
+int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st, const RouterArgs* router) {
+    if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
+    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+    const size_t stage_bytes = 2 * kTileRows * ((size_t)a.H / 2 + (size_t)a.H / 16);
+    size_t fixed = (size_t)(a.slot_token ? 2 : 1) * (a.H / kGroupSize) * MathQ16::kStride +
+                   (size_t)slots * 2 * a.P * sizeof(PageEntry) +
+                   (2 * kMaxStages + 1) * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + 128;
+    const int total = slots * a.I;
+    const int grid = min(sm_count(), (total + kTileRows - 1) / kTileRows);
+    if (router) {
+        const RouterArgs& r = *router;
+        const size_t row_bytes = (size_t)r.H * (r.w_dtype == W_F32 ? 4 : 2);
+        const size_t xraw = (size_t)a.H * (a.x_dtype == X_F32 ? 4 : 2);
+        if (a.slot_token || a.num_active_dev || r.H != a.H || r.x != a.x || r.x_dtype != a.x_dtype) return VIB3_ERR_UNSUPPORTED;
+        if (r.E > kRouterMaxExperts || r.H > kRouterXMax || r.H % 8 != 0 || row_bytes > stage_bytes) return VIB3_ERR_UNSUPPORTED;
+        if (((uintptr_t)r.W & 15) || ((uintptr_t)r.x & 15)) return VIB3_ERR_UNSUPPORTED;
+        fixed += ((xraw > kSeqRingFloats * sizeof(float) ? xraw : kSeqRingFloats * sizeof(float)) + 15) / 16 * 16 + sizeof(RoutedSmem) + 32;
+        const int nstages = pick_stages(fixed, stage_bytes, 3);
+        if (nstages == 0 || (r.E + grid - 1) / grid > nstages) return VIB3_ERR_UNSUPPORTED;
+        return launch_gateup_nch<true>(a, r, st, nstages, fixed + (size_t)nstages * stage_bytes, grid);
+    }
+    // leave kRouterCtaSmem of the SM's shared memory to a router CTA, so that this kernel's CTAs become
+    // resident while the router still runs (see the kernel's first pass)
+    int nstages = pick_stages(fixed + kRouterCtaSmem, stage_bytes, 3);
+    if (nstages == 0) nstages = pick_stages(fixed, stage_bytes, 3);
+    if (nstages == 0) return VIB3_ERR_UNSUPPORTED;
+    return launch_gateup_nch<false>(a, RouterArgs{}, st, nstages, fixed + (size_t)nstages * stage_bytes, grid);
 }
 
 template <int NCH, int R, int WPS>
@@ -610,8 +782,8 @@ int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     // register-resident activations: at most two chunks per lane
     if (nchunks != 32 && nchunks != 64) return VIB3_ERR_UNSUPPORTED;
     const size_t row_bytes = (size_t)a.I / 2 + (size_t)a.I / 16;
-    const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + 2 * (kMaxStages + kDownYStages) * sizeof(uint64_t) +
-                         2 * kMaxSlots * sizeof(float) + kDownYStages * 6 * kMaxSlots * sizeof(float) + 256;
+    const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + (2 * (kMaxStages + kDownYStages) + 1) * sizeof(uint64_t) +
+                         2 * kMaxSlots * sizeof(float) + kDownYStages * kDownTileRows * kMaxSlots * sizeof(float) + 256;
     if (slots > 9) {
         // Launch sized for up to 17 slots; how many are active is known only on the device, and the kernel
         // picks tile height, warps per slot and ring depth from that number.
@@ -621,10 +793,7 @@ int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
         return nchunks == 64 ? launch_down_pipe_t<2, 0, 0>(a, st, ring, kSmemBudget, grid, kDownMaxThreads)
                              : launch_down_pipe_t<1, 0, 0>(a, st, ring, kSmemBudget, grid, kDownMaxThreads);
     }
-#ifndef VIB3_DOWN_ROWS
-#define VIB3_DOWN_ROWS 6
-#endif
-    constexpr int rows = VIB3_DOWN_ROWS, wps = 2;
+    constexpr int rows = kDownTileRows, wps = 2;
     const size_t stage_bytes = (size_t)slots * rows * row_bytes;
     const int nstages = pick_stages(fixed, stage_bytes, 2);
     if (nstages == 0) return VIB3_ERR_UNSUPPORTED;

@@ -5,15 +5,9 @@
 
 namespace vib3 {
 
-#ifndef VIB3_G_TILE_ROWS
-#define VIB3_G_TILE_ROWS 4
-#endif
 constexpr int kConsumerWarps = 16;
-constexpr int kTileRows = VIB3_G_TILE_ROWS;       // row pairs per gate/up stage
-#ifndef VIB3_G_PAIRS_PER_WARP
-#define VIB3_G_PAIRS_PER_WARP 2
-#endif
-constexpr int kPairsPerWarp = VIB3_G_PAIRS_PER_WARP;  // a consumer warp takes two row pairs (4 rows share each activation load)
+constexpr int kTileRows = 4;       // row pairs per gate/up stage
+constexpr int kPairsPerWarp = 2;   // a consumer warp takes two row pairs (4 rows share each activation load)
 constexpr int kGroupWarps = kTileRows / kPairsPerWarp;  // 2 warps consume a stage
 constexpr int kGroups = kConsumerWarps / kGroupWarps;   // 8 groups; group g takes tiles g, g+8, ...
 constexpr int kPipeThreads = (kConsumerWarps + 1) * 32;

@@ -200,9 +200,6 @@ def bench_main(args) -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    # stdout carries exactly one JSON line: keep NCCL's version/info banner off it
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "INFO"):
-        os.environ["NCCL_DEBUG"] = "WARN"
     dist.init_process_group("nccl", device_id=dev)
     sh = KIMI
     layers = B.PHYS_LAYERS

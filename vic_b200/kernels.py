@@ -145,6 +145,23 @@ def moe_layer_int4_paged(x: torch.Tensor, page_table: int, num_experts: int, sha
         pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status), _stream(stream)))
 
 
+def moe_layer_routed_int4_paged(x: torch.Tensor, router_w: torch.Tensor, scores_buf, bias, logit_offset, ids_out, weights_out,
+                                top_k: int, scoring_mode: int, scaling_factor: float, normalize: bool, exact_order: bool,
+                                workspace, page_table: int, num_experts: int, shared_pages: int, shared_weight: float,
+                                act_scratch, out, out_accumulate: bool, hidden_dim: int, expert_hidden_dim: int,
+                                pages_per_segment: int, rows_per_page_gate_up: int, rows_per_page_down: int, status=None,
+                                stream: Optional[int] = None) -> None:
+    """Router and experts of one token; the routing (ids_out, weights_out) is an output.  Two launches where
+    the gate/up kernel can route the token in its own prologue, three otherwise."""
+    w_dtype = {torch.float16: W_F16, torch.float32: W_F32}[router_w.dtype]
+    check("moe_layer_routed_int4_paged", lib().vib3_launch_moe_layer_routed_int4_paged(
+        _ptr(x), x_dtype_code(x), _ptr(router_w), w_dtype, _ptr(scores_buf), _ptr(bias), _ptr(logit_offset), _ptr(ids_out),
+        _ptr(weights_out), num_experts, top_k, scoring_mode, scaling_factor, int(normalize), int(exact_order), _ptr(workspace),
+        page_table, shared_pages or 0, shared_weight, _ptr(act_scratch), _ptr(out), int(out_accumulate), hidden_dim,
+        expert_hidden_dim, pages_per_segment, rows_per_page_gate_up, rows_per_page_down, INT4_GROUP_SIZE, _ptr(status),
+        _stream(stream)))
+
+
 def moe_layer_int4_paged_var(x: torch.Tensor, page_table: int, num_experts: int, shared_pages: int, expert_ids,
                              expert_weights, top_k: int, shared_weight: float, act_scratch, out, out_accumulate: bool,
                              hidden_dim: int, expert_hidden_dim: int, pages_per_segment: int,

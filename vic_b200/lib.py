@@ -56,6 +56,8 @@ SIGNATURES = {
                                                 _i, _i, _vp, _vp]),
     "vib3_launch_moe_down_int4_paged": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _i, _i, _i,
                                              _i, _i, _vp, _vp]),
+    "vib3_launch_moe_layer_routed_int4_paged": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp, _vp,
+                                                     _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "vib3_launch_moe_layer_int4_paged_noalloc": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _i, _i, _i, _i,
                                                       _i, _vp, _vp]),
     "vib3_launch_moe_layer_int4_paged_var": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _i, _i, _i,
@@ -87,7 +89,7 @@ SIGNATURES = {
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
-        path = os.environ.get("VIB3_CUDA_LIB") or _build.LIB_PATH   # override: a differently tuned build of the same ABI
+        path = _build.LIB_PATH
         if not os.path.exists(path):
             path = _build.build()
         handle = C.CDLL(path)

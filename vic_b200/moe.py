@@ -1,7 +1,7 @@
 """The MoE sublayer of one decode token on the GPU: router -> experts -> accumulate.
 
-``MoeDecoder.forward_layer`` is the fused path (3 launches, no host synchronisation, graph
-capturable).  ``run_moe_sublayer_paged_calls`` drives the per-page entry points in the order the
+``MoeDecoder.forward_layer`` is the fused path (2 launches — the gate/up kernel routes the token in its
+prologue — or 3 for shapes it cannot route; no host synchronisation, graph capturable).  ``run_moe_sublayer_paged_calls`` drives the per-page entry points in the order the
 reference engine does (src/runtime/engine.rs:5052-5360, :5801-6306) and exists so that path stays
 exercised and comparable."""
 from __future__ import annotations
@@ -35,7 +35,7 @@ class MoeDecoder:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.tables = [model.page_table(l) for l in range(model.n_layers)]
         self.shared_tables = [model.shared_table(l) for l in range(model.n_layers)]
-        self.launches_per_layer = 3
+        self.launches_per_layer = 2 if (sh.hidden % 256 == 0 and sh.intermediate % 256 == 0) else 3
 
     def route(self, layer: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
               logit_offset: Optional[torch.Tensor] = None) -> None:
@@ -57,9 +57,17 @@ class MoeDecoder:
     def forward_layer(self, layer: int, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                       accumulate: bool = False, bias: Optional[torch.Tensor] = None,
                       logit_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """x: [H] activations (bf16 / fp16 / fp32).  Returns the fp32 [H] sublayer output."""
-        self.route(layer, x, bias, logit_offset)
-        return self.experts(layer, x, out, accumulate)
+        """x: [H] activations (bf16 / fp16 / fp32).  Returns the fp32 [H] sublayer output.  The routing is left in
+        ``self.ids`` / ``self.weights``."""
+        sh = self.model.shape
+        out = self.out if out is None else out
+        kernels.moe_layer_routed_int4_paged(x, self.model.router_w[layer], self.scores, bias, logit_offset, self.ids,
+                                            self.weights, sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize,
+                                            self.exact_order, self.workspace, self.tables[layer], sh.num_experts,
+                                            self.shared_tables[layer], 1.0, self.act, out, accumulate, sh.hidden,
+                                            sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page,
+                                            sh.down.rows_per_page, self.status)
+        return out
 
     def forward_host(self, layer: int, x_host: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
         """One token from and to HOST memory: x_host [H] (any of the activation dtypes, ordinary or pinned
