@@ -94,6 +94,17 @@ int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_
                                int hidden_dim, int num_experts, int top_k, int scoring_mode, float scaling_factor,
                                int normalize, int exact_order, unsigned int* workspace, void* stream);
 
+/* vib3_launch_router_topk_ex for n_tokens tokens in one launch (no counterpart in the reference, whose
+ * prefill routes token by token): token t reads x + t * x_stride_bytes and writes scores_buf + t *
+ * scores_stride (floats, >= 3 * num_experts), out_ids + t * ids_stride, out_weights + t * weights_stride
+ * (entries, >= top_k); workspace: 4 * n_tokens uint32, zero before the first call. */
+int vib3_launch_router_topk_batch(const void* x, int x_dtype, int x_stride_bytes, int n_tokens, const void* W,
+                                  int w_dtype, float* scores_buf, int scores_stride, const float* bias_or_null,
+                                  const float* logit_offset_or_null, unsigned short* out_ids, int ids_stride,
+                                  float* out_weights, int weights_stride, int hidden_dim, int num_experts, int top_k,
+                                  int scoring_mode, float scaling_factor, int normalize, int exact_order,
+                                  unsigned int* workspace, void* stream);
+
 /* Device page-table entry, one per (expert, segment, page): the device form of ResolvedPage
  * (src/runtime/query_planner.rs:36-42).  ptr == 0 marks an absent page. */
 typedef struct vib3_page_entry {
@@ -236,9 +247,40 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
                                              int rows_per_page_gate_up, int rows_per_page_down, int group_size,
                                              int* status, void* stream);
 
+/* ── Grouped multi-token layer (every distinct expert read once; tcgen05 tensor-core tiles) ── */
+/* No counterpart in the reference, whose prefill runs the batch-1 path token by token
+ * (src/runtime/engine.rs:1837-1838); the nearest precedent is its fused NVFP4 expert launch
+ * (cuda/src/kernels.cu:5357-5612, :5868).  Bytes of device scratch vib3_moe_grouped_prewarm needs. */
+size_t vib3_moe_grouped_workspace_bytes(int max_tokens, int top_k, int num_experts, int hidden_dim,
+                                        int expert_hidden_dim);
+/* Builds the TMA tensor maps of the grouped kernels over a page pool (pool_base: start of the pool's
+ * single allocation, 16-byte aligned, capacity_pages slots of 2 MiB) and over the caller's scratch
+ * (workspace, 1024-byte aligned, at least vib3_moe_grouped_workspace_bytes).  hidden_dim and
+ * expert_hidden_dim must be multiples of 256.  last_page_rows_*: rows of the last (ragged) page of a
+ * gate/up and of a down matrix.  The handle owns host memory only; nothing is allocated on the device
+ * (the role of vib3_moe_prewarm_gpu_bufs, cuda/src/kernels.cu:6507).  Like it, call it before any
+ * stream capture. */
+int vib3_moe_grouped_prewarm(void* pool_base, size_t capacity_pages, int num_experts, int top_k, int hidden_dim,
+                             int expert_hidden_dim, int rows_per_page_gate_up, int rows_per_page_down,
+                             int last_page_rows_gate_up, int last_page_rows_down, int max_tokens, void* workspace,
+                             size_t workspace_bytes, void** handle_out);
+void vib3_moe_grouped_destroy(void* handle);
+/* One MoE sublayer for n_tokens (<= max_tokens <= 128) tokens: ids / weights are the tokens' routing
+ * (rows of top_k entries, strides in bytes, device), x the activations (rows x_stride_bytes apart), out
+ * [n_tokens] fp32 rows out_stride floats apart (overwritten, or added to).  Five launches (bucketing, token
+ * gather, gate/up, down, per-token combine in plan order), no host synchronisation.  The pages of the
+ * page tables must lie in the pool given to vib3_moe_grouped_prewarm. */
+int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_dtype, int x_stride_bytes, int n_tokens,
+                                 const unsigned short* ids, int ids_stride_bytes, const float* weights,
+                                 int weights_stride_bytes, const void* page_table, const void* shared_pages,
+                                 float shared_weight, int pages_per_segment, float* out, int out_stride,
+                                 int out_accumulate, int* status, void* stream);
+
 /* Library options.  key 0: use the bulk-copy staged MoE kernels where the shape allows (default 1);
  * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
- * launch so that their prologue overlaps the previous kernel's tail (default 1).  The switches are
+ * launch so that their prologue overlaps the previous kernel's tail (default 1).  key 2:
+ * vib3_launch_moe_layer_routed_int4_paged routes inside the gate/up kernel (default 0: the router is a
+ * launch of its own, which measures faster on the Kimi shape).  The switches are
  * atomics: a launch running concurrently on another thread sees the old or the new value.  Returns
  * the previous value, or VIB3_ERR_UNSUPPORTED for an unknown key. */
 int vib3_config_set(int key, int value);

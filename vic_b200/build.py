@@ -16,6 +16,7 @@ SOURCES = [
     "moe_layer.cu",
     "moe_pipe.cu",
     "moe_noalloc.cu",
+    "moe_grouped.cu",
     "router.cu",
     "host/page_pool.cpp",
 ]

@@ -1,0 +1,752 @@
+// Grouped multi-token MoE sublayer: every DISTINCT expert that the tokens of a step select is read once.
+//
+// The reference has no such kernel — its prefill runs token by token through the batch-1 path
+// (src/runtime/engine.rs:1837-1838), so an expert chosen by 40 tokens is read 40 times.  Here the
+// (token, expert) pairs of the step are bucketed by expert on the device, and per expert the projections
+// are real matrix products on the 5th-generation tensor cores:
+//
+//   D[128 weight rows x N tokens] += A[128 x 256] . B[N x 256]^T      per 256-column slab of K
+//
+//   A  the INT4 page tile.  cp.async.bulk.tensor (one 3-D tensor map over the whole page pool: byte in
+//      row, row in page, pool slot) brings 128 B of codes and 16 B of scales per row and slab into shared
+//      memory (128-byte swizzle, so that 32 lanes reading 32 rows hit 32 different bank groups); eight
+//      warps turn the codes into fp16 weights (n - 8) * scale in registers and store them with tcgen05.st
+//      into TENSOR MEMORY: the A operand never goes back through shared memory, whose bandwidth could
+//      not carry 4x-expanded weights at the HBM rate.
+//   B  the tokens of the expert: rows of a gathered fp16 activation matrix (pairs sorted by expert), loaded
+//      by the same TMA unit as 128-byte-swizzled K-major tiles and read by the MMA through a shared-memory
+//      descriptor.  Within every 8 columns the K order of both operands is (0,4,1,5,2,6,3,7): that is
+//      the order in which one logic operation per two weights isolates the 4-bit codes, and a contraction
+//      does not care about the order of K as long as both operands agree.
+//   D  fp32 in tensor memory; tcgen05.ld brings it to registers for the epilogue (gate/up: SiLU product
+//      rounded to fp16 as the batch-1 path does; down: fp16 per (pair, row), combined per token in plan
+//      order by a last kernel, so that the result does not depend on scheduling).
+//
+// One elected thread issues the MMAs; completion is tracked with tcgen05.commit on mbarriers.  Every wait is
+// bounded: a thread that gives up sets VIB3_STATUS_TIMEOUT and the CTA drains and frees its tensor memory.
+// No cluster launch, no multicast: every CTA fetches its own tiles.
+//
+// The path stays HBM-bound by construction: at 128 tokens the step has 90 GFLOP of tensor work (64 us at
+// peak) against up to 7 GB of distinct expert weights (1 ms of HBM time); the figure of merit is bytes per
+// second over the distinct experts, the tensor pipe's utilisation is reported beside it.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <new>
+
+#include "int4_math.cuh"
+#include "launch_common.h"
+#include "pipe_common.cuh"
+
+namespace vib3 {
+
+constexpr int kGrpThreads = 512;
+constexpr int kGrpStages = 4;
+constexpr int kGrpSlabK = 256;                  // columns of K per pipeline step
+constexpr int kGrpMaxN = 64;                    // tokens of one expert per pass over its tile
+constexpr int kGrpRawBytes = 18 * 1024;         // codes 16 KB + scales 2 KB per stage
+constexpr int kGrpStageBytes = kGrpRawBytes + kGrpMaxN * kGrpSlabK * 2;   // + the tokens' slab: 50 KB
+constexpr int kGrpTmemCols = 512;
+constexpr int kGrpACols = kGrpSlabK / 2;        // 128 columns: 256 fp16 per row
+constexpr int kGrpDCol0 = 2 * kGrpACols;        // two A buffers, then two D buffers of kGrpMaxN columns
+constexpr int kGrpMaxTokens = 128;
+constexpr int kRouterMaxExpertsGrouped = 512;   // MAX_EXPERTS, src/core/types.rs:20
+
+struct GroupedMaps {
+    CUtensorMap gu_codes, gu_scales_full, gu_scales_last, dn_codes, dn_scales_full, dn_scales_last;
+    CUtensorMap xg16, xg64, act16, act64;
+};
+
+// Device-side description of the step, written by group_pairs_kernel.
+struct GroupedWork {
+    int n_active;            // distinct experts with at least one token (the shared expert counts as one)
+    int n_pairs;
+    int pad[2];
+};
+
+struct GroupedArgs {
+    const PageEntry* page_table;    // [E][3][P]
+    const PageEntry* shared_pages;  // [3][P] or null
+    const unsigned char* pool_base;
+    const GroupedWork* work;
+    const int* active;       // [n_active] expert ids, E = the shared expert; most tokens first
+    const int* counts;       // [E + 1]
+    const int* offsets;      // [E + 1] first sorted pair of the expert
+    __half* act;             // [pairs][I], K order permuted
+    __half* y;               // [pairs][H]
+    int E, P, H, I;
+    int rpp_gu, rpp_dn;
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 codes (one scale group, word j = columns 8j .. 8j+7) -> 16 half2 of (n - 8) * scale in the K order
+// (0,4),(1,5),(2,6),(3,7) per word.  (n + 1024) and (16 n + 1024) are exact fp16 numbers made by one logic
+// operation per pair; subtracting 1032, or multiplying by 1/16 and subtracting 72, is exact as well; the
+// only rounding is the product with the scale.
+__device__ __forceinline__ void dequant_chunk(const uint4& q, uint32_t scale2, uint32_t* out) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t w8 = w[j] >> 8;
+        const uint32_t a0 = lop3_and_or(w[j], 0x000F000Fu, 0x64006400u);
+        const uint32_t a1 = lop3_and_or(w[j], 0x00F000F0u, 0x64006400u);
+        const uint32_t a2 = lop3_and_or(w8, 0x000F000Fu, 0x64006400u);
+        const uint32_t a3 = lop3_and_or(w8, 0x00F000F0u, 0x64006400u);
+        uint32_t r0, r1, r2, r3;
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r0) : "r"(a0), "r"(0x64086408u));                  // (n + 1024) - 1032
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r1) : "r"(a1), "r"(0x2C002C00u), "r"(0xD480D480u));  // / 16 - 72
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r2) : "r"(a2), "r"(0x64086408u));
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r3) : "r"(a3), "r"(0x2C002C00u), "r"(0xD480D480u));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[4 * j + 0]) : "r"(r0), "r"(scale2));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[4 * j + 1]) : "r"(r1), "r"(scale2));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[4 * j + 2]) : "r"(r2), "r"(scale2));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(out[4 * j + 3]) : "r"(r3), "r"(scale2));
+    }
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                 "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+
+// Position of row r (column of the down projection) in the permuted K order.
+__device__ __forceinline__ int perm8(int r) {
+    const int i = r & 7;
+    return (r & ~7) | (i < 4 ? 2 * i : 2 * (i - 4) + 1);
+}
+
+// One work unit: a 128-row A tile of one expert (gate/up: 64 gate rows and the same 64 up rows; down: 128 rows).
+struct Unit {
+    int expert, n_tok, pair_off;
+    int slot_a, slot_b;      // pool slots of the page(s)
+    int rows_in_page;        // the page's row count (selects the scales map)
+    int row0;                // first row of the tile inside the page
+    int rows;                // valid rows of the tile (gate/up: of each half)
+    int mrow0;               // first row inside the matrix
+    bool present;
+};
+
+template <bool DOWN>
+__device__ __forceinline__ bool load_unit(const GroupedArgs& a, int u, Unit& t) {
+    const int half_rows = DOWN ? 128 : 64;
+    const int rpp = DOWN ? a.rpp_dn : a.rpp_gu;
+    const int tiles_per_page = (rpp + half_rows - 1) / half_rows;
+    const int m_rows = DOWN ? a.H : a.I;
+    const int tiles = min(a.P, (m_rows + rpp - 1) / rpp) * tiles_per_page;   // pages the matrix really has
+    const int ai = u / tiles, rem = u - ai * tiles;
+    if (ai >= a.work->n_active) return false;
+    const int page = rem / tiles_per_page, tp = rem - page * tiles_per_page;
+    t.expert = a.active[ai];
+    t.n_tok = a.counts[t.expert];
+    t.pair_off = a.offsets[t.expert];
+    const PageEntry* pg = t.expert < a.E ? a.page_table + (size_t)t.expert * 3 * a.P : a.shared_pages;
+    const PageEntry ea = pg[(DOWN ? kSegDown : kSegGate) * a.P + page];
+    const PageEntry eb = DOWN ? ea : pg[kSegUp * a.P + page];
+    t.present = ea.ptr != 0 && eb.ptr != 0;
+    t.rows_in_page = ea.row_count;
+    t.row0 = tp * half_rows;
+    t.rows = max(0, min(half_rows, (int)ea.row_count - t.row0));
+    t.mrow0 = ea.row_start + t.row0;
+    t.slot_a = (int)((ea.ptr - (unsigned long long)a.pool_base) >> 21);
+    t.slot_b = (int)((eb.ptr - (unsigned long long)a.pool_base) >> 21);
+    if (!t.present) t.rows = 0;
+    return true;
+}
+
+// DOWN = false: act[pair][perm(row)] = f16(silu(f16(Wg x)) * f16(Wu x)); DOWN = true: y[pair][row] = f16(Wd act).
+template <bool DOWN>
+__global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __grid_constant__ GroupedMaps maps, GroupedArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_dyn[];
+    unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    float* exch = reinterpret_cast<float*>(stages + kGrpStages * kGrpStageBytes);            // [64][kGrpMaxN + 1]
+    uint64_t* full = reinterpret_cast<uint64_t*>(exch + 64 * (kGrpMaxN + 1));
+    uint64_t* empty = full + kGrpStages;
+    uint64_t* a_full = empty + kGrpStages;
+    uint64_t* a_empty = a_full + 2;
+    uint64_t* d_full = a_empty + 2;
+    uint64_t* d_empty = d_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = DOWN ? a.I : a.H;
+    const int nslab = K / kGrpSlabK;
+    if (tid == 0) {
+        for (int s = 0; s < kGrpStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 9);       // eight converting warps and the MMA's commit
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(a_full + s, 8);
+            mbar_init(a_empty + s, 1);
+            mbar_init(d_full + s, 1);
+            mbar_init(d_empty + s, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kGrpTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();   // the work lists, the gathered tokens and (down) the intermediate are earlier kernels' outputs
+
+    // Every role walks the same sequence: units blockIdx.x, + gridDim.x, ...; per unit ceil(n_tok / 64) passes;
+    // per pass nslab slabs.  `it` counts slabs (ring stage it % 4, A buffer it & 1), `pc` passes (D buffer pc & 1).
+    bool ok = true;
+    if (warp == 0) {
+        // ── TMA producer ──
+        int it = 0;
+        Unit t;
+        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
+            if (t.rows == 0 || t.n_tok == 0) continue;
+            const CUtensorMap* codes = DOWN ? &maps.dn_codes : &maps.gu_codes;
+            const int rpp = DOWN ? a.rpp_dn : a.rpp_gu;
+            const CUtensorMap* scales = DOWN ? (t.rows_in_page == rpp ? &maps.dn_scales_full : &maps.dn_scales_last)
+                                             : (t.rows_in_page == rpp ? &maps.gu_scales_full : &maps.gu_scales_last);
+            for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN) {
+                const int ntok = min(kGrpMaxN, t.n_tok - p0);
+                const bool small = ntok <= 16;
+                const CUtensorMap* xmap = DOWN ? (small ? &maps.act16 : &maps.act64) : (small ? &maps.xg16 : &maps.xg64);
+                const int nb = small ? 16 : 64;
+                for (int s = 0; s < nslab; ++s, ++it) {
+                    const int st = it % kGrpStages;
+                    if (it >= kGrpStages) ok = mbar_wait(empty + st, ((it / kGrpStages) - 1) & 1);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        unsigned char* sb = stages + (size_t)st * kGrpStageBytes;
+                        mbar_expect_tx(full + st, kGrpRawBytes + nb * kGrpSlabK * 2);
+                        if (DOWN) {
+                            tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
+                            tma_load_3d(sb + 16384, scales, s * 16, t.row0, t.slot_a, full + st);
+                        } else {
+                            tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
+                            tma_load_3d(sb + 8192, codes, s * 128, t.row0, t.slot_b, full + st);
+                            tma_load_3d(sb + 16384, scales, s * 16, t.row0, t.slot_a, full + st);
+                            tma_load_3d(sb + 17408, scales, s * 16, t.row0, t.slot_b, full + st);
+                        }
+                        for (int j = 0; j < 4; ++j)
+                            tma_load_2d(sb + kGrpRawBytes + j * nb * 128, xmap, s * kGrpSlabK + 64 * j, t.pair_off + p0, full + st);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+        if (!ok && lane == 0) flag(a.status, kStatusTimeout);
+        // drain: every issued stage must have landed before the CTA's shared memory goes away
+        if (lane == 0)
+            for (int k = max(0, it - kGrpStages); k < it; ++k)
+                if (!mbar_wait(full + (k % kGrpStages), (k / kGrpStages) & 1)) flag(a.status, kStatusTimeout);
+    } else if (warp == 1) {
+        // ── MMA issuer ──
+        int it = 0, pc = 0;
+        Unit t;
+        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
+            if (t.rows == 0 || t.n_tok == 0) continue;
+            for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
+                const int ntok = min(kGrpMaxN, t.n_tok - p0);
+                const int nb = ntok <= 16 ? 16 : 64;
+                const int n_mma = (ntok + 15) & ~15;
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                const int db = pc & 1;
+                if (pc >= 2) ok = mbar_wait(d_empty + db, ((pc >> 1) - 1) & 1);
+                for (int s = 0; ok && s < nslab; ++s, ++it) {
+                    const int st = it % kGrpStages, ab = it & 1;
+                    ok = mbar_wait(full + st, (it / kGrpStages) & 1) && mbar_wait(a_full + ab, (it >> 1) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t xs = smem_u32(stages + (size_t)st * kGrpStageBytes + kGrpRawBytes);
+#pragma unroll
+                        for (int k = 0; k < kGrpSlabK / 16; ++k) {
+                            const uint32_t baddr = xs + (k >> 2) * nb * 128 + (k & 3) * 32;
+                            const uint64_t bdesc = (uint64_t)((baddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+                                                   ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+                            const uint32_t acc = (s > 0 || k > 0) ? 1u : 0u;
+                            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                                         ::"r"(tmem + kGrpDCol0 + db * kGrpMaxN), "r"(tmem + ab * kGrpACols + 8 * k), "l"(bdesc), "r"(idesc), "r"(acc)
+                                         : "memory");
+                        }
+                        umma_commit(a_empty + ab);
+                        umma_commit(empty + st);
+                        if (s == nslab - 1) umma_commit(d_full + db);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+        if (!ok && lane == 0) flag(a.status, kStatusTimeout);
+    } else if (warp >= 8) {
+        // ── converting warps: row m = 32 (warp % 4) + lane of the A tile, K half (warp - 8) / 4 of the slab ──
+        const int q = warp & 3, kh = (warp - 8) >> 2;
+        const int m = 32 * q + lane;
+        // where row m's codes and scales sit in a stage
+        const int src_row = DOWN ? m : (m & 63);
+        const uint32_t code_off = (DOWN ? 0u : (m >= 64 ? 8192u : 0u)) + (uint32_t)src_row * 128u;
+        const uint32_t scale_off = 16384u + (DOWN ? 0u : (m >= 64 ? 1024u : 0u)) + (uint32_t)src_row * 16u + (uint32_t)kh * 8u;
+        const uint32_t sw = (uint32_t)(src_row & 7);
+        int it = 0;
+        Unit t;
+        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
+            if (t.rows == 0 || t.n_tok == 0) continue;
+            const int total = ((t.n_tok + kGrpMaxN - 1) / kGrpMaxN) * nslab;
+            for (int i = 0; i < total; ++i, ++it) {
+                const int st = it % kGrpStages, ab = it & 1;
+                ok = mbar_wait(full + st, (it / kGrpStages) & 1);
+                if (ok && it >= 2) ok = mbar_wait(a_empty + ab, ((it >> 1) - 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sb = smem_u32(stages + (size_t)st * kGrpStageBytes);
+                const uint2 sc = lds64(sb + scale_off);   // four group scales
+                const uint32_t sc2[4] = {__byte_perm(sc.x, 0, 0x1010), __byte_perm(sc.x, 0, 0x3232), __byte_perm(sc.y, 0, 0x1010),
+                                         __byte_perm(sc.y, 0, 0x3232)};
+                const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + ab * kGrpACols + kh * 64;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t chunk = (uint32_t)(4 * kh + c) ^ sw;
+                    const uint4 codes = lds128(sb + code_off + chunk * 16u);
+                    uint32_t h[16];
+                    dequant_chunk(codes, sc2[c], h);
+                    tmem_st16(taddr + 16 * c, h);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(empty + st);
+                    mbar_arrive(a_full + ab);
+                }
+            }
+        }
+        if (!ok && lane == 0) flag(a.status, kStatusTimeout);
+    } else if (warp >= 4) {
+        // ── epilogue warps: TMEM lanes 32 (warp % 4) .. + 31 ──
+        const int q = warp & 3;
+        const int m = 32 * q + lane;
+        int pc = 0;
+        Unit t;
+        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
+            if (t.rows == 0 || t.n_tok == 0) continue;
+            for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
+                const int ntok = min(kGrpMaxN, t.n_tok - p0);
+                const int db = pc & 1;
+                ok = mbar_wait(d_full + db, (pc >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + kGrpDCol0 + db * kGrpMaxN;
+                for (int n0 = 0; n0 < ntok; n0 += 16) {
+                    uint32_t d[16];
+                    tmem_ld16(taddr + n0, d);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (DOWN) {
+                        if (m < t.rows) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (n0 + j < ntok)
+                                    a.y[(size_t)(t.pair_off + p0 + n0 + j) * a.H + t.mrow0 + m] = __float2half_rn(__uint_as_float(d[j]));
+                        }
+                    } else {
+                        // the up half hands its values to the gate half of the same rows
+                        if (m >= 64) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) exch[(m - 64) * (kGrpMaxN + 1) + n0 + j] = __uint_as_float(d[j]);
+                        }
+                        asm volatile("bar.sync 3, 128;" ::: "memory");
+                        if (m < 64 && m < t.rows) {
+                            const int col = perm8(t.mrow0 + m);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                if (n0 + j < ntok) {
+                                    const float g16 = __half2float(__float2half_rn(__uint_as_float(d[j])));
+                                    const float u16 = __half2float(__float2half_rn(exch[m * (kGrpMaxN + 1) + n0 + j]));
+                                    a.act[(size_t)(t.pair_off + p0 + n0 + j) * a.I + col] = __float2half_rn(silu_mul_f32(g16, u16));
+                                }
+                            }
+                        }
+                        asm volatile("bar.sync 3, 128;" ::: "memory");
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(d_empty + db);
+            }
+        }
+        if (!ok && lane == 0) flag(a.status, kStatusTimeout);
+    }
+    // Free the tensor memory once every role is done with it (a role that gave up has stopped touching it).
+    tc_fence_before();
+    __syncthreads();
+    pdl_trigger();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kGrpTmemCols) : "memory");
+    }
+}
+
+// ── bucketing ────────────────────────────────────────────────────────────────────────────────
+// One CTA.  Pairs (token, slot) -> sorted by expert (stable in token order); the shared expert, if any, is
+// expert E with every token.  Also the list of active experts, most tokens first (ties: lower id), so that
+// the experts with several passes start first.
+struct GroupPairsArgs {
+    const unsigned short* ids;   // [T] rows of top_k, stride in bytes
+    int ids_stride;
+    int T, top_k, E, has_shared;
+    GroupedWork* work;
+    int* active;
+    int* counts;     // [E + 1]
+    int* offsets;    // [E + 2]
+    int* pos;        // [T][top_k + 1]: sorted position of (token, slot); slot top_k = the shared expert
+    unsigned short* pair_token;  // [pairs]
+    int* status;
+};
+
+__global__ void __launch_bounds__(1024) group_pairs_kernel(GroupPairsArgs g) {
+    __shared__ int cnt[kRouterMaxExpertsGrouped + 1];
+    __shared__ int off[kRouterMaxExpertsGrouped + 2];
+    __shared__ int nact;
+    const int tid = threadIdx.x;
+    const int NE = g.E + 1;
+    pdl_wait();
+    for (int e = tid; e < NE; e += blockDim.x) cnt[e] = 0;
+    if (tid == 0) nact = 0;
+    __syncthreads();
+    const int total = g.T * g.top_k;
+    for (int i = tid; i < total; i += blockDim.x) {
+        const int t = i / g.top_k, s = i - t * g.top_k;
+        const unsigned e = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(g.ids) + (size_t)t * g.ids_stride)[s];
+        if (e < (unsigned)g.E) atomicAdd(&cnt[e], 1);
+        else flag(g.status, kStatusBadExpert);
+    }
+    if (tid == 0) cnt[g.E] = g.has_shared ? g.T : 0;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int e = 0; e < NE; ++e) {
+            off[e] = run;
+            run += cnt[e];
+        }
+        off[NE] = run;
+        g.work->n_pairs = run;
+    }
+    __syncthreads();
+    for (int e = tid; e < NE; e += blockDim.x) {
+        g.counts[e] = cnt[e];
+        g.offsets[e] = off[e];
+        if (cnt[e] > 0) {
+            int rank = 0;
+            for (int o = 0; o < NE; ++o)
+                if (cnt[o] > cnt[e] || (cnt[o] == cnt[e] && o < e && cnt[o] > 0)) ++rank;
+            g.active[rank] = e;
+            atomicAdd(&nact, 1);
+        }
+    }
+    // stable placement: thread e walks the pairs in token order (T * top_k <= 2048 entries, read from L1/L2)
+    for (int e = tid; e < g.E; e += blockDim.x) {
+        if (cnt[e] == 0) continue;
+        int p = off[e];
+        for (int t = 0; t < g.T; ++t) {
+            const unsigned short* row = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(g.ids) + (size_t)t * g.ids_stride);
+            for (int s = 0; s < g.top_k; ++s)
+                if (row[s] == e) {
+                    g.pair_token[p] = (unsigned short)t;
+                    g.pos[t * (g.top_k + 1) + s] = p;
+                    ++p;
+                }
+        }
+    }
+    if (g.has_shared)
+        for (int t = tid; t < g.T; t += blockDim.x) {
+            g.pair_token[off[g.E] + t] = (unsigned short)t;
+            g.pos[t * (g.top_k + 1) + g.top_k] = off[g.E] + t;
+        }
+    __syncthreads();
+    if (tid == 0) g.work->n_active = nact;
+    pdl_trigger();
+}
+
+// xg[p][perm(k)] = fp16(x[token(p)][k]): the tokens gathered in pair order, K order permuted per 8 columns.
+__global__ void __launch_bounds__(256) gather_tokens_kernel(const void* x, int x_dtype, int x_stride, const GroupedWork* work,
+                                                            const unsigned short* pair_token, __half* xg, int H) {
+    pdl_wait();
+    const int n_pairs = work->n_pairs;
+    const int items = H >> 3;
+    for (int p = blockIdx.x; p < n_pairs; p += gridDim.x) {
+        const unsigned char* row = reinterpret_cast<const unsigned char*>(x) + (size_t)pair_token[p] * x_stride;
+        for (int i = threadIdx.x; i < items; i += blockDim.x) {
+            float v[8];
+            load_x8(row, x_dtype, i, v);
+            const __half2 h0 = __floats2half2_rn(fminf(fmaxf(v[0], -65504.f), 65504.f), fminf(fmaxf(v[4], -65504.f), 65504.f));
+            const __half2 h1 = __floats2half2_rn(fminf(fmaxf(v[1], -65504.f), 65504.f), fminf(fmaxf(v[5], -65504.f), 65504.f));
+            const __half2 h2 = __floats2half2_rn(fminf(fmaxf(v[2], -65504.f), 65504.f), fminf(fmaxf(v[6], -65504.f), 65504.f));
+            const __half2 h3 = __floats2half2_rn(fminf(fmaxf(v[3], -65504.f), 65504.f), fminf(fmaxf(v[7], -65504.f), 65504.f));
+            uint4 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&h0);
+            o.y = *reinterpret_cast<const uint32_t*>(&h1);
+            o.z = *reinterpret_cast<const uint32_t*>(&h2);
+            o.w = *reinterpret_cast<const uint32_t*>(&h3);
+            reinterpret_cast<uint4*>(xg + (size_t)p * H)[i] = o;
+        }
+    }
+    pdl_trigger();
+}
+
+// out[t][r] = sum over the token's slots in plan order of w * y[pair][r], then the shared expert (fp32 FMAs,
+// cuda/src/kernels.cu:803-813).
+__global__ void __launch_bounds__(256) combine_pairs_kernel(const __half* y, const int* pos, const float* weights, int w_stride,
+                                                            int T, int top_k, int has_shared, float shared_weight, float* out,
+                                                            int out_stride, int out_accumulate, int H) {
+    pdl_wait();
+    const int t = blockIdx.y;
+    const float* wrow = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(weights) + (size_t)t * w_stride);
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) * 2; r < H; r += gridDim.x * blockDim.x * 2) {
+        float o0 = 0.f, o1 = 0.f;
+        for (int s = 0; s < top_k; ++s) {
+            const __half2 v = *reinterpret_cast<const __half2*>(y + (size_t)pos[t * (top_k + 1) + s] * H + r);
+            o0 = fmaf(wrow[s], __low2float(v), o0);
+            o1 = fmaf(wrow[s], __high2float(v), o1);
+        }
+        if (has_shared) {
+            const __half2 v = *reinterpret_cast<const __half2*>(y + (size_t)pos[t * (top_k + 1) + top_k] * H + r);
+            o0 = fmaf(shared_weight, __low2float(v), o0);
+            o1 = fmaf(shared_weight, __high2float(v), o1);
+        }
+        float* o = out + (size_t)t * out_stride + r;
+        if (out_accumulate) {
+            o[0] += o0;
+            o[1] += o1;
+        } else {
+            o[0] = o0;
+            o[1] = o1;
+        }
+    }
+    pdl_trigger();
+}
+
+}  // namespace vib3
+
+using namespace vib3;
+
+// ── host side ────────────────────────────────────────────────────────────────────────────────
+
+namespace {
+
+struct GroupedHandle {
+    GroupedMaps maps;
+    unsigned char* pool_base;
+    size_t capacity_pages;
+    int H, I, rpp_gu, rpp_dn, max_tokens, top_k, E;
+    // workspace carve-up (device pointers)
+    GroupedWork* work;
+    int *active, *counts, *offsets, *pos;
+    unsigned short* pair_token;
+    __half *xg, *act, *y;
+    int max_pairs;
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// 3-D map over the pool: x = byte in a row (row_bytes), y = row in the page (rows), z = pool slot.
+int make_pool_map(CUtensorMap* m, void* base, size_t row_bytes, int rows, size_t slots, int box_x, int box_y, bool swizzle) {
+    const cuuint64_t dims[3] = {(cuuint64_t)row_bytes, (cuuint64_t)rows, (cuuint64_t)slots};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)(2u << 20)};
+    const cuuint32_t box[3] = {(cuuint32_t)box_x, (cuuint32_t)box_y, 1};
+    const cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : VIB3_ERR_STATE;
+}
+
+// 2-D fp16 map [rows][cols], box 64 columns x box_rows, 128-byte swizzle (the K-major operand layout).
+int make_rows_map(CUtensorMap* m, void* base, int cols, int rows, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : VIB3_ERR_STATE;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Carve {
+    size_t work, active, counts, offsets, pos, pair_token, xg, act, y, total;
+};
+
+Carve carve(int max_tokens, int top_k, int E, int H, int I) {
+    Carve c;
+    const size_t pairs = (size_t)max_tokens * (top_k + 1);
+    size_t o = 0;
+    c.work = o; o = align_up(o + sizeof(GroupedWork), 256);
+    c.active = o; o = align_up(o + (E + 1) * sizeof(int), 256);
+    c.counts = o; o = align_up(o + (E + 1) * sizeof(int), 256);
+    c.offsets = o; o = align_up(o + (E + 2) * sizeof(int), 256);
+    c.pos = o; o = align_up(o + pairs * sizeof(int), 256);
+    c.pair_token = o; o = align_up(o + pairs * sizeof(unsigned short), 256);
+    c.xg = o; o = align_up(o + pairs * (size_t)H * 2, 1024);
+    c.act = o; o = align_up(o + pairs * (size_t)I * 2, 1024);
+    c.y = o; o = align_up(o + pairs * (size_t)H * 2, 1024);
+    c.total = o;
+    return c;
+}
+
+template <class K, class... Args>
+int launch_pdl(K kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+constexpr size_t kGrpSmem = 1024 + (size_t)kGrpStages * kGrpStageBytes + 64 * (kGrpMaxN + 1) * sizeof(float) + 32 * sizeof(uint64_t);
+
+}  // namespace
+
+extern "C" size_t vib3_moe_grouped_workspace_bytes(int max_tokens, int top_k, int num_experts, int hidden_dim, int expert_hidden_dim) {
+    if (max_tokens <= 0 || top_k <= 0 || num_experts <= 0 || hidden_dim <= 0 || expert_hidden_dim <= 0) return 0;
+    return carve(max_tokens, top_k, num_experts, hidden_dim, expert_hidden_dim).total;
+}
+
+extern "C" int vib3_moe_grouped_prewarm(void* pool_base, size_t capacity_pages, int num_experts, int top_k, int hidden_dim,
+                                        int expert_hidden_dim, int rows_per_page_gate_up, int rows_per_page_down,
+                                        int last_page_rows_gate_up, int last_page_rows_down, int max_tokens, void* workspace,
+                                        size_t workspace_bytes, void** handle_out) {
+    if (!pool_base || !workspace || !handle_out) return VIB3_ERR_NULL;
+    if (num_experts <= 0 || num_experts > kRouterMaxExpertsGrouped || top_k <= 0 || top_k > 16) return VIB3_ERR_COUNT;
+    if (max_tokens <= 0 || max_tokens > kGrpMaxTokens) return VIB3_ERR_COUNT;
+    if (hidden_dim % kGrpSlabK || expert_hidden_dim % kGrpSlabK) return VIB3_ERR_UNSUPPORTED;
+    if (((uintptr_t)pool_base & 15) || ((uintptr_t)workspace & 1023)) return VIB3_ERR_ALIGN;
+    const Carve c = carve(max_tokens, top_k, num_experts, hidden_dim, expert_hidden_dim);
+    if (workspace_bytes < c.total) return VIB3_ERR_CAPACITY;
+    if (!encode_fn()) return VIB3_ERR_UNSUPPORTED;
+    GroupedHandle* h = new (std::nothrow) GroupedHandle();
+    if (!h) return VIB3_ERR_STATE;
+    unsigned char* pb = static_cast<unsigned char*>(pool_base);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    h->pool_base = pb; h->capacity_pages = capacity_pages;
+    h->H = hidden_dim; h->I = expert_hidden_dim; h->rpp_gu = rows_per_page_gate_up; h->rpp_dn = rows_per_page_down;
+    h->max_tokens = max_tokens; h->top_k = top_k; h->E = num_experts;
+    h->work = reinterpret_cast<GroupedWork*>(ws + c.work);
+    h->active = reinterpret_cast<int*>(ws + c.active);
+    h->counts = reinterpret_cast<int*>(ws + c.counts);
+    h->offsets = reinterpret_cast<int*>(ws + c.offsets);
+    h->pos = reinterpret_cast<int*>(ws + c.pos);
+    h->pair_token = reinterpret_cast<unsigned short*>(ws + c.pair_token);
+    h->xg = reinterpret_cast<__half*>(ws + c.xg);
+    h->act = reinterpret_cast<__half*>(ws + c.act);
+    h->y = reinterpret_cast<__half*>(ws + c.y);
+    h->max_pairs = max_tokens * (top_k + 1);
+    const size_t gu_code_row = hidden_dim / 2, gu_scale_row = hidden_dim / 16;
+    const size_t dn_code_row = expert_hidden_dim / 2, dn_scale_row = expert_hidden_dim / 16;
+    int e = 0;
+    e |= make_pool_map(&h->maps.gu_codes, pb, gu_code_row, rows_per_page_gate_up, capacity_pages, 128, 64, true);
+    e |= make_pool_map(&h->maps.gu_scales_full, pb + (size_t)rows_per_page_gate_up * gu_code_row, gu_scale_row, rows_per_page_gate_up,
+                       capacity_pages, 16, 64, false);
+    e |= make_pool_map(&h->maps.gu_scales_last, pb + (size_t)last_page_rows_gate_up * gu_code_row, gu_scale_row, last_page_rows_gate_up,
+                       capacity_pages, 16, 64, false);
+    e |= make_pool_map(&h->maps.dn_codes, pb, dn_code_row, rows_per_page_down, capacity_pages, 128, 128, true);
+    e |= make_pool_map(&h->maps.dn_scales_full, pb + (size_t)rows_per_page_down * dn_code_row, dn_scale_row, rows_per_page_down,
+                       capacity_pages, 16, 128, false);
+    e |= make_pool_map(&h->maps.dn_scales_last, pb + (size_t)last_page_rows_down * dn_code_row, dn_scale_row, last_page_rows_down,
+                       capacity_pages, 16, 128, false);
+    e |= make_rows_map(&h->maps.xg16, h->xg, hidden_dim, h->max_pairs, 16);
+    e |= make_rows_map(&h->maps.xg64, h->xg, hidden_dim, h->max_pairs, 64);
+    e |= make_rows_map(&h->maps.act16, h->act, expert_hidden_dim, h->max_pairs, 16);
+    e |= make_rows_map(&h->maps.act64, h->act, expert_hidden_dim, h->max_pairs, 64);
+    if (e) {
+        delete h;
+        return VIB3_ERR_STATE;
+    }
+    cudaError_t ce = cudaFuncSetAttribute(moe_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGrpSmem);
+    if (ce == cudaSuccess) ce = cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGrpSmem);
+    if (ce != cudaSuccess) {
+        delete h;
+        return (int)ce;
+    }
+    *handle_out = h;
+    return VIB3_OK;
+}
+
+extern "C" void vib3_moe_grouped_destroy(void* handle) { delete static_cast<GroupedHandle*>(handle); }
+
+extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_dtype, int x_stride_bytes, int n_tokens,
+                                            const unsigned short* ids, int ids_stride_bytes, const float* weights,
+                                            int weights_stride_bytes, const void* page_table, const void* shared_pages,
+                                            float shared_weight, int pages_per_segment, float* out, int out_stride,
+                                            int out_accumulate, int* status, void* stream) {
+    GroupedHandle* h = static_cast<GroupedHandle*>(handle);
+    if (!h || !x || !ids || !weights || !page_table || !out) return VIB3_ERR_NULL;
+    if (n_tokens <= 0 || n_tokens > h->max_tokens) return VIB3_ERR_COUNT;
+    if (x_dtype < X_F32 || x_dtype > X_BF16) return VIB3_ERR_UNSUPPORTED;
+    if (pages_per_segment <= 0 || pages_per_segment > kMaxPages) return VIB3_ERR_COUNT;
+    if (((uintptr_t)x & 15) || (x_stride_bytes & 15) || (ids_stride_bytes & 1) || (weights_stride_bytes & 3) || ((uintptr_t)out & 7) ||
+        (out_stride & 1) || out_stride < h->H)
+        return VIB3_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int has_shared = shared_pages ? 1 : 0;
+
+    GroupPairsArgs g;
+    g.ids = ids; g.ids_stride = ids_stride_bytes; g.T = n_tokens; g.top_k = h->top_k; g.E = h->E; g.has_shared = has_shared;
+    g.work = h->work; g.active = h->active; g.counts = h->counts; g.offsets = h->offsets; g.pos = h->pos;
+    g.pair_token = h->pair_token; g.status = status;
+    int err = launch_pdl(group_pairs_kernel, dim3(1), 1024, 0, st, g);
+    if (err) return err;
+    err = launch_pdl(gather_tokens_kernel, dim3(min(h->max_pairs, 2 * sm_count())), 256, 0, st, x, x_dtype, x_stride_bytes,
+                     (const GroupedWork*)h->work, (const unsigned short*)h->pair_token, h->xg, h->H);
+    if (err) return err;
+
+    GroupedArgs a;
+    a.page_table = (const PageEntry*)page_table; a.shared_pages = (const PageEntry*)shared_pages; a.pool_base = h->pool_base;
+    a.work = h->work; a.active = h->active; a.counts = h->counts; a.offsets = h->offsets; a.act = h->act; a.y = h->y;
+    a.E = h->E; a.P = pages_per_segment; a.H = h->H; a.I = h->I; a.rpp_gu = h->rpp_gu; a.rpp_dn = h->rpp_dn; a.status = status;
+    err = launch_pdl(moe_grouped_kernel<false>, dim3(sm_count()), kGrpThreads, kGrpSmem, st, h->maps, a);
+    if (err) return err;
+    err = launch_pdl(moe_grouped_kernel<true>, dim3(sm_count()), kGrpThreads, kGrpSmem, st, h->maps, a);
+    if (err) return err;
+    return launch_pdl(combine_pairs_kernel, dim3(4, n_tokens), 256, 0, st, (const __half*)h->y, (const int*)h->pos, weights,
+                      weights_stride_bytes, n_tokens, h->top_k, has_shared, shared_weight, out, out_stride, out_accumulate, h->H);
+}

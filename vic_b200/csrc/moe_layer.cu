@@ -214,6 +214,9 @@ int sm_count() {
 
 std::atomic<int> g_use_pipeline{1};
 std::atomic<int> g_use_pdl{1};
+// 1 = vib3_launch_moe_layer_routed_int4_paged lets the gate/up kernel route the token in its prologue where the
+// shapes allow; 0 (default: measured 2 us per layer-token faster on the Kimi shape) = the router is a launch of its own.
+std::atomic<int> g_route_in_kernel{0};
 
 template <class K>
 static int ensure_smem(K kernel, size_t bytes) {
@@ -290,7 +293,8 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, const Route
     int err = 0;
     if (router) {
         // the gate/up kernel routes the token itself where the shapes allow; otherwise the router is a launch of its own
-        err = ((phases & 1) && use_pipe) ? launch_gateup_pipelined(a, st, router) : VIB3_ERR_UNSUPPORTED;
+        err = ((phases & 1) && use_pipe && g_route_in_kernel.load(std::memory_order_relaxed)) ? launch_gateup_pipelined(a, st, router)
+                                                                                               : VIB3_ERR_UNSUPPORTED;
         if (err == 0) phases &= ~1;
         else if (err != VIB3_ERR_UNSUPPORTED) return err;
         else if ((err = launch_router_args(*router, st)) != 0) return err;
@@ -334,11 +338,12 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, const Route
         rows_per_page_down, group_size, status, stream
 
 // key 0: staged (bulk-copy) kernels on/off; key 1: programmatic dependent launch of the staged
-// kernels on/off.  Atomic exchanges: safe against concurrent launches from other threads (a launch
+// kernels on/off; key 2: routing inside the gate/up kernel on/off.  Atomic exchanges: safe against concurrent launches from other threads (a launch
 // sees the old or the new value).  Returns the previous value, or VIB3_ERR_UNSUPPORTED.
 extern "C" int vib3_config_set(int key, int value) {
     if (key == 0) return g_use_pipeline.exchange(value ? 1 : 0);
     if (key == 1) return g_use_pdl.exchange(value ? 1 : 0);
+    if (key == 2) return g_route_in_kernel.exchange(value ? 1 : 0);
     return VIB3_ERR_UNSUPPORTED;
 }
 

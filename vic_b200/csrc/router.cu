@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_kernel(RouterArgs a) {
     static_assert(kSeqRingFloats <= kRouterXMax, "the recomputation ring reuses the activation buffer");
     // let a dependent kernel (launched with programmatic stream serialization) begin its prologue
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    router_args_of_token(a, blockIdx.y);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int expert = blockIdx.x * kRouterWarps + warp;
     const int row = min(expert, a.E - 1);  // every warp reaches the barrier below
@@ -162,31 +163,31 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(RouterArgs 
 }
 
 template <int XD, int WD>
-static int launch_router_t(const RouterArgs& a, cudaStream_t st) {
+static int launch_router_t(const RouterArgs& a, cudaStream_t st, int n_tokens) {
     // The largest shared-memory carve-out: the gate/up kernel that follows sizes itself to fit beside one
     // router CTA on an SM, which only works if both want the same SM configuration.
     static const cudaError_t carve = cudaFuncSetAttribute(router_kernel<XD, WD>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                                           (int)cudaSharedmemCarveoutMaxShared);
     (void)carve;
-    const int grid = (a.E + kRouterWarps - 1) / kRouterWarps;
+    const dim3 grid((a.E + kRouterWarps - 1) / kRouterWarps, n_tokens);
     router_kernel<XD, WD><<<grid, kRouterThreads, 0, st>>>(a);
     return (int)cudaGetLastError();
 }
 
 template <int WD>
-static int launch_router_w(const RouterArgs& a, cudaStream_t st) {
+static int launch_router_w(const RouterArgs& a, cudaStream_t st, int n_tokens) {
     const uintptr_t walign = WD == W_F32 ? 15 : 7;
     const bool vec = a.H % (a.x_dtype == X_F32 ? 4 : 8) == 0 && a.H <= kRouterXMax && ((uintptr_t)a.x & 15) == 0 &&
-                     ((uintptr_t)a.W & walign) == 0;
-    if (!vec) return launch_router_t<-1, WD>(a, st);
-    if (a.x_dtype == X_F32) return launch_router_t<X_F32, WD>(a, st);
-    if (a.x_dtype == X_F16) return launch_router_t<X_F16, WD>(a, st);
-    return launch_router_t<X_BF16, WD>(a, st);
+                     (a.x_stride & 15) == 0 && ((uintptr_t)a.W & walign) == 0;
+    if (!vec) return launch_router_t<-1, WD>(a, st, n_tokens);
+    if (a.x_dtype == X_F32) return launch_router_t<X_F32, WD>(a, st, n_tokens);
+    if (a.x_dtype == X_F16) return launch_router_t<X_F16, WD>(a, st, n_tokens);
+    return launch_router_t<X_BF16, WD>(a, st, n_tokens);
 }
 
-static int launch_router(const RouterArgs& a, cudaStream_t st) {
-    if (a.w_dtype == W_F32) return launch_router_w<W_F32>(a, st);
-    if (a.w_dtype == W_F16) return launch_router_w<W_F16>(a, st);
+static int launch_router(const RouterArgs& a, cudaStream_t st, int n_tokens = 1) {
+    if (a.w_dtype == W_F32) return launch_router_w<W_F32>(a, st, n_tokens);
+    if (a.w_dtype == W_F16) return launch_router_w<W_F16>(a, st, n_tokens);
     return VIB3_ERR_UNSUPPORTED;
 }
 
@@ -280,4 +281,23 @@ extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void
     if (int e = make_router_args(x, x_dtype, W, w_dtype, scores_buf, bias, logit_offset, out_ids, out_weights, hidden_dim,
                                  num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order, workspace, a)) return e;
     return launch_router(a, (cudaStream_t)stream);
+}
+
+// The single-launch router for n_tokens tokens in one launch (grid y = token): token t reads x + t * x_stride_bytes
+// and writes scores_buf + t * scores_stride (3E floats each), out_ids + t * ids_stride, out_weights + t *
+// weights_stride, and uses the four workspace words at workspace + 4 t.  The router's weights are read from
+// HBM once and by the other tokens from L2.
+extern "C" int vib3_launch_router_topk_batch(const void* x, int x_dtype, int x_stride_bytes, int n_tokens, const void* W, int w_dtype,
+                                             float* scores_buf, int scores_stride, const float* bias, const float* logit_offset,
+                                             unsigned short* out_ids, int ids_stride, float* out_weights, int weights_stride,
+                                             int hidden_dim, int num_experts, int top_k, int scoring_mode, float scaling_factor,
+                                             int normalize, int exact_order, unsigned int* workspace, void* stream) {
+    RouterArgs a;
+    if (int e = make_router_args(x, x_dtype, W, w_dtype, scores_buf, bias, logit_offset, out_ids, out_weights, hidden_dim,
+                                 num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order, workspace, a)) return e;
+    if (n_tokens <= 0 || n_tokens > 65535) return VIB3_ERR_COUNT;
+    if (x_stride_bytes <= 0 || scores_stride < 3 * num_experts || ids_stride < top_k || weights_stride < top_k) return VIB3_ERR_SHAPE;
+    a.x_stride = x_stride_bytes; a.scores_stride = scores_stride; a.ids_stride = ids_stride; a.weights_stride = weights_stride;
+    a.counter_stride = 4;
+    return launch_router(a, (cudaStream_t)stream, n_tokens);
 }

@@ -31,7 +31,22 @@ struct RouterArgs {
     float scaling;
     int normalize;
     int exact_order;
+    // batched launch (grid y = token): distances between the tokens' vectors / buffers; zero for one token
+    int x_stride;        // bytes
+    int scores_stride;   // floats
+    int ids_stride;      // entries
+    int weights_stride;  // entries
+    int counter_stride;  // words
 };
+
+// The arguments of token blockIdx.y of a batched launch.
+__device__ __forceinline__ void router_args_of_token(RouterArgs& a, int t) {
+    a.x = reinterpret_cast<const unsigned char*>(a.x) + (size_t)t * a.x_stride;
+    a.scores += (size_t)t * a.scores_stride;
+    if (a.out_ids) a.out_ids += (size_t)t * a.ids_stride;
+    if (a.out_weights) a.out_weights += (size_t)t * a.weights_stride;
+    if (a.counter) a.counter += (size_t)t * a.counter_stride;
+}
 
 __device__ __forceinline__ float load_w(const void* W, int w_dtype, size_t i) {
     return w_dtype == W_F32 ? reinterpret_cast<const float*>(W)[i]
@@ -246,25 +261,67 @@ __device__ inline float sequential_logits(const RouterArgs& a, TopKSmem& sm, flo
             const int half = gb & 1;
             if (gb >= 2 && !seq_bar_wait(&sm.seq_empty[half], ((gb >> 1) - 1) & 1)) { sm.failed = 1; break; }
             const int n = min(kSeqBlock, a.H - b * kSeqBlock);
-            // (candidate, element) pairs of the block, 16 loads in flight per lane
-            const int total = nc * n;
-            for (int t0 = (hw * 32 + lane); t0 < total; t0 += nh * 32 * 8) {
-                float xv[8], wv[8];
+            // (candidate, 4-element item) pairs of the block: one 16-byte (fp16 weights: 8-byte) load of the
+            // weights and one of the activations per item, all of a lane's items requested before any is used
+            // (one round trip per block); rows that are not 16-byte aligned take the scalar path
+            const bool vec = a.H % 4 == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.W & 15) == 0 && n % 4 == 0;
+            if (vec) {
+                const int n4 = n >> 2, total = nc * n4;
+                constexpr int U = 4;
+                for (int t0 = hw * 32 + lane; t0 < total; t0 += nh * 32 * U) {
+                    float4 xv[U], wv[U];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int t = t0 + u * nh * 32;
-                    const bool in = t < total;
-                    const int c = in ? t / n : 0, i = in ? t - c * n : 0;
-                    const int d = b * kSeqBlock + i;
-                    xv[u] = in ? load_x_as_f32(a.x, a.x_dtype, d) : 0.f;
-                    wv[u] = in ? load_w(a.W, a.w_dtype, (size_t)cands[c] * a.H + d) : 0.f;
+                    for (int u = 0; u < U; ++u) {
+                        const int t = t0 + u * nh * 32;
+                        const bool in = t < total;
+                        const int c = in ? t / n4 : 0, i = in ? t - c * n4 : 0;
+                        const int item = (b * kSeqBlock >> 2) + i;
+                        if (a.x_dtype == X_F32) xv[u] = __ldg(reinterpret_cast<const float4*>(a.x) + item);
+                        else {
+                            const uint2 r2 = __ldg(reinterpret_cast<const uint2*>(a.x) + item);
+                            if (a.x_dtype == X_F16) {
+                                const __half2 p0 = *reinterpret_cast<const __half2*>(&r2.x), p1 = *reinterpret_cast<const __half2*>(&r2.y);
+                                xv[u] = make_float4(__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1));
+                            } else {
+                                xv[u] = make_float4(__uint_as_float(r2.x << 16), __uint_as_float(r2.x & 0xFFFF0000u),
+                                                    __uint_as_float(r2.y << 16), __uint_as_float(r2.y & 0xFFFF0000u));
+                            }
+                        }
+                        const size_t wi = ((size_t)cands[c] * a.H >> 2) + item;
+                        if (a.w_dtype == W_F32) wv[u] = __ldcg(reinterpret_cast<const float4*>(a.W) + wi);
+                        else wv[u] = WItem<W_F16>::cvt(__ldcg(reinterpret_cast<const uint2*>(a.W) + wi));
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int t = t0 + u * nh * 32;
+                        if (t < total) {
+                            const int c = t / n4, i = t - c * n4;
+                            *reinterpret_cast<float4*>(ring + (c * 2 + half) * kSeqBlock + 4 * i) =
+                                make_float4(__fmul_rn(xv[u].x, wv[u].x), __fmul_rn(xv[u].y, wv[u].y), __fmul_rn(xv[u].z, wv[u].z),
+                                            __fmul_rn(xv[u].w, wv[u].w));
+                        }
+                    }
                 }
+            } else {
+                const int total = nc * n;
+                for (int t0 = (hw * 32 + lane); t0 < total; t0 += nh * 32 * 8) {
+                    float xv[8], wv[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int t = t0 + u * nh * 32;
-                    if (t < total) {
-                        const int c = t / n, i = t - c * n;
-                        ring[(c * 2 + half) * kSeqBlock + i] = __fmul_rn(xv[u], wv[u]);
+                    for (int u = 0; u < 8; ++u) {
+                        const int t = t0 + u * nh * 32;
+                        const bool in = t < total;
+                        const int c = in ? t / n : 0, i = in ? t - c * n : 0;
+                        const int d = b * kSeqBlock + i;
+                        xv[u] = in ? load_x_as_f32(a.x, a.x_dtype, d) : 0.f;
+                        wv[u] = in ? load_w(a.W, a.w_dtype, (size_t)cands[c] * a.H + d) : 0.f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int t = t0 + u * nh * 32;
+                        if (t < total) {
+                            const int c = t / n, i = t - c * n;
+                            ring[(c * 2 + half) * kSeqBlock + i] = __fmul_rn(xv[u], wv[u]);
+                        }
                     }
                 }
             }

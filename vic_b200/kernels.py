@@ -132,6 +132,21 @@ def router_topk_ex(x: torch.Tensor, W: torch.Tensor, scores_buf, bias, out_ids, 
         top_k, scoring_mode, scaling_factor, int(normalize), int(exact_order), _ptr(workspace), _stream(stream)))
 
 
+def router_topk_batch(xs: torch.Tensor, W: torch.Tensor, scores_buf: torch.Tensor, bias, logit_offset, out_ids: torch.Tensor,
+                      out_weights: torch.Tensor, top_k: int, scoring_mode: int, scaling_factor: float, normalize: bool,
+                      exact_order: bool, workspace: torch.Tensor, stream: Optional[int] = None) -> None:
+    """The single-launch router for T tokens in ONE launch (grid y = token): xs [T, H]; scores_buf [T, 3E] fp32,
+    out_ids [T, >= top_k] int16, out_weights [T, >= top_k] fp32, workspace [T, 4] int32 (zero before the first call)."""
+    E, H = W.shape
+    T = xs.shape[0]
+    w_dtype = {torch.float16: W_F16, torch.float32: W_F32}[W.dtype]
+    check("router_topk_batch", lib().vib3_launch_router_topk_batch(
+        _ptr(xs), x_dtype_code(xs), xs.stride(0) * xs.element_size(), T, _ptr(W), w_dtype, _ptr(scores_buf),
+        scores_buf.stride(0), _ptr(bias), _ptr(logit_offset), _ptr(out_ids), out_ids.stride(0), _ptr(out_weights),
+        out_weights.stride(0), H, E, top_k, scoring_mode, scaling_factor, int(normalize), int(exact_order), _ptr(workspace),
+        _stream(stream)))
+
+
 def moe_layer_int4_paged(x: torch.Tensor, page_table: int, num_experts: int, shared_pages: int, expert_ids,
                          expert_weights, top_k: int, shared_weight: float, act_scratch, out, out_accumulate: bool,
                          hidden_dim: int, expert_hidden_dim: int, pages_per_segment: int, rows_per_page_gate_up: int,

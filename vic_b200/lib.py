@@ -69,6 +69,12 @@ SIGNATURES = {
                                       _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "vib3_launch_sum_rows_f32": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "vib3_launch_select_local_experts": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "vib3_moe_grouped_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i, _i]),
+    "vib3_moe_grouped_prewarm": (_i, [_vp, C.c_size_t, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, C.c_size_t, C.POINTER(_vp)]),
+    "vib3_moe_grouped_destroy": (None, [_vp]),
+    "vib3_launch_moe_grouped_int4": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _i, _vp, _i, _i, _vp, _vp]),
+    "vib3_launch_router_topk_batch": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _i,
+                                           _i, _vp, _vp]),
     "vib3_config_set": (_i, [_i, _i]),
     "vib3_pool_create": (_vp, [_vp, C.c_size_t, C.c_uint64]),
     "vib3_pool_destroy": (None, [_vp]),

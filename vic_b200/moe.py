@@ -1,7 +1,7 @@
 """The MoE sublayer of one decode token on the GPU: router -> experts -> accumulate.
 
-``MoeDecoder.forward_layer`` is the fused path (2 launches — the gate/up kernel routes the token in its
-prologue — or 3 for shapes it cannot route; no host synchronisation, graph capturable).  ``run_moe_sublayer_paged_calls`` drives the per-page entry points in the order the
+``MoeDecoder.forward_layer`` is the fused path (3 launches, or 2 when the library is set to route inside
+the gate/up kernel; no host synchronisation, graph capturable).  ``run_moe_sublayer_paged_calls`` drives the per-page entry points in the order the
 reference engine does (src/runtime/engine.rs:5052-5360, :5801-6306) and exists so that path stays
 exercised and comparable."""
 from __future__ import annotations
@@ -35,7 +35,7 @@ class MoeDecoder:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.tables = [model.page_table(l) for l in range(model.n_layers)]
         self.shared_tables = [model.shared_table(l) for l in range(model.n_layers)]
-        self.launches_per_layer = 2 if (sh.hidden % 256 == 0 and sh.intermediate % 256 == 0) else 3
+        self.launches_per_layer = 3
 
     def route(self, layer: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
               logit_offset: Optional[torch.Tensor] = None) -> None:
