@@ -65,6 +65,9 @@ int vib3_launch_weighted_accumulate_f32(void* out_f32, const void* y_f16, float 
 int vib3_launch_weighted_accumulate_f32_f32(void* out_f32, const void* y_f32, float w, int dim, void* stream);
 /* replaces cuda/src/kernels.cu:1132: acc += layer_out */
 int vib3_launch_residual_add_f32_f32(void* acc_f32, const void* layer_out_f32, int dim, void* stream);
+/* replaces cuda/src/kernels.cu:1178: output = input * inv_rms(input) * weight (fp32 in and out, fp16 weight) */
+int vib3_launch_rms_norm_f32(const void* input_f32, void* output_f32, const void* weight_f16, int hidden_dim, float eps,
+                             void* stream);
 /* replace cuda/src/kernels.cu:1143 and :1477: logits[e] = W[e,:] . x, W fp16 [E,H] */
 int vib3_launch_router_gemv(const void* x_f16, const void* W_f16, float* scores, int hidden_dim, int num_experts,
                             void* stream);
@@ -194,6 +197,22 @@ int vib3_moe_layer_step_host(const void* x_host, int x_dtype, void* x_dev, const
                              float* out_host, int hidden_dim, int expert_hidden_dim, int pages_per_segment,
                              int rows_per_page_gate_up, int rows_per_page_down, int group_size, int* status,
                              void* stream);
+/* vib3_moe_layer_step_host bound to one layer as a CUDA graph: create once (allocates pinned staging memory and
+ * the graph: at start-up, outside any stream capture, on a non-default stream; the role of
+ * vib3_moe_prewarm_gpu_bufs, cuda/src/kernels.cu:6507), then per token vib3_moe_step_run(handle, x_host, stream):
+ * host-to-host copy of the token into the staging buffer, one graph launch (copy in, router, gate/up, down storing
+ * into out_host_pinned), stream synchronisation.  Arguments as for vib3_moe_layer_step_host; out_host_pinned must
+ * be pinned (device-addressable) host memory and receives every token's result. */
+int vib3_moe_step_create(int x_dtype, void* x_dev, const void* router_w, int w_dtype, float* scores_buf,
+                         const float* bias_or_null, unsigned short* ids_dev, float* weights_dev, int num_experts, int top_k,
+                         int scoring_mode, float scaling_factor, int normalize, int exact_order, unsigned int* workspace,
+                         const void* page_table, const void* shared_pages, float shared_weight, void* act_scratch,
+                         float* out_host_pinned, int hidden_dim, int expert_hidden_dim, int pages_per_segment,
+                         int rows_per_page_gate_up, int rows_per_page_down, int group_size, int* status, void* stream,
+                         void** handle_out);
+int vib3_moe_step_run(void* handle, const void* x_host, void* stream);
+void vib3_moe_step_destroy(void* handle);
+
 /* Grouped form for expert parallelism: one launch pair for the (token, expert) pairs of SEVERAL tokens
  * that this GPU owns.  pair_experts / pair_weights / pair_tokens: device lists in ascending token order
  * (as vib3_launch_select_local_pairs writes them), *num_pairs_dev their length; this launch takes the
@@ -247,12 +266,26 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
                                              int rows_per_page_gate_up, int rows_per_page_down, int group_size,
                                              int* status, void* stream);
 
+/* The steps either side of the MoE sublayer in the reference's layer loop — residual_add_f32_f32
+ * (cuda/src/kernels.cu:1132, called at src/runtime/engine.rs:5302) and the next rms_norm_f32 (:1178, called at
+ * engine.rs:5072) — as one launch over n_tokens rows: hidden[t] += delta[t] + delta2[t] (either may be NULL;
+ * delta2 is fp32 with a stride in floats: e.g. the previous MoE sublayer's output summed over expert-parallel ranks),
+ * x_out[t] = cast(hidden[t] * inv_rms(hidden[t]) * weight) (weight_f16 NULL: no weight).  Dtypes VIB3_X_*;
+ * strides of delta and x_out in bytes, of hidden in floats.  center != 0 (no counterpart in the reference) removes
+ * the row's mean before normalising: for stacks of synthetic layers whose uniformly drawn INT4 codes have mean -0.5
+ * (a common term that feeds itself through the residual stream).  With out_accumulate = 1 in the MoE launch that
+ * follows, a layer is this launch plus the MoE launches. */
+int vib3_launch_residual_rms_norm(float* hidden, int hidden_stride, const void* delta_or_null, int delta_dtype,
+                                  int delta_stride_bytes, const float* delta2_or_null, int delta2_stride,
+                                  const void* weight_f16_or_null, float eps, int center, void* x_out, int x_dtype,
+                                  int x_stride_bytes, int hidden_dim, int n_tokens, void* stream);
+
 /* ── Grouped multi-token layer (every distinct expert read once; tcgen05 tensor-core tiles) ── */
 /* No counterpart in the reference, whose prefill runs the batch-1 path token by token
  * (src/runtime/engine.rs:1837-1838); the nearest precedent is its fused NVFP4 expert launch
  * (cuda/src/kernels.cu:5357-5612, :5868).  Bytes of device scratch vib3_moe_grouped_prewarm needs. */
 size_t vib3_moe_grouped_workspace_bytes(int max_tokens, int top_k, int num_experts, int hidden_dim,
-                                        int expert_hidden_dim);
+                                        int expert_hidden_dim, int rows_per_page_gate_up, int rows_per_page_down);
 /* Builds the TMA tensor maps of the grouped kernels over a page pool (pool_base: start of the pool's
  * single allocation, 16-byte aligned, capacity_pages slots of 2 MiB) and over the caller's scratch
  * (workspace, 1024-byte aligned, at least vib3_moe_grouped_workspace_bytes).  hidden_dim and
@@ -267,14 +300,16 @@ int vib3_moe_grouped_prewarm(void* pool_base, size_t capacity_pages, int num_exp
 void vib3_moe_grouped_destroy(void* handle);
 /* One MoE sublayer for n_tokens (<= max_tokens <= 128) tokens: ids / weights are the tokens' routing
  * (rows of top_k entries, strides in bytes, device), x the activations (rows x_stride_bytes apart), out
- * [n_tokens] fp32 rows out_stride floats apart (overwritten, or added to).  Five launches (bucketing, token
- * gather, gate/up, down, per-token combine in plan order), no host synchronisation.  The pages of the
+ * [n_tokens] fp32 rows out_stride floats apart (overwritten, or added to).  Only the pairs whose expert lies
+ * in [expert_lo, expert_hi) are computed (0 and num_experts: all; an expert-parallel rank passes its own range
+ * and sums the ranks' outputs afterwards), and the shared expert only if shared_pages is given.  Six launches (bucketing, token
+ * gather, work-unit tables, gate/up, down, per-token combine in plan order), no host synchronisation.  The pages of the
  * page tables must lie in the pool given to vib3_moe_grouped_prewarm. */
 int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_dtype, int x_stride_bytes, int n_tokens,
                                  const unsigned short* ids, int ids_stride_bytes, const float* weights,
                                  int weights_stride_bytes, const void* page_table, const void* shared_pages,
-                                 float shared_weight, int pages_per_segment, float* out, int out_stride,
-                                 int out_accumulate, int* status, void* stream);
+                                 float shared_weight, int pages_per_segment, int expert_lo, int expert_hi, float* out,
+                                 int out_stride, int out_accumulate, int* status, void* stream);
 
 /* Library options.  key 0: use the bulk-copy staged MoE kernels where the shape allows (default 1);
  * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
@@ -329,6 +364,47 @@ typedef struct vib3_resolved_page {
 } vib3_resolved_page;
 int vib3_planner_plan_layer(const vib3_pool* pool, uint16_t layer, const uint16_t* expert_ids, int num_active,
                             int pages_per_segment, vib3_resolved_page* out_pages, int max_pages);
+
+/* ── `.vib3` container: INT4 quantiser, page-split writer, reader (host only) ───────────── */
+/* Mirrors quantize_weights_to_int4 (src/compute/kernels.rs:3778-3831), add_pages_from_data
+ * (src/storage/convert.rs:1841-1901), Vib3Writer::finalize and Vib3File::open
+ * (src/storage/format.rs:842-1090, :241-339) for uncompressed INT4 pages. */
+/* bytes of a quantised [rows, cols] matrix: rows * ceil(cols / 2) codes + rows * ceil(cols / 32) 16-bit scales */
+size_t vib3_int4_matrix_bytes(int rows, int cols);
+/* group-32 quantisation: scale = max|w| / 7 (1 for an all-zero group), q = clamp(round(w / scale) + 8, 0, 15), low
+ * nibble = even column.  scale_format 0: bf16 (what the reference's quantiser writes), 1: fp16 (what its CUDA
+ * kernels and this library's kernels decode). */
+int vib3_quantize_int4(const float* w, int rows, int cols, int scale_format, uint8_t* out);
+typedef struct vib3_writer vib3_writer;
+vib3_writer* vib3_writer_create(const char* path, const char* metadata_json, uint32_t num_layers, uint32_t num_experts,
+                                uint32_t num_active_experts, uint32_t hidden_dim, uint32_t expert_hidden_dim);
+/* cuts a quantised matrix into 2 MiB pages (rows_per_page = 2 MiB / bytes_per_row) and queues them; returns the
+ * number of pages */
+int vib3_writer_add_int4_matrix(vib3_writer* w, uint16_t layer, uint16_t expert, uint16_t segment, int rows, int cols,
+                                const uint8_t* int4_data);
+/* sorts the catalog by (layer, expert, segment, page), builds the expert index and writes the file */
+int vib3_writer_finalize(vib3_writer* w);
+void vib3_writer_destroy(vib3_writer* w);
+typedef struct vib3_file vib3_file;
+typedef struct vib3_file_page {
+    uint16_t layer, expert, segment, page_idx;
+    uint16_t row_start, row_count, col_count, compression;
+    uint64_t file_offset;
+    uint32_t raw_size;
+} vib3_file_page;
+/* NULL on failure with *error_out = VIB3_ERR_SHAPE (too small), _UNSUPPORTED (magic / version), _RANGE (a section or
+ * page beyond the end of the file), _STATE (cannot open) */
+vib3_file* vib3_file_open(const char* path, int* error_out);
+void vib3_file_close(vib3_file* f);
+int vib3_file_page_count(const vib3_file* f);
+int vib3_file_summary(const vib3_file* f, uint32_t* num_layers, uint32_t* num_experts, uint32_t* num_active_experts,
+                      uint32_t* hidden_dim, uint32_t* expert_hidden_dim, uint32_t* expert_dtype,
+                      uint64_t* page_data_offset);
+int vib3_file_page_info(const vib3_file* f, int index, vib3_file_page* out);
+int vib3_file_read_page(vib3_file* f, int index, void* dst, size_t dst_bytes);
+/* every page of layers [layer_lo, layer_hi) and experts [expert_lo, expert_hi) (plus the shared expert) into the
+ * pool — PageBufferManager::preload_all (src/storage/buffer_manager.rs:1226-1254); returns the pages loaded */
+long long vib3_file_load_into_pool(vib3_file* f, vib3_pool* pool, int layer_lo, int layer_hi, int expert_lo, int expert_hi);
 
 const char* vib3_b200_version(void);
 

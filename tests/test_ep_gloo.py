@@ -87,3 +87,24 @@ def test_placement():
         assert owners == sorted(owners) and set(owners) == set(range(world))
         assert all(len(local_experts(r, 384, world)) == 384 // world for r in range(world))
     assert local_experts(1, 8, 2) == [4, 5, 6, 7]
+
+
+def test_stack_placement_rules_and_imbalance_bound():
+    """Host logic of the expert-parallel stack: every layer's shared expert has exactly one owner and the owners
+    take turns; expert ranges tile [0, E) without overlap; the Monte-Carlo imbalance bound reproduces the
+    figures the scaling targets were derived from (8 GPUs, uniform routing: about 3.1x at batch 1, 6.6x at batch 32)."""
+    from vic_b200 import ep
+    for world in (1, 2, 4, 8):
+        owners = [ep.shared_expert_owner(l, world) for l in range(61)]
+        assert all(0 <= o < world for o in owners) and len(set(owners)) == world
+        cover = []
+        for r in range(world):
+            lo, hi = ep.expert_range(r, 384, world)
+            assert list(range(lo, hi)) == ep.local_experts(r, 384, world)
+            cover += list(range(lo, hi))
+        assert cover == list(range(384))
+    b1 = ep.imbalance_bound(384, 8, 8, 1, trials=1500)
+    b32 = ep.imbalance_bound(384, 8, 8, 32, trials=300)
+    assert 2.8 < b1["speedup_bound"] < 3.4 and abs(b1["distinct_experts"] - 8) < 1e-9
+    assert 6.2 < b32["speedup_bound"] < 7.0 and 180 < b32["distinct_experts"] < 195
+    assert ep.imbalance_bound(384, 8, 1, 4, trials=10)["speedup_bound"] == 1.0

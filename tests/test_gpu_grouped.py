@@ -91,6 +91,16 @@ def test_grouped_accumulates_and_refuses_bad_arguments(cuda_dev):
     # more tokens than the handle was built for, a null output: refused before any launch
     p = xs.data_ptr()
     st = torch.cuda.current_stream().cuda_stream
-    assert lib().vib3_launch_moe_grouped_int4(gd._h, p, 2, 2 * sh.hidden, 17, p, 32, p, 64, p, None, 1.0, 4, p, sh.hidden, 0, None, st) == -2
-    assert lib().vib3_launch_moe_grouped_int4(gd._h, p, 2, 2 * sh.hidden, 4, p, 32, p, 64, p, None, 1.0, 4, None, sh.hidden, 0, None, st) == -3
-    assert lib().vib3_moe_grouped_workspace_bytes(0, 8, 384, 7168, 2048) == 0
+    E = sh.num_experts
+    assert lib().vib3_launch_moe_grouped_int4(gd._h, p, 2, 2 * sh.hidden, 17, p, 32, p, 64, p, None, 1.0, 4, 0, E, p, sh.hidden, 0, None, st) == -2
+    assert lib().vib3_launch_moe_grouped_int4(gd._h, p, 2, 2 * sh.hidden, 4, p, 32, p, 64, p, None, 1.0, 4, 0, E, None, sh.hidden, 0, None, st) == -3
+    assert lib().vib3_launch_moe_grouped_int4(gd._h, p, 2, 2 * sh.hidden, 4, p, 32, p, 64, p, None, 1.0, 4, 3, E + 1, p, sh.hidden, 0, None, st) == -2
+    # expert ranges: the outputs of disjoint ranges (the shared expert in one of them) add up to the whole
+    whole = gd.forward(0, xs).clone()
+    part = torch.zeros_like(whole)
+    gd.experts(0, xs, out=part, expert_range=(0, 5), shared=True)
+    gd.experts(0, xs, out=part, accumulate=True, expert_range=(5, E), shared=False)
+    torch.cuda.synchronize()
+    assert int(gd.status.item()) == 0
+    assert torch.allclose(part, whole, rtol=0, atol=2e-5)
+    assert lib().vib3_moe_grouped_workspace_bytes(0, 8, 384, 7168, 2048, 520, 1820) == 0

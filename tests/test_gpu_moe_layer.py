@@ -95,6 +95,7 @@ def test_host_to_host_step_equals_device_step(cuda_dev):
     dec = MoeDecoder(model)
     g = torch.Generator(device=cuda_dev).manual_seed(6)
     xs = synth_activation(model.shape, g, cuda_dev, torch.bfloat16, 4)
+    side = torch.cuda.Stream()
     for t in range(4):
         want = dec.forward_layer(0, xs[t]).clone().cpu()
         xh = xs[t].cpu()
@@ -104,6 +105,8 @@ def test_host_to_host_step_equals_device_step(cuda_dev):
         assert got.is_pinned() and torch.equal(got, want)
         got2 = dec.forward_host_call(0, xh)      # the single C call with host pointers
         assert got2.is_pinned() and torch.equal(got2, want)
+        got3 = dec.forward_host_bound(0, xh, side)   # the layer bound once as a graph inside the library
+        assert got3.is_pinned() and torch.equal(got3, want)
     assert int(dec.status.item()) == 0
 
 
@@ -368,3 +371,103 @@ def test_fused_launcher_refusals(cuda_dev):
     assert call(rg=100) == -5            # pages cannot cover the matrix: row range out of [0, M)
     assert call(tab=p + 8) == -4 and call(x=p + 4) == -4
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("name,xdt", [("kimi", torch.bfloat16), ("mid", torch.float32)])
+def test_routing_inside_the_gate_up_kernel_equals_separate_router(cuda_dev, name, xdt):
+    """Library option 2: the gate/up kernel streams the router's rows and selects in its prologue.  Same
+    arithmetic as the router kernel: identical routing and identical layer output."""
+    from vic_b200.lib import lib
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import synth_activation
+    from vic_b200.core_types import SCORING_SIGMOID, MoeShape
+    from vic_b200.synth import build_synthetic_moe
+    if name == "kimi":
+        model = _model("kimi", cuda_dev)
+    else:
+        model = build_synthetic_moe(MoeShape("routed-mid", 1024, 2048, 40, 4, 1, SCORING_SIGMOID, 2.5, True), 1, cuda_dev, seed=5, slot_seed=2)
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(78)
+    xs = synth_activation(model.shape, g, cuda_dev, xdt, 6)
+    try:
+        for t in range(6):
+            lib().vib3_config_set(2, 0)
+            a = dec.forward_layer(0, xs[t]).clone()
+            ids_a, w_a = dec.routing()
+            lib().vib3_config_set(2, 1)
+            b = dec.forward_layer(0, xs[t]).clone()
+            b2 = dec.forward_layer(0, xs[t]).clone()     # back to back: the grid-wide counter was reset
+            torch.cuda.synchronize()
+            ids_b, w_b = dec.routing()
+            assert int(dec.status.item()) == 0
+            assert int(dec.workspace[0].item()) == 0 and int(dec.workspace[2].item()) == 0
+            assert np.array_equal(ids_a, ids_b) and np.array_equal(w_a, w_b)
+            assert torch.equal(a, b) and torch.equal(a, b2)
+    finally:
+        lib().vib3_config_set(2, 0)
+
+
+def test_back_to_back_layers_on_one_scratch_without_a_router(cuda_dev, oracle):
+    """Two launch pairs in a row that share the activation scratch, small hidden size (fewer CTAs than SMs, so
+    the second gate/up kernel finds free SMs while the first down kernel still runs) and a shared expert, whose
+    rows the gate/up kernel writes before its dependency wait: the down kernel lets its successor go only after
+    every consumer warp has read the scratch."""
+    from vic_b200 import kernels
+    from vic_b200.core_types import SCORING_SIGMOID, MoeShape
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import build_synthetic_moe, synth_activation
+    sh = MoeShape("b2b", 512, 1024, 6, 2, 1, SCORING_SIGMOID, 2.0, True)
+    model = build_synthetic_moe(sh, 1, cuda_dev, seed=31, slot_seed=4)
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(9)
+    xs = synth_activation(sh, g, cuda_dev, torch.bfloat16, 8)
+    routes = []
+    for t in range(8):
+        dec.route(0, xs[t])
+        torch.cuda.synchronize()
+        routes.append((dec.ids.clone(), dec.weights.clone()))
+    outs = torch.zeros(8, sh.hidden, dtype=torch.float32, device=cuda_dev)
+    for rep in range(20):
+        for t in range(8):      # no router in between: gate/up follows down directly
+            kernels.moe_layer_int4_paged(xs[t], dec.tables[0], sh.num_experts, dec.shared_tables[0], routes[t][0], routes[t][1],
+                                         sh.top_k, 1.0, dec.act, outs[t], False, sh.hidden, sh.intermediate, sh.pages_per_segment,
+                                         sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status)
+        torch.cuda.synchronize()
+        if rep == 0:
+            first = outs.clone()
+        assert torch.equal(outs, first)
+    assert int(dec.status.item()) == 0
+    x32 = xs.float().cpu().numpy()
+    for t in (0, 7):
+        ids = routes[t][0][:sh.top_k].cpu().numpy().view(np.uint16)
+        ws = routes[t][1][:sh.top_k].cpu().numpy()
+        want = oracle.moe_layer(x32[t], oracle_experts(oracle, model, 0, list(zip(ids.tolist(), ws.tolist()))), sh.hidden,
+                                sh.intermediate, oracle.SCALE_FP16, "gpu")
+        assert_close(first[t].cpu().numpy(), want, f"back-to-back token {t}")
+
+
+def test_activation_outliers_stay_inside_the_tolerance(cuda_dev, oracle):
+    """The staged kernels hold each 32-column chunk of the activation vector as 16-bit fixed point against the
+    chunk's largest magnitude.  Worst case for that: every chunk carries one value 100x larger than the rest, so
+    the small values keep only 9-10 significant bits.  The layer output must still meet the layer tolerance."""
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import synth_activation
+    model = _model("kimi", cuda_dev)
+    sh = model.shape
+    dec = MoeDecoder(model)
+    g = torch.Generator(device=cuda_dev).manual_seed(41)
+    for t in range(2):
+        x = synth_activation(sh, g, cuda_dev, torch.float32, 1)[0]
+        x.view(-1, 32)[:, (3 + 7 * t) % 32] *= 100.0
+        x = x.to(torch.bfloat16)
+        out = dec.forward_layer(0, x).cpu().numpy()
+        torch.cuda.synchronize()
+        ids, w = dec.routing()
+        x32 = x.float().cpu().numpy()
+        oi, ow, _ = oracle.router(x32, model.router_w[0].cpu().numpy(), sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize)
+        assert np.array_equal(ids, oi)
+        want = oracle.moe_layer(x32, oracle_experts(oracle, model, 0, list(zip(oi.tolist(), ow.tolist()))), sh.hidden, sh.intermediate,
+                                oracle.SCALE_FP16, "gpu")
+        # max-abs scales with the output magnitude here (outputs are ~100x larger than for N(0,1) tokens)
+        scale = max(1.0, float(np.abs(want).max()) / 2.5)
+        assert_close(out, want, f"outlier token {t}", max_abs_tol=2e-2 * scale)

@@ -186,3 +186,69 @@ def test_against_reference_cuda_kernels(cuda_dev, K, M):
     torch.cuda.synchronize()
     assert_close(ours.cpu().numpy().astype(np.float32), theirs.cpu().numpy().astype(np.float32), "vs reference kernel f16",
                  rel_l2_tol=4e-4)
+
+
+@pytest.mark.parametrize("H,T", [(7168, 3), (4096, 1), (200, 2)])
+def test_rms_norm_entry_points(cuda_dev, oracle, H, T):
+    """vib3_launch_rms_norm_f32 (reference signature) and the fused residual-add + norm launch against the CPU
+    restatement of rms_norm (sequential sum of squares there, a tree here: a few ulps) and, where it is built,
+    the reference's own kernel."""
+    from vic_b200 import kernels
+    from tests.parity import load_ref_lib
+    g = torch.Generator(device="cpu").manual_seed(H + T)
+    h = torch.randn(T, H, generator=g) * 2.0
+    delta = (torch.randn(T, H, generator=g) * 0.3).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.float16)
+    eps = 1e-6
+    hd, dd, wd = h.to(cuda_dev), delta.to(cuda_dev), w.to(cuda_dev)
+    out = torch.zeros(H, dtype=torch.float32, device=cuda_dev)
+    kernels.rms_norm_f32(hd[0], out, wd, H, eps)
+    want = oracle.rms_norm_f32(h[0].numpy(), w.float().numpy(), eps)
+    assert np.allclose(out.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+    ref = load_ref_lib()
+    if ref is not None and hasattr(ref, "vib3_launch_rms_norm_f32"):
+        import ctypes
+        fn = ref.vib3_launch_rms_norm_f32
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_void_p]
+        theirs = torch.zeros(H, dtype=torch.float32, device=cuda_dev)
+        assert fn(hd[0].data_ptr(), theirs.data_ptr(), wd.data_ptr(), H, eps, torch.cuda.current_stream().cuda_stream) == 0
+        torch.cuda.synchronize()
+        assert np.allclose(out.cpu().numpy(), theirs.cpu().numpy(), rtol=2e-6, atol=1e-7)   # its build uses approximate sqrt / reciprocal
+    # fused: hidden += delta; x = bf16(norm(hidden) * w), all T rows in one launch
+    hid = hd.clone()
+    x = torch.zeros(T, H, dtype=torch.bfloat16, device=cuda_dev)
+    kernels.residual_rms_norm(hid, dd, wd, eps, x)
+    torch.cuda.synchronize()
+    h2 = (h + delta.float())
+    assert torch.equal(hid.cpu(), h2)
+    for t in range(T):
+        want = oracle.rms_norm_f32(h2[t].numpy(), w.float().numpy(), eps)
+        got = x[t].float().cpu().numpy()
+        assert np.allclose(got, torch.from_numpy(want).to(torch.bfloat16).float().numpy(), rtol=1e-2, atol=1e-6)
+        assert np.mean(got == torch.from_numpy(want).to(torch.bfloat16).float().numpy()) > 0.99
+    # no delta, no weight, fp32 out
+    x32 = torch.zeros(T, H, dtype=torch.float32, device=cuda_dev)
+    kernels.residual_rms_norm(hid, None, None, eps, x32)
+    want = oracle.rms_norm_f32(h2[0].numpy(), None, eps)
+    assert np.allclose(x32[0].cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+
+
+def test_rms_norm_centering_and_second_delta(cuda_dev, oracle):
+    from vic_b200 import kernels
+    g = torch.Generator(device="cpu").manual_seed(12)
+    T, H = 4, 1024
+    h = torch.randn(T, H, generator=g) + 3.0
+    d1 = (torch.randn(T, H, generator=g) * 0.2).to(torch.float16)
+    d2 = torch.randn(T, H, generator=g) * 0.1
+    hid = h.to(cuda_dev)
+    x = torch.zeros(T, H, dtype=torch.float32, device=cuda_dev)
+    kernels.residual_rms_norm(hid, d1.to(cuda_dev), None, 1e-6, x, delta2=d2.to(cuda_dev), center=True)
+    torch.cuda.synchronize()
+    h2 = h + d1.float() + d2
+    assert torch.allclose(hid.cpu(), h2, rtol=0, atol=1e-6)
+    for t in range(T):
+        c = (h2[t] - h2[t].mean()).numpy()
+        want = oracle.rms_norm_f32(c, None, 1e-6)
+        assert np.allclose(x[t].cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+        assert abs(float(x[t].mean())) < 1e-5

@@ -19,6 +19,7 @@ SOURCES = [
     "moe_grouped.cu",
     "router.cu",
     "host/page_pool.cpp",
+    "host/vib3_file.cpp",
 ]
 
 NVCC_FLAGS = [

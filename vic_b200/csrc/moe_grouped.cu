@@ -8,7 +8,9 @@
 //   D[128 weight rows x N tokens] += A[128 x 256] . B[N x 256]^T      per 256-column slab of K
 //
 //   A  the INT4 page tile.  cp.async.bulk.tensor (one 3-D tensor map over the whole page pool: byte in
-//      row, row in page, pool slot) brings 128 B of codes and 16 B of scales per row and slab into shared
+//      row, row in page, pool slot) brings 128 B of codes per row and slab — and, once per tile, the rows' group
+//      scales for all of K: the TMA unit pays per row segment, so 16-byte scale segments per slab would cost as
+//      much as the codes — into shared
 //      memory (128-byte swizzle, so that 32 lanes reading 32 rows hit 32 different bank groups); eight
 //      warps turn the codes into fp16 weights (n - 8) * scale in registers and store them with tcgen05.st
 //      into TENSOR MEMORY: the A operand never goes back through shared memory, whose bandwidth could
@@ -41,12 +43,15 @@
 
 namespace vib3 {
 
-constexpr int kGrpThreads = 512;
-constexpr int kGrpStages = 4;
+constexpr int kGrpConvWarps = 16;               // converting warps: TMEM lane quarter = warp & 3, K quarter of the slab = (warp - 6) >> 2
+constexpr int kGrpFirstConvWarp = 6;            // warp 0 TMA, 1 MMA, 2..5 epilogue, 6..21 converting
+constexpr int kGrpThreads = (kGrpFirstConvWarp + kGrpConvWarps) * 32;
+constexpr int kGrpStages = 3;
 constexpr int kGrpSlabK = 256;                  // columns of K per pipeline step
-constexpr int kGrpMaxN = 64;                    // tokens of one expert per pass over its tile
-constexpr int kGrpRawBytes = 18 * 1024;         // codes 16 KB + scales 2 KB per stage
-constexpr int kGrpStageBytes = kGrpRawBytes + kGrpMaxN * kGrpSlabK * 2;   // + the tokens' slab: 50 KB
+constexpr int kGrpMaxN = 32;                    // tokens of one expert per pass over its tile
+constexpr int kGrpRawBytes = 16 * 1024;         // codes of 128 rows x 256 columns per stage
+constexpr int kGrpStageBytes = kGrpRawBytes + kGrpMaxN * kGrpSlabK * 2;   // + the tokens' slab: 32 KB
+constexpr int kGrpMaxScaleRow = 448;            // bytes of group scales per row the scale buffers are sized for (K <= 7168)
 constexpr int kGrpTmemCols = 512;
 constexpr int kGrpACols = kGrpSlabK / 2;        // 128 columns: 256 fp16 per row
 constexpr int kGrpDCol0 = 2 * kGrpACols;        // two A buffers, then two D buffers of kGrpMaxN columns
@@ -65,6 +70,7 @@ struct GroupedWork {
     int pad[2];
 };
 
+struct Unit;
 struct GroupedArgs {
     const PageEntry* page_table;    // [E][3][P]
     const PageEntry* shared_pages;  // [3][P] or null
@@ -75,6 +81,10 @@ struct GroupedArgs {
     const int* offsets;      // [E + 1] first sorted pair of the expert
     __half* act;             // [pairs][I], K order permuted
     __half* y;               // [pairs][H]
+    int sc_inner_gu, sc_inner_dn;   // bytes per row of one scale box (a row's scales are cut into boxes of at most 256 bytes)
+    const Unit* units_gu;    // [n_active * tiles_gu]
+    const Unit* units_dn;    // [n_active * tiles_dn]
+    int tiles_gu, tiles_dn;
     int E, P, H, I;
     int rpp_gu, rpp_dn;
     int* status;
@@ -138,56 +148,73 @@ __device__ __forceinline__ int perm8(int r) {
 }
 
 // One work unit: a 128-row A tile of one expert (gate/up: 64 gate rows and the same 64 up rows; down: 128 rows).
-struct Unit {
-    int expert, n_tok, pair_off;
-    int slot_a, slot_b;      // pool slots of the page(s)
-    int rows_in_page;        // the page's row count (selects the scales map)
-    int row0;                // first row of the tile inside the page
-    int rows;                // valid rows of the tile (gate/up: of each half)
+// The units of a step are listed by build_units_kernel; unit u = (active expert u / tiles, tile u % tiles).
+struct __align__(16) Unit {
+    int slot_a, slot_b;      // pool slots of the page(s); -1: page absent
+    short row0;              // first row of the tile inside the page
+    short rows;              // valid rows of the tile (gate/up: of each half)
+    short scales_last;       // 1: the page is a last (short) page, its scales start earlier
+    short pad;
     int mrow0;               // first row inside the matrix
-    bool present;
+    int n_tok, pair_off;     // the expert's tokens: count and first sorted pair
+    int pad2;
+};
+static_assert(sizeof(Unit) == 32, "a unit is two 16-byte loads");
+
+struct UnitWalk {
+    const Unit* units;
+    int n_units, u;
+    Unit cur, nxt;
+    bool have_next;
+    __device__ __forceinline__ void load(Unit& t, int i) const {
+        const uint4* p = reinterpret_cast<const uint4*>(units + i);
+        const uint4 a = __ldg(p), b = __ldg(p + 1);
+        uint4* q = reinterpret_cast<uint4*>(&t);
+        q[0] = a;
+        q[1] = b;
+    }
+    __device__ __forceinline__ UnitWalk(const Unit* units_, int n_units_) : units(units_), n_units(n_units_), u(blockIdx.x) {
+        have_next = u < n_units;
+        if (have_next) load(nxt, u);
+    }
+    // the next unit with work of this CTA (the one after it is requested at once, so its latency hides under this one)
+    __device__ __forceinline__ bool next(Unit& t) {
+        while (have_next) {
+            cur = nxt;
+            u += gridDim.x;
+            have_next = u < n_units;
+            if (have_next) load(nxt, u);
+            if (cur.rows > 0 && cur.n_tok > 0) {
+                t = cur;
+                return true;
+            }
+        }
+        return false;
+    }
 };
 
 template <bool DOWN>
-__device__ __forceinline__ bool load_unit(const GroupedArgs& a, int u, Unit& t) {
-    const int half_rows = DOWN ? 128 : 64;
-    const int rpp = DOWN ? a.rpp_dn : a.rpp_gu;
-    const int tiles_per_page = (rpp + half_rows - 1) / half_rows;
-    const int m_rows = DOWN ? a.H : a.I;
-    const int tiles = min(a.P, (m_rows + rpp - 1) / rpp) * tiles_per_page;   // pages the matrix really has
-    const int ai = u / tiles, rem = u - ai * tiles;
-    if (ai >= a.work->n_active) return false;
-    const int page = rem / tiles_per_page, tp = rem - page * tiles_per_page;
-    t.expert = a.active[ai];
-    t.n_tok = a.counts[t.expert];
-    t.pair_off = a.offsets[t.expert];
-    const PageEntry* pg = t.expert < a.E ? a.page_table + (size_t)t.expert * 3 * a.P : a.shared_pages;
-    const PageEntry ea = pg[(DOWN ? kSegDown : kSegGate) * a.P + page];
-    const PageEntry eb = DOWN ? ea : pg[kSegUp * a.P + page];
-    t.present = ea.ptr != 0 && eb.ptr != 0;
-    t.rows_in_page = ea.row_count;
-    t.row0 = tp * half_rows;
-    t.rows = max(0, min(half_rows, (int)ea.row_count - t.row0));
-    t.mrow0 = ea.row_start + t.row0;
-    t.slot_a = (int)((ea.ptr - (unsigned long long)a.pool_base) >> 21);
-    t.slot_b = (int)((eb.ptr - (unsigned long long)a.pool_base) >> 21);
-    if (!t.present) t.rows = 0;
-    return true;
-}
+__device__ __forceinline__ int K_of(const GroupedArgs& a) { return DOWN ? a.I : a.H; }
 
 // DOWN = false: act[pair][perm(row)] = f16(silu(f16(Wg x)) * f16(Wu x)); DOWN = true: y[pair][row] = f16(Wd act).
 template <bool DOWN>
 __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __grid_constant__ GroupedMaps maps, GroupedArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-    float* exch = reinterpret_cast<float*>(stages + kGrpStages * kGrpStageBytes);            // [64][kGrpMaxN + 1]
+    unsigned char* scbuf = stages + kGrpStages * kGrpStageBytes;                               // two buffers of 128 rows of scales
+    float* exch = reinterpret_cast<float*>(scbuf + 2 * 128 * kGrpMaxScaleRow);                 // [64][kGrpMaxN + 1]
     uint64_t* full = reinterpret_cast<uint64_t*>(exch + 64 * (kGrpMaxN + 1));
     uint64_t* empty = full + kGrpStages;
     uint64_t* a_full = empty + kGrpStages;
     uint64_t* a_empty = a_full + 2;
     uint64_t* d_full = a_empty + 2;
     uint64_t* d_empty = d_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
+    uint64_t* sc_full = d_empty + 2;
+    uint64_t* sc_empty = sc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_empty + 2);
+    const int scale_row = K_of<DOWN>(a) / 16;                       // bytes of scales per row
+    const int sc_inner = DOWN ? a.sc_inner_dn : a.sc_inner_gu;
+    const int sc_boxes = scale_row / sc_inner;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = DOWN ? a.I : a.H;
@@ -195,13 +222,15 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
     if (tid == 0) {
         for (int s = 0; s < kGrpStages; ++s) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, 9);       // eight converting warps and the MMA's commit
+            mbar_init(empty + s, kGrpConvWarps + 1);       // the converting warps and the MMA's commit
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(a_full + s, 8);
+            mbar_init(a_full + s, kGrpConvWarps);
             mbar_init(a_empty + s, 1);
             mbar_init(d_full + s, 1);
             mbar_init(d_empty + s, 4);
+            mbar_init(sc_full + s, 1);
+            mbar_init(sc_empty + s, kGrpConvWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -214,62 +243,79 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     pdl_wait();   // the work lists, the gathered tokens and (down) the intermediate are earlier kernels' outputs
+    UnitWalk walk(DOWN ? a.units_dn : a.units_gu, a.work->n_active * (DOWN ? a.tiles_dn : a.tiles_gu));
 
     // Every role walks the same sequence: units blockIdx.x, + gridDim.x, ...; per unit ceil(n_tok / 64) passes;
     // per pass nslab slabs.  `it` counts slabs (ring stage it % 4, A buffer it & 1), `pc` passes (D buffer pc & 1).
     bool ok = true;
     if (warp == 0) {
         // ── TMA producer ──
-        int it = 0;
+        int it = 0, uc = 0;
         Unit t;
-        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
-            if (t.rows == 0 || t.n_tok == 0) continue;
+        while (ok && walk.next(t)) {
             const CUtensorMap* codes = DOWN ? &maps.dn_codes : &maps.gu_codes;
-            const int rpp = DOWN ? a.rpp_dn : a.rpp_gu;
-            const CUtensorMap* scales = DOWN ? (t.rows_in_page == rpp ? &maps.dn_scales_full : &maps.dn_scales_last)
-                                             : (t.rows_in_page == rpp ? &maps.gu_scales_full : &maps.gu_scales_last);
+            const CUtensorMap* scales = DOWN ? (t.scales_last ? &maps.dn_scales_last : &maps.dn_scales_full)
+                                             : (t.scales_last ? &maps.gu_scales_last : &maps.gu_scales_full);
+            {
+                // the tile's scales for all of K: buffer uc & 1; lanes 0 .. issue one box each
+                const int sbi = uc & 1;
+                if (uc >= 2) ok = mbar_wait(sc_empty + sbi, ((uc >> 1) - 1) & 1);
+                if (!ok) break;
+                unsigned char* dst = scbuf + (size_t)sbi * 128 * kGrpMaxScaleRow;
+                const int half_rows = DOWN ? 128 : 64;
+                if (lane == 0) mbar_expect_tx(sc_full + sbi, 128 * scale_row);
+                __syncwarp();
+                const int nops = (DOWN ? 1 : 2) * sc_boxes;
+                for (int o = lane; o < nops; o += 32) {
+                    const int mat = o / sc_boxes, j = o - mat * sc_boxes;
+                    tma_load_3d(dst + (size_t)mat * half_rows * scale_row + (size_t)j * half_rows * sc_inner, scales, j * sc_inner, t.row0,
+                                mat ? t.slot_b : t.slot_a, sc_full + sbi);
+                }
+                __syncwarp();
+                ++uc;
+            }
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN) {
                 const int ntok = min(kGrpMaxN, t.n_tok - p0);
                 const bool small = ntok <= 16;
                 const CUtensorMap* xmap = DOWN ? (small ? &maps.act16 : &maps.act64) : (small ? &maps.xg16 : &maps.xg64);
-                const int nb = small ? 16 : 64;
+                const int nb = small ? 16 : kGrpMaxN;
                 for (int s = 0; s < nslab; ++s, ++it) {
                     const int st = it % kGrpStages;
                     if (it >= kGrpStages) ok = mbar_wait(empty + st, ((it / kGrpStages) - 1) & 1);
                     if (!ok) break;
-                    if (lane == 0) {
-                        unsigned char* sb = stages + (size_t)st * kGrpStageBytes;
-                        mbar_expect_tx(full + st, kGrpRawBytes + nb * kGrpSlabK * 2);
-                        if (DOWN) {
-                            tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
-                            tma_load_3d(sb + 16384, scales, s * 16, t.row0, t.slot_a, full + st);
-                        } else {
-                            tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
-                            tma_load_3d(sb + 8192, codes, s * 128, t.row0, t.slot_b, full + st);
-                            tma_load_3d(sb + 16384, scales, s * 16, t.row0, t.slot_a, full + st);
-                            tma_load_3d(sb + 17408, scales, s * 16, t.row0, t.slot_b, full + st);
-                        }
-                        for (int j = 0; j < 4; ++j)
-                            tma_load_2d(sb + kGrpRawBytes + j * nb * 128, xmap, s * kGrpSlabK + 64 * j, t.pair_off + p0, full + st);
+                    // one lane arms the barrier, then eight lanes issue one copy each (a copy costs its issuing
+                    // thread a few hundred cycles: one lane alone would bound the ring)
+                    unsigned char* sb = stages + (size_t)st * kGrpStageBytes;
+                    if (lane == 0) mbar_expect_tx(full + st, kGrpRawBytes + nb * kGrpSlabK * 2);
+                    __syncwarp();
+                    if (DOWN) {
+                        if (lane == 0) tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
+                    } else {
+                        if (lane == 0) tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
+                        if (lane == 1) tma_load_3d(sb + 8192, codes, s * 128, t.row0, t.slot_b, full + st);
                     }
+                    if (lane >= 4 && lane < 8)
+                        tma_load_2d(sb + kGrpRawBytes + (lane - 4) * nb * 128, xmap, s * kGrpSlabK + 64 * (lane - 4), t.pair_off + p0, full + st);
                     __syncwarp();
                 }
             }
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
-        // drain: every issued stage must have landed before the CTA's shared memory goes away
-        if (lane == 0)
+        // drain: every issued copy must have landed before the CTA's shared memory goes away
+        if (lane == 0) {
             for (int k = max(0, it - kGrpStages); k < it; ++k)
                 if (!mbar_wait(full + (k % kGrpStages), (k / kGrpStages) & 1)) flag(a.status, kStatusTimeout);
+            for (int k = max(0, uc - 2); k < uc; ++k)
+                if (!mbar_wait(sc_full + (k & 1), (k >> 1) & 1)) flag(a.status, kStatusTimeout);
+        }
     } else if (warp == 1) {
         // ── MMA issuer ──
         int it = 0, pc = 0;
         Unit t;
-        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
-            if (t.rows == 0 || t.n_tok == 0) continue;
+        while (ok && walk.next(t)) {
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
                 const int ntok = min(kGrpMaxN, t.n_tok - p0);
-                const int nb = ntok <= 16 ? 16 : 64;
+                const int nb = ntok <= 16 ? 16 : kGrpMaxN;
                 const int n_mma = (ntok + 15) & ~15;
                 const uint32_t idesc = (1u << 4) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
                 const int db = pc & 1;
@@ -300,40 +346,50 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             }
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
-    } else if (warp >= 8) {
-        // ── converting warps: row m = 32 (warp % 4) + lane of the A tile, K half (warp - 8) / 4 of the slab ──
-        const int q = warp & 3, kh = (warp - 8) >> 2;
+    } else if (warp >= kGrpFirstConvWarp) {
+        // ── converting warps: row m = 32 (warp % 4) + lane of the A tile, K quarter (warp - 6) / 4 of the slab ──
+        const int q = warp & 3, kq = (warp - kGrpFirstConvWarp) >> 2;
         const int m = 32 * q + lane;
         // where row m's codes and scales sit in a stage
         const int src_row = DOWN ? m : (m & 63);
         const uint32_t code_off = (DOWN ? 0u : (m >= 64 ? 8192u : 0u)) + (uint32_t)src_row * 128u;
-        const uint32_t scale_off = 16384u + (DOWN ? 0u : (m >= 64 ? 1024u : 0u)) + (uint32_t)src_row * 16u + (uint32_t)kh * 8u;
+        const int half_rows = DOWN ? 128 : 64;
+        // row m's scales in a scale buffer: matrix block, then box j of sc_inner bytes per row
+        const uint32_t sc_row_off = (DOWN ? 0u : (m >= 64 ? (uint32_t)(64 * scale_row) : 0u)) + (uint32_t)src_row * (uint32_t)sc_inner;
+        const int first_row = DOWN ? 32 * q : 32 * (q & 1);   // first row (of the matrix half) among this warp's 32
         const uint32_t sw = (uint32_t)(src_row & 7);
-        int it = 0;
+        int it = 0, uc = 0;
         Unit t;
-        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
-            if (t.rows == 0 || t.n_tok == 0) continue;
+        while (ok && walk.next(t)) {
             const int total = ((t.n_tok + kGrpMaxN - 1) / kGrpMaxN) * nslab;
-            for (int i = 0; i < total; ++i, ++it) {
+            const int sbi = uc & 1;
+            ok = mbar_wait(sc_full + sbi, (uc >> 1) & 1);
+            const uint32_t sc_base = smem_u32(scbuf + (size_t)sbi * 128 * kGrpMaxScaleRow) + sc_row_off;
+            for (int i = 0; ok && i < total; ++i, ++it) {
+                const int s = i % nslab;
                 const int st = it % kGrpStages, ab = it & 1;
                 ok = mbar_wait(full + st, (it / kGrpStages) & 1);
                 if (ok && it >= 2) ok = mbar_wait(a_empty + ab, ((it >> 1) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sb = smem_u32(stages + (size_t)st * kGrpStageBytes);
-                const uint2 sc = lds64(sb + scale_off);   // four group scales
-                const uint32_t sc2[4] = {__byte_perm(sc.x, 0, 0x1010), __byte_perm(sc.x, 0, 0x3232), __byte_perm(sc.y, 0, 0x1010),
-                                         __byte_perm(sc.y, 0, 0x3232)};
-                const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + ab * kGrpACols + kh * 64;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t chunk = (uint32_t)(4 * kh + c) ^ sw;
-                    const uint4 codes = lds128(sb + code_off + chunk * 16u);
+                // a warp whose 32 rows all lie beyond the tile's last row has nothing to convert: its lanes of the
+                // accumulator are never read
+                if (first_row < t.rows) {
+                    const uint32_t sb = smem_u32(stages + (size_t)st * kGrpStageBytes);
+                    uint32_t sc;   // two group scales: bytes 16 s + 4 kq of the row's scales
+                    const int sbyte = 16 * s + 4 * kq, sj = sbyte / sc_inner;
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc) : "r"(sc_base + (uint32_t)(sj * half_rows * sc_inner + (sbyte - sj * sc_inner))));
+                    const uint32_t sc2[2] = {__byte_perm(sc, 0, 0x1010), __byte_perm(sc, 0, 0x3232)};
+                    const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + ab * kGrpACols + kq * 32;
+                    const uint4 codes0 = lds128(sb + code_off + (((uint32_t)(2 * kq) ^ sw) * 16u));
+                    const uint4 codes1 = lds128(sb + code_off + (((uint32_t)(2 * kq + 1) ^ sw) * 16u));
                     uint32_t h[16];
-                    dequant_chunk(codes, sc2[c], h);
-                    tmem_st16(taddr + 16 * c, h);
+                    dequant_chunk(codes0, sc2[0], h);
+                    tmem_st16(taddr, h);
+                    dequant_chunk(codes1, sc2[1], h);
+                    tmem_st16(taddr + 16, h);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
@@ -341,16 +397,18 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
                     mbar_arrive(a_full + ab);
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sc_empty + sbi);
+            ++uc;
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
-    } else if (warp >= 4) {
+    } else if (warp >= 2) {
         // ── epilogue warps: TMEM lanes 32 (warp % 4) .. + 31 ──
         const int q = warp & 3;
         const int m = 32 * q + lane;
         int pc = 0;
         Unit t;
-        for (int u = blockIdx.x; ok && load_unit<DOWN>(a, u, t); u += gridDim.x) {
-            if (t.rows == 0 || t.n_tok == 0) continue;
+        while (ok && walk.next(t)) {
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
                 const int ntok = min(kGrpMaxN, t.n_tok - p0);
                 const int db = pc & 1;
@@ -415,6 +473,7 @@ struct GroupPairsArgs {
     const unsigned short* ids;   // [T] rows of top_k, stride in bytes
     int ids_stride;
     int T, top_k, E, has_shared;
+    int expert_lo, expert_hi;    // only pairs whose expert lies in [lo, hi) are taken (an expert-parallel rank's share)
     GroupedWork* work;
     int* active;
     int* counts;     // [E + 1]
@@ -438,8 +497,9 @@ __global__ void __launch_bounds__(1024) group_pairs_kernel(GroupPairsArgs g) {
     for (int i = tid; i < total; i += blockDim.x) {
         const int t = i / g.top_k, s = i - t * g.top_k;
         const unsigned e = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(g.ids) + (size_t)t * g.ids_stride)[s];
-        if (e < (unsigned)g.E) atomicAdd(&cnt[e], 1);
-        else flag(g.status, kStatusBadExpert);
+        if (e >= (unsigned)g.E) flag(g.status, kStatusBadExpert);
+        else if ((int)e >= g.expert_lo && (int)e < g.expert_hi) atomicAdd(&cnt[e], 1);
+        g.pos[t * (g.top_k + 1) + s] = -1;   // (overwritten below for the pairs that are taken)
     }
     if (tid == 0) cnt[g.E] = g.has_shared ? g.T : 0;
     __syncthreads();
@@ -483,8 +543,59 @@ __global__ void __launch_bounds__(1024) group_pairs_kernel(GroupPairsArgs g) {
             g.pair_token[off[g.E] + t] = (unsigned short)t;
             g.pos[t * (g.top_k + 1) + g.top_k] = off[g.E] + t;
         }
+    else
+        for (int t = tid; t < g.T; t += blockDim.x) g.pos[t * (g.top_k + 1) + g.top_k] = -1;
     __syncthreads();
     if (tid == 0) g.work->n_active = nact;
+    pdl_trigger();
+}
+
+// The unit tables of the step: one thread per (active expert, tile).
+struct BuildUnitsArgs {
+    const PageEntry* page_table;
+    const PageEntry* shared_pages;
+    const unsigned char* pool_base;
+    const GroupedWork* work;
+    const int* active;
+    const int* counts;
+    const int* offsets;
+    Unit* units_gu;
+    Unit* units_dn;
+    int tiles_gu, tiles_dn, tiles_per_page_gu, tiles_per_page_dn;
+    int E, P, rpp_gu, rpp_dn;
+    int* status;
+};
+
+__global__ void __launch_bounds__(256) build_units_kernel(BuildUnitsArgs b) {
+    pdl_wait();
+    const int per = b.tiles_gu + b.tiles_dn;
+    const int total = b.work->n_active * per;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int ai = i / per, r = i - ai * per;
+        const bool down = r >= b.tiles_gu;
+        const int tile = down ? r - b.tiles_gu : r;
+        const int tpp = down ? b.tiles_per_page_dn : b.tiles_per_page_gu;
+        const int half_rows = down ? 128 : 64;
+        const int page = tile / tpp, tp = tile - page * tpp;
+        const int e = b.active[ai];
+        const PageEntry* pg = e < b.E ? b.page_table + (size_t)e * 3 * b.P : b.shared_pages;
+        const PageEntry ea = pg[(down ? kSegDown : kSegGate) * b.P + page];
+        const PageEntry eb = down ? ea : pg[kSegUp * b.P + page];
+        Unit u;
+        const bool present = ea.ptr != 0 && eb.ptr != 0;
+        if (!present) flag(b.status, kStatusMissingPage);
+        u.slot_a = present ? (int)((ea.ptr - (unsigned long long)b.pool_base) >> 21) : -1;
+        u.slot_b = present ? (int)((eb.ptr - (unsigned long long)b.pool_base) >> 21) : -1;
+        u.row0 = (short)(tp * half_rows);
+        u.rows = (short)(present ? max(0, min(half_rows, (int)ea.row_count - tp * half_rows)) : 0);
+        u.scales_last = (short)(ea.row_count != (down ? b.rpp_dn : b.rpp_gu));
+        u.pad = 0;
+        u.mrow0 = ea.row_start + tp * half_rows;
+        u.n_tok = b.counts[e];
+        u.pair_off = b.offsets[e];
+        u.pad2 = 0;
+        (down ? b.units_dn : b.units_gu)[ai * (down ? b.tiles_dn : b.tiles_gu) + tile] = u;
+    }
     pdl_trigger();
 }
 
@@ -525,7 +636,9 @@ __global__ void __launch_bounds__(256) combine_pairs_kernel(const __half* y, con
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) * 2; r < H; r += gridDim.x * blockDim.x * 2) {
         float o0 = 0.f, o1 = 0.f;
         for (int s = 0; s < top_k; ++s) {
-            const __half2 v = *reinterpret_cast<const __half2*>(y + (size_t)pos[t * (top_k + 1) + s] * H + r);
+            const int p = pos[t * (top_k + 1) + s];
+            if (p < 0) continue;   // a pair of another rank's expert
+            const __half2 v = *reinterpret_cast<const __half2*>(y + (size_t)p * H + r);
             o0 = fmaf(wrow[s], __low2float(v), o0);
             o1 = fmaf(wrow[s], __high2float(v), o1);
         }
@@ -564,6 +677,9 @@ struct GroupedHandle {
     int *active, *counts, *offsets, *pos;
     unsigned short* pair_token;
     __half *xg, *act, *y;
+    Unit *units_gu, *units_dn;
+    int tiles_gu, tiles_dn, tiles_per_page_gu, tiles_per_page_dn;
+    int sc_inner_gu, sc_inner_dn;
     int max_pairs;
 };
 
@@ -606,13 +722,30 @@ int make_rows_map(CUtensorMap* m, void* base, int cols, int rows, int box_rows) 
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// A row's scales (row_bytes) are fetched as equal boxes of at most 256 bytes, each a multiple of 16 bytes; 0: impossible.
+int scale_box_bytes(int row_bytes) {
+    for (int n = (row_bytes + 255) / 256; n <= row_bytes / 16; ++n)
+        if (row_bytes % n == 0 && (row_bytes / n) % 16 == 0) return row_bytes / n;
+    return 0;
+}
+
 struct Carve {
-    size_t work, active, counts, offsets, pos, pair_token, xg, act, y, total;
+    size_t work, active, counts, offsets, pos, pair_token, units_gu, units_dn, xg, act, y, total;
+    int tiles_gu, tiles_dn, tpp_gu, tpp_dn;
 };
 
-Carve carve(int max_tokens, int top_k, int E, int H, int I) {
+// tiles of a matrix of `rows` rows cut into pages of `rpp` rows, in tiles of `tile_rows`
+int tiles_of(int rows, int rpp, int tile_rows, int* per_page) {
+    *per_page = (rpp + tile_rows - 1) / tile_rows;
+    return ((rows + rpp - 1) / rpp) * *per_page;
+}
+
+Carve carve(int max_tokens, int top_k, int E, int H, int I, int rpp_gu, int rpp_dn) {
     Carve c;
     const size_t pairs = (size_t)max_tokens * (top_k + 1);
+    c.tiles_gu = tiles_of(I, rpp_gu, 64, &c.tpp_gu);
+    c.tiles_dn = tiles_of(H, rpp_dn, 128, &c.tpp_dn);
+    const size_t max_active = (size_t)(max_tokens * top_k < E ? max_tokens * top_k : E) + 1;
     size_t o = 0;
     c.work = o; o = align_up(o + sizeof(GroupedWork), 256);
     c.active = o; o = align_up(o + (E + 1) * sizeof(int), 256);
@@ -620,6 +753,8 @@ Carve carve(int max_tokens, int top_k, int E, int H, int I) {
     c.offsets = o; o = align_up(o + (E + 2) * sizeof(int), 256);
     c.pos = o; o = align_up(o + pairs * sizeof(int), 256);
     c.pair_token = o; o = align_up(o + pairs * sizeof(unsigned short), 256);
+    c.units_gu = o; o = align_up(o + max_active * c.tiles_gu * sizeof(Unit), 256);
+    c.units_dn = o; o = align_up(o + max_active * c.tiles_dn * sizeof(Unit), 256);
     c.xg = o; o = align_up(o + pairs * (size_t)H * 2, 1024);
     c.act = o; o = align_up(o + pairs * (size_t)I * 2, 1024);
     c.y = o; o = align_up(o + pairs * (size_t)H * 2, 1024);
@@ -642,13 +777,17 @@ int launch_pdl(K kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, A
     return (int)cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-constexpr size_t kGrpSmem = 1024 + (size_t)kGrpStages * kGrpStageBytes + 64 * (kGrpMaxN + 1) * sizeof(float) + 32 * sizeof(uint64_t);
+constexpr size_t kGrpSmem = 1024 + (size_t)kGrpStages * kGrpStageBytes + 2 * 128 * kGrpMaxScaleRow + 64 * (kGrpMaxN + 1) * sizeof(float) +
+                            40 * sizeof(uint64_t);
 
 }  // namespace
 
-extern "C" size_t vib3_moe_grouped_workspace_bytes(int max_tokens, int top_k, int num_experts, int hidden_dim, int expert_hidden_dim) {
-    if (max_tokens <= 0 || top_k <= 0 || num_experts <= 0 || hidden_dim <= 0 || expert_hidden_dim <= 0) return 0;
-    return carve(max_tokens, top_k, num_experts, hidden_dim, expert_hidden_dim).total;
+extern "C" size_t vib3_moe_grouped_workspace_bytes(int max_tokens, int top_k, int num_experts, int hidden_dim, int expert_hidden_dim,
+                                                   int rows_per_page_gate_up, int rows_per_page_down) {
+    if (max_tokens <= 0 || top_k <= 0 || num_experts <= 0 || hidden_dim <= 0 || expert_hidden_dim <= 0 || rows_per_page_gate_up <= 0 ||
+        rows_per_page_down <= 0)
+        return 0;
+    return carve(max_tokens, top_k, num_experts, hidden_dim, expert_hidden_dim, rows_per_page_gate_up, rows_per_page_down).total;
 }
 
 extern "C" int vib3_moe_grouped_prewarm(void* pool_base, size_t capacity_pages, int num_experts, int top_k, int hidden_dim,
@@ -660,7 +799,8 @@ extern "C" int vib3_moe_grouped_prewarm(void* pool_base, size_t capacity_pages, 
     if (max_tokens <= 0 || max_tokens > kGrpMaxTokens) return VIB3_ERR_COUNT;
     if (hidden_dim % kGrpSlabK || expert_hidden_dim % kGrpSlabK) return VIB3_ERR_UNSUPPORTED;
     if (((uintptr_t)pool_base & 15) || ((uintptr_t)workspace & 1023)) return VIB3_ERR_ALIGN;
-    const Carve c = carve(max_tokens, top_k, num_experts, hidden_dim, expert_hidden_dim);
+    if (rows_per_page_gate_up <= 0 || rows_per_page_down <= 0 || rows_per_page_gate_up > 32767 || rows_per_page_down > 32767) return VIB3_ERR_SHAPE;
+    const Carve c = carve(max_tokens, top_k, num_experts, hidden_dim, expert_hidden_dim, rows_per_page_gate_up, rows_per_page_down);
     if (workspace_bytes < c.total) return VIB3_ERR_CAPACITY;
     if (!encode_fn()) return VIB3_ERR_UNSUPPORTED;
     GroupedHandle* h = new (std::nothrow) GroupedHandle();
@@ -679,24 +819,33 @@ extern "C" int vib3_moe_grouped_prewarm(void* pool_base, size_t capacity_pages, 
     h->xg = reinterpret_cast<__half*>(ws + c.xg);
     h->act = reinterpret_cast<__half*>(ws + c.act);
     h->y = reinterpret_cast<__half*>(ws + c.y);
+    h->units_gu = reinterpret_cast<Unit*>(ws + c.units_gu);
+    h->units_dn = reinterpret_cast<Unit*>(ws + c.units_dn);
+    h->tiles_gu = c.tiles_gu; h->tiles_dn = c.tiles_dn; h->tiles_per_page_gu = c.tpp_gu; h->tiles_per_page_dn = c.tpp_dn;
     h->max_pairs = max_tokens * (top_k + 1);
     const size_t gu_code_row = hidden_dim / 2, gu_scale_row = hidden_dim / 16;
     const size_t dn_code_row = expert_hidden_dim / 2, dn_scale_row = expert_hidden_dim / 16;
     int e = 0;
     e |= make_pool_map(&h->maps.gu_codes, pb, gu_code_row, rows_per_page_gate_up, capacity_pages, 128, 64, true);
+    h->sc_inner_gu = scale_box_bytes((int)gu_scale_row);
+    h->sc_inner_dn = scale_box_bytes((int)dn_scale_row);
+    if (!h->sc_inner_gu || !h->sc_inner_dn || gu_scale_row > (size_t)kGrpMaxScaleRow || dn_scale_row > (size_t)kGrpMaxScaleRow) {
+        delete h;
+        return VIB3_ERR_UNSUPPORTED;
+    }
     e |= make_pool_map(&h->maps.gu_scales_full, pb + (size_t)rows_per_page_gate_up * gu_code_row, gu_scale_row, rows_per_page_gate_up,
-                       capacity_pages, 16, 64, false);
+                       capacity_pages, h->sc_inner_gu, 64, false);
     e |= make_pool_map(&h->maps.gu_scales_last, pb + (size_t)last_page_rows_gate_up * gu_code_row, gu_scale_row, last_page_rows_gate_up,
-                       capacity_pages, 16, 64, false);
+                       capacity_pages, h->sc_inner_gu, 64, false);
     e |= make_pool_map(&h->maps.dn_codes, pb, dn_code_row, rows_per_page_down, capacity_pages, 128, 128, true);
     e |= make_pool_map(&h->maps.dn_scales_full, pb + (size_t)rows_per_page_down * dn_code_row, dn_scale_row, rows_per_page_down,
-                       capacity_pages, 16, 128, false);
+                       capacity_pages, h->sc_inner_dn, 128, false);
     e |= make_pool_map(&h->maps.dn_scales_last, pb + (size_t)last_page_rows_down * dn_code_row, dn_scale_row, last_page_rows_down,
-                       capacity_pages, 16, 128, false);
+                       capacity_pages, h->sc_inner_dn, 128, false);
     e |= make_rows_map(&h->maps.xg16, h->xg, hidden_dim, h->max_pairs, 16);
-    e |= make_rows_map(&h->maps.xg64, h->xg, hidden_dim, h->max_pairs, 64);
+    e |= make_rows_map(&h->maps.xg64, h->xg, hidden_dim, h->max_pairs, kGrpMaxN);
     e |= make_rows_map(&h->maps.act16, h->act, expert_hidden_dim, h->max_pairs, 16);
-    e |= make_rows_map(&h->maps.act64, h->act, expert_hidden_dim, h->max_pairs, 64);
+    e |= make_rows_map(&h->maps.act64, h->act, expert_hidden_dim, h->max_pairs, kGrpMaxN);
     if (e) {
         delete h;
         return VIB3_ERR_STATE;
@@ -716,13 +865,15 @@ extern "C" void vib3_moe_grouped_destroy(void* handle) { delete static_cast<Grou
 extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_dtype, int x_stride_bytes, int n_tokens,
                                             const unsigned short* ids, int ids_stride_bytes, const float* weights,
                                             int weights_stride_bytes, const void* page_table, const void* shared_pages,
-                                            float shared_weight, int pages_per_segment, float* out, int out_stride,
-                                            int out_accumulate, int* status, void* stream) {
+                                            float shared_weight, int pages_per_segment, int expert_lo, int expert_hi, float* out,
+                                            int out_stride, int out_accumulate, int* status, void* stream) {
     GroupedHandle* h = static_cast<GroupedHandle*>(handle);
     if (!h || !x || !ids || !weights || !page_table || !out) return VIB3_ERR_NULL;
     if (n_tokens <= 0 || n_tokens > h->max_tokens) return VIB3_ERR_COUNT;
+    if (expert_lo < 0 || expert_hi < expert_lo || expert_hi > h->E) return VIB3_ERR_COUNT;
     if (x_dtype < X_F32 || x_dtype > X_BF16) return VIB3_ERR_UNSUPPORTED;
     if (pages_per_segment <= 0 || pages_per_segment > kMaxPages) return VIB3_ERR_COUNT;
+    if (pages_per_segment * h->tiles_per_page_gu < h->tiles_gu || pages_per_segment * h->tiles_per_page_dn < h->tiles_dn) return VIB3_ERR_SHAPE;
     if (((uintptr_t)x & 15) || (x_stride_bytes & 15) || (ids_stride_bytes & 1) || (weights_stride_bytes & 3) || ((uintptr_t)out & 7) ||
         (out_stride & 1) || out_stride < h->H)
         return VIB3_ERR_ALIGN;
@@ -731,6 +882,7 @@ extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_d
 
     GroupPairsArgs g;
     g.ids = ids; g.ids_stride = ids_stride_bytes; g.T = n_tokens; g.top_k = h->top_k; g.E = h->E; g.has_shared = has_shared;
+    g.expert_lo = expert_lo; g.expert_hi = expert_hi;
     g.work = h->work; g.active = h->active; g.counts = h->counts; g.offsets = h->offsets; g.pos = h->pos;
     g.pair_token = h->pair_token; g.status = status;
     int err = launch_pdl(group_pairs_kernel, dim3(1), 1024, 0, st, g);
@@ -739,7 +891,18 @@ extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_d
                      (const GroupedWork*)h->work, (const unsigned short*)h->pair_token, h->xg, h->H);
     if (err) return err;
 
+    BuildUnitsArgs bu;
+    bu.page_table = (const PageEntry*)page_table; bu.shared_pages = (const PageEntry*)shared_pages; bu.pool_base = h->pool_base;
+    bu.work = h->work; bu.active = h->active; bu.counts = h->counts; bu.offsets = h->offsets; bu.units_gu = h->units_gu;
+    bu.units_dn = h->units_dn; bu.tiles_gu = h->tiles_gu; bu.tiles_dn = h->tiles_dn; bu.tiles_per_page_gu = h->tiles_per_page_gu;
+    bu.tiles_per_page_dn = h->tiles_per_page_dn; bu.E = h->E; bu.P = pages_per_segment; bu.rpp_gu = h->rpp_gu; bu.rpp_dn = h->rpp_dn;
+    bu.status = status;
+    err = launch_pdl(build_units_kernel, dim3(64), 256, 0, st, bu);
+    if (err) return err;
+
     GroupedArgs a;
+    a.units_gu = h->units_gu; a.units_dn = h->units_dn; a.tiles_gu = h->tiles_gu; a.tiles_dn = h->tiles_dn;
+    a.sc_inner_gu = h->sc_inner_gu; a.sc_inner_dn = h->sc_inner_dn;
     a.page_table = (const PageEntry*)page_table; a.shared_pages = (const PageEntry*)shared_pages; a.pool_base = h->pool_base;
     a.work = h->work; a.active = h->active; a.counts = h->counts; a.offsets = h->offsets; a.act = h->act; a.y = h->y;
     a.E = h->E; a.P = pages_per_segment; a.H = h->H; a.I = h->I; a.rpp_gu = h->rpp_gu; a.rpp_dn = h->rpp_dn; a.status = status;

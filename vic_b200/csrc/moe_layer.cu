@@ -16,6 +16,9 @@
 #include "moe_common.cuh"
 #include "router_core.cuh"
 
+#include <cstring>
+#include <new>
+
 namespace vib3 {
 
 // ── gate/up + SiLU ─────────────────────────────────────────────────────────────────────────
@@ -408,6 +411,88 @@ extern "C" int vib3_moe_layer_step_host(const void* x_host, int x_dtype, void* x
         if (ce != cudaSuccess) return (int)ce;
     }
     ce = cudaStreamSynchronize(st);
+    return ce == cudaSuccess ? 0 : (int)ce;
+}
+
+// ── One token from and to host memory as ONE graph launch ──────────────────────────────────────
+// vib3_moe_layer_step_host costs the host a copy, three launches and a synchronisation per token.  A caller
+// that decodes many tokens through the same layer binds the layer once: vib3_moe_step_create records the copy of
+// the token from a pinned staging buffer, the router and the two expert kernels (the last one storing the fp32
+// output straight into the caller's pinned buffer) into a CUDA graph, after one eager run that also takes care
+// of one-time kernel attributes; vib3_moe_step_run then copies the token into the staging buffer (host to host),
+// launches the graph and waits for the stream.  Create allocates (pinned staging memory, the graph): call it at
+// start-up and outside any stream capture, like vib3_moe_prewarm_gpu_bufs (cuda/src/kernels.cu:6507).
+namespace {
+struct StepHandle {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    void* x_pin = nullptr;
+    size_t xbytes = 0;
+};
+}  // namespace
+
+extern "C" void vib3_moe_step_destroy(void* handle) {
+    StepHandle* h = static_cast<StepHandle*>(handle);
+    if (!h) return;
+    if (h->exec) cudaGraphExecDestroy(h->exec);
+    if (h->graph) cudaGraphDestroy(h->graph);
+    if (h->x_pin) cudaFreeHost(h->x_pin);
+    delete h;
+}
+
+extern "C" int vib3_moe_step_create(int x_dtype, void* x_dev, const void* router_w, int w_dtype, float* scores_buf, const float* bias,
+                                    unsigned short* ids_dev, float* weights_dev, int num_experts, int top_k, int scoring_mode,
+                                    float scaling_factor, int normalize, int exact_order, unsigned int* workspace,
+                                    const void* page_table, const void* shared_pages, float shared_weight, void* act_scratch,
+                                    float* out_host_pinned, int hidden_dim, int expert_hidden_dim, int pages_per_segment,
+                                    int rows_per_page_gate_up, int rows_per_page_down, int group_size, int* status, void* stream,
+                                    void** handle_out) {
+    if (!x_dev || !out_host_pinned || !handle_out) return VIB3_ERR_NULL;
+    if (x_dtype < X_F32 || x_dtype > X_BF16 || hidden_dim <= 0) return VIB3_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!st) return VIB3_ERR_UNSUPPORTED;   // the legacy default stream cannot be captured
+    StepHandle* h = new (std::nothrow) StepHandle();
+    if (!h) return VIB3_ERR_STATE;
+    h->xbytes = (size_t)hidden_dim * (x_dtype == X_F32 ? 4 : 2);
+    cudaError_t ce = cudaHostAlloc(&h->x_pin, h->xbytes, cudaHostAllocDefault);
+    if (ce != cudaSuccess) {
+        delete h;
+        return (int)ce;
+    }
+    memset(h->x_pin, 0, h->xbytes);
+    auto body = [&]() -> int {
+        cudaError_t e = cudaMemcpyAsync(x_dev, h->x_pin, h->xbytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return (int)e;
+        return vib3_launch_moe_layer_routed_int4_paged(x_dev, x_dtype, router_w, w_dtype, scores_buf, bias, nullptr, ids_dev, weights_dev,
+                                                       num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order, workspace,
+                                                       page_table, shared_pages, shared_weight, act_scratch, out_host_pinned, 0,
+                                                       hidden_dim, expert_hidden_dim, pages_per_segment, rows_per_page_gate_up,
+                                                       rows_per_page_down, group_size, status, stream);
+    };
+    int err = body();   // eager: validates the arguments, sets one-time kernel attributes
+    if (!err && (ce = cudaStreamSynchronize(st)) != cudaSuccess) err = (int)ce;
+    if (!err && (ce = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal)) != cudaSuccess) err = (int)ce;
+    if (!err) {
+        err = body();
+        ce = cudaStreamEndCapture(st, &h->graph);
+        if (!err && ce != cudaSuccess) err = (int)ce;
+    }
+    if (!err && (ce = cudaGraphInstantiate(&h->exec, h->graph, 0)) != cudaSuccess) err = (int)ce;
+    if (err) {
+        vib3_moe_step_destroy(h);
+        return err;
+    }
+    *handle_out = h;
+    return VIB3_OK;
+}
+
+extern "C" int vib3_moe_step_run(void* handle, const void* x_host, void* stream) {
+    StepHandle* h = static_cast<StepHandle*>(handle);
+    if (!h || !x_host) return VIB3_ERR_NULL;
+    memcpy(h->x_pin, x_host, h->xbytes);
+    cudaError_t ce = cudaGraphLaunch(h->exec, (cudaStream_t)stream);
+    if (ce != cudaSuccess) return (int)ce;
+    ce = cudaStreamSynchronize((cudaStream_t)stream);
     return ce == cudaSuccess ? 0 : (int)ce;
 }
 

@@ -254,3 +254,185 @@ extern "C" int vib3_launch_residual_add_f32_f32(void* acc_f32, const void* layer
     residual_add_kernel<<<(dim + 255) / 256, 256, 0, (cudaStream_t)stream>>>((float*)acc_f32, (const float*)layer_out_f32, dim);
     return (int)cudaGetLastError();
 }
+
+// ── RMS norm in front of the MoE sublayer ──────────────────────────────────────────────────
+// Sum of squares: 256 partial sums (fused multiply-add), then a halving tree in shared memory, as the reference
+// kernel (cuda/src/kernels.cu:921-953); square root and reciprocal are IEEE (the reference's CPU path,
+// src/compute/kernels.rs:2591-2603; its CUDA build uses the fast-math approximations).
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    const int tid = threadIdx.x;
+    __syncthreads();   // (red may still be read from an earlier call)
+    red[tid] = v;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (tid < s) red[tid] += red[tid + s];
+        __syncthreads();
+    }
+    return red[0];
+}
+__device__ __forceinline__ float block_inv_rms_256(float ss, int H, float eps, float* red) {
+    const float rms = sqrtf(block_sum_256(ss, red) / (float)H + eps);
+    return 1.0f / rms;
+}
+
+__device__ __forceinline__ void store_x(void* out, int dtype, int d, float v) {
+    if (dtype == X_F32) reinterpret_cast<float*>(out)[d] = v;
+    else if (dtype == X_F16) reinterpret_cast<__half*>(out)[d] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16*>(out)[d] = __float2bfloat16_rn(v);
+}
+
+// One CTA of 256 threads per token: hidden += delta (optional), x = cast(hidden * inv_rms * weight).
+// VEC: H a multiple of 4 and at most 8192, 16-byte aligned rows: a thread keeps its (at most eight) 4-column
+// items in registers — every load is requested before anything is stored, one pass over the row.
+template <bool VEC>
+__global__ void __launch_bounds__(256) residual_rms_norm_kernel(float* __restrict__ hidden, int hidden_stride, const void* __restrict__ delta,
+                                                                int delta_dtype, int delta_stride, const float* __restrict__ delta2,
+                                                                int delta2_stride, const __half* __restrict__ weight, float eps,
+                                                                int center, void* __restrict__ x_out, int x_dtype, int x_stride, int H) {
+    __shared__ float red[256];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    float* row = hidden + (size_t)t * hidden_stride;
+    const unsigned char* drow = delta ? reinterpret_cast<const unsigned char*>(delta) + (size_t)t * delta_stride : nullptr;
+    const float* d2row = delta2 ? delta2 + (size_t)t * delta2_stride : nullptr;
+    unsigned char* xrow = reinterpret_cast<unsigned char*>(x_out) + (size_t)t * x_stride;
+    if (VEC) {
+        constexpr int kItems = 8;
+        const int n4 = H >> 2;
+        float4 h[kItems], dl[kItems];
+        uint2 wv[kItems];
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) {
+            const int it = tid + 256 * i;
+            h[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            dl[i] = h[i];
+            wv[i] = make_uint2(0x3C003C00u, 0x3C003C00u);   // 1.0
+            if (it < n4) {
+                h[i] = reinterpret_cast<const float4*>(row)[it];
+                if (drow) {
+                    if (delta_dtype == X_F32) dl[i] = reinterpret_cast<const float4*>(drow)[it];
+                    else {
+                        const uint2 r2 = reinterpret_cast<const uint2*>(drow)[it];
+                        if (delta_dtype == X_F16) {
+                            const __half2 p0 = *reinterpret_cast<const __half2*>(&r2.x), p1 = *reinterpret_cast<const __half2*>(&r2.y);
+                            dl[i] = make_float4(__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1));
+                        } else {
+                            dl[i] = make_float4(__uint_as_float(r2.x << 16), __uint_as_float(r2.x & 0xFFFF0000u), __uint_as_float(r2.y << 16),
+                                                __uint_as_float(r2.y & 0xFFFF0000u));
+                        }
+                    }
+                }
+                if (d2row) {
+                    const float4 e = reinterpret_cast<const float4*>(d2row)[it];
+                    dl[i].x += e.x; dl[i].y += e.y; dl[i].z += e.z; dl[i].w += e.w;
+                }
+                if (weight) wv[i] = reinterpret_cast<const uint2*>(weight)[it];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) {
+            h[i].x += dl[i].x; h[i].y += dl[i].y; h[i].z += dl[i].z; h[i].w += dl[i].w;
+        }
+        float mean = 0.f;
+        if (center) {
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < kItems; ++i) sum += (h[i].x + h[i].y) + (h[i].z + h[i].w);
+            mean = block_sum_256(sum, red) / (float)H;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) {
+            if (tid + 256 * i < n4) {
+                ss = fmaf(h[i].x - mean, h[i].x - mean, ss);
+                ss = fmaf(h[i].y - mean, h[i].y - mean, ss);
+                ss = fmaf(h[i].z - mean, h[i].z - mean, ss);
+                ss = fmaf(h[i].w - mean, h[i].w - mean, ss);
+            }
+        }
+        const float inv_rms = block_inv_rms_256(ss, H, eps, red);
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) {
+            const int it = tid + 256 * i;
+            if (it < n4) {
+                if (drow || d2row) reinterpret_cast<float4*>(row)[it] = h[i];
+                const __half2 w0 = *reinterpret_cast<const __half2*>(&wv[i].x), w1 = *reinterpret_cast<const __half2*>(&wv[i].y);
+                float v[4] = {(h[i].x - mean) * inv_rms, (h[i].y - mean) * inv_rms, (h[i].z - mean) * inv_rms, (h[i].w - mean) * inv_rms};
+                if (weight) {
+                    v[0] *= __low2float(w0); v[1] *= __high2float(w0); v[2] *= __low2float(w1); v[3] *= __high2float(w1);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) store_x(xrow, x_dtype, 4 * it + c, v[c]);
+            }
+        }
+    } else {
+        if (drow || d2row)
+            for (int d = tid; d < H; d += 256)   // (a thread re-reads only its own columns)
+                row[d] += (drow ? load_x_as_f32(drow, delta_dtype, d) : 0.f) + (d2row ? d2row[d] : 0.f);
+        float mean = 0.f;
+        if (center) {
+            float sum = 0.f;
+            for (int d = tid; d < H; d += 256) sum += row[d];
+            mean = block_sum_256(sum, red) / (float)H;
+        }
+        float ss = 0.f;
+        for (int d = tid; d < H; d += 256) ss = fmaf(row[d] - mean, row[d] - mean, ss);
+        const float inv_rms = block_inv_rms_256(ss, H, eps, red);
+        for (int d = tid; d < H; d += 256) {
+            float v = (row[d] - mean) * inv_rms;
+            if (weight) v *= __half2float(weight[d]);
+            store_x(xrow, x_dtype, d, v);
+        }
+    }
+}
+
+static int launch_norm(float* hidden, int hidden_stride, const void* delta, int delta_dtype, int delta_stride, const float* delta2,
+                       int delta2_stride, const void* weight, float eps, int center, void* x_out, int x_dtype, int x_stride, int H,
+                       int n_tokens, cudaStream_t st) {
+    const bool vec = H % 4 == 0 && H <= 8192 && ((uintptr_t)hidden & 15) == 0 && (hidden_stride & 3) == 0 && ((uintptr_t)delta & 15) == 0 &&
+                     (delta_stride & 15) == 0 && ((uintptr_t)delta2 & 15) == 0 && (delta2_stride & 3) == 0 && ((uintptr_t)weight & 7) == 0 &&
+                     ((uintptr_t)x_out & 15) == 0 && (x_stride & 15) == 0;
+    if (vec)
+        residual_rms_norm_kernel<true><<<n_tokens, 256, 0, st>>>(hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2, delta2_stride,
+                                                                 (const __half*)weight, eps, center, x_out, x_dtype, x_stride, H);
+    else
+        residual_rms_norm_kernel<false><<<n_tokens, 256, 0, st>>>(hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2, delta2_stride,
+                                                                  (const __half*)weight, eps, center, x_out, x_dtype, x_stride, H);
+    return (int)cudaGetLastError();
+}
+
+// Reference signature (cuda/src/kernels.cu:1178): fp32 in, fp32 out, fp16 weight, one vector.
+extern "C" int vib3_launch_rms_norm_f32(const void* input, void* output, const void* weight, int hidden_dim, float eps,
+                                        void* stream) {
+    if (!input || !output || !weight) return VIB3_ERR_NULL;
+    if (hidden_dim <= 0) return VIB3_ERR_SHAPE;
+    if (input != output)
+        if (cudaMemcpyAsync(output, input, (size_t)hidden_dim * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream) != cudaSuccess)
+            return (int)cudaGetLastError();
+    // normalise in place on the copy: the kernel reads and writes the same row
+    return launch_norm((float*)output, hidden_dim, nullptr, 0, 0, nullptr, 0, weight, eps, 0, output, X_F32, 0, hidden_dim, 1,
+                       (cudaStream_t)stream);
+}
+
+// The two steps either side of the MoE sublayer in the reference's layer loop (residual_add_f32_f32, then
+// rms_norm_f32 of the next sublayer: src/runtime/engine.rs:5302, :5072) as ONE launch for n_tokens rows:
+//   hidden[t] += delta[t] + delta2[t]   (delta: the other sublayer's output, fp32 / fp16 / bf16, or NULL; delta2: fp32 or
+//                                        NULL, e.g. the sum over expert-parallel ranks of the previous MoE sublayer's outputs)
+//   x_out[t]   = cast(hidden[t] * inv_rms(hidden[t]) * weight)      (weight fp16 or NULL; x_out fp32 / fp16 / bf16)
+// center != 0 (not in the reference): the row's mean is removed first, x = (hidden - mean) * inv_rms(hidden - mean) * weight.
+// For stacks of SYNTHETIC layers: INT4 codes drawn uniformly from [-8, 7] have mean -0.5, so every output row of such a
+// matrix carries a common term proportional to the sum of its input; through a residual stream that term feeds itself and
+// after a few layers every token routes alike.  Trained weights have no such mean.
+// The MoE sublayer that follows adds its own output to hidden (out_accumulate = 1), so a layer costs this
+// launch plus the MoE launches.
+extern "C" int vib3_launch_residual_rms_norm(float* hidden, int hidden_stride, const void* delta, int delta_dtype,
+                                             int delta_stride_bytes, const float* delta2, int delta2_stride,
+                                             const void* weight_f16, float eps, int center, void* x_out, int x_dtype,
+                                             int x_stride_bytes, int hidden_dim, int n_tokens, void* stream) {
+    if (!hidden || !x_out) return VIB3_ERR_NULL;
+    if (hidden_dim <= 0 || n_tokens <= 0 || hidden_stride < hidden_dim) return VIB3_ERR_SHAPE;
+    if (x_dtype < X_F32 || x_dtype > X_BF16 || (delta && (delta_dtype < X_F32 || delta_dtype > X_BF16))) return VIB3_ERR_UNSUPPORTED;
+    if ((void*)hidden == x_out) return VIB3_ERR_UNSUPPORTED;
+    if (delta2 && delta2_stride < hidden_dim) return VIB3_ERR_SHAPE;
+    return launch_norm(hidden, hidden_stride, delta, delta_dtype, delta_stride_bytes, delta2, delta2_stride, weight_f16, eps, center, x_out,
+                       x_dtype, x_stride_bytes, hidden_dim, n_tokens, (cudaStream_t)stream);
+}

@@ -112,7 +112,7 @@ def combine_partials(out: torch.Tensor, partial: torch.Tensor, rank: int, world:
 class ExpertParallelDecoder:
     """One rank's share of an expert-parallel MoE layer stack."""
 
-    def __init__(self, model, rank: int, world: int, group=None):
+    def __init__(self, model, rank: int, world: int, group=None, collectives: Optional[str] = None):
         from .moe import MoeDecoder
         self.model, self.rank, self.world, self.group = model, rank, world, group
         self.dec = MoeDecoder(model, exact_order=True)
@@ -127,7 +127,7 @@ class ExpertParallelDecoder:
         self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
         # "a2a": both exchanges as one-hop all-to-alls (plus a row sum); "ring": NCCL all-gather / reduce-scatter
         # measured: two ranks ring 11 + 11 us, a2a 14 + 14 us; eight ranks ring 21 + 19 us, a2a 16 + 17 us
-        self.collectives = os.environ.get("VIB3_EP_COLLECTIVES", "a2a" if world >= 8 else "ring")
+        self.collectives = collectives or ("a2a" if world >= 8 else "ring")
         self.send_rep = torch.zeros(world, self.msg_bytes, dtype=torch.uint8, device=dev) if self.collectives == "a2a" else None
         self.partial_in = torch.zeros(world, sh.hidden, dtype=torch.float32, device=dev) if self.collectives == "a2a" else None
         cap = world * sh.top_k
@@ -142,20 +142,21 @@ class ExpertParallelDecoder:
         # router, pair selection, (gate/up, down) per grouped launch, the row sum of the all-to-all form
         self.launches_per_step = 2 + 2 * self.grouped_launches + (1 if self.collectives == "a2a" else 0)
 
-    def step(self, layer: int, x: torch.Tensor) -> torch.Tensor:
+    def step(self, layer: int, x: torch.Tensor, logit_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
-        self.route(layer, x)
+        self.route(layer, x, logit_offset)
         self.gather()
         self.experts(layer)
         return self.combine()
 
-    def route(self, layer: int, x: torch.Tensor) -> None:
+    def route(self, layer: int, x: torch.Tensor, logit_offset: Optional[torch.Tensor] = None) -> None:
         from . import kernels
         sh, dec = self.model.shape, self.dec
         self.send_x.copy_(x)
         # the router writes the expert ids and routing weights into the message
         kernels.router_topk_ex(self.send_x, self.model.router_w[layer], dec.scores, None, self.send_ids, self.send_w,
-                               sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, dec.exact_order, dec.workspace)
+                               sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, dec.exact_order, dec.workspace,
+                               logit_offset=logit_offset)
 
     def gather(self) -> None:
         gather_messages(self.send, self.recv, self.world, self.group, self.send_rep)
@@ -185,10 +186,171 @@ class ExpertParallelDecoder:
         return (self.send_ids[:k].cpu().view(torch.int16).numpy().view("uint16"), self.send_w[:k].cpu().numpy())
 
 
+def shared_expert_owner(layer: int, world: int) -> int:
+    """The rank that computes the shared expert of a layer when the hidden state is replicated (stack mode):
+    layers take turns, so that no rank repeats another's bytes."""
+    return layer % world
+
+
+def expert_range(rank: int, num_experts: int, world: int) -> Tuple[int, int]:
+    mine = local_experts(rank, num_experts, world)
+    return (mine[0], mine[-1] + 1) if mine else (0, 0)
+
+
+class ExpertParallelStack:
+    """The n_layers-deep MoE stack, expert-parallel, for ONE batch of tokens that every rank holds (the hidden
+    state is replicated; a data-parallel attention stage would all-gather its tokens first).  Per layer: fused
+    residual-add + RMS-norm launch (the attention block's stand-in is a seeded bf16 tensor added to the hidden
+    state; the previous layer's MoE output, summed over ranks, is added by the same launch), the router (replicated:
+    identical top-k on every rank by construction), the rank's own experts — batch 1 through the batch-1 kernels over
+    the token's local experts, larger batches through the grouped tensor-core kernels restricted to the rank's
+    expert range — the shared expert on rank layer mod G, and an all-reduce of the partial outputs.
+    Physical layers are reused in rotation (layer l -> l mod L)."""
+
+    def __init__(self, model, rank: int, world: int, n_layers: int, batch: int, seed: int = 77, group=None):
+        from .moe import MoeDecoder
+        self.model, self.rank, self.world, self.n_layers, self.T, self.group = model, rank, world, n_layers, batch, group
+        sh = model.shape
+        dev = model.router_w.device
+        g = torch.Generator(device=dev).manual_seed(seed)           # the same tensors on every rank
+        self.attn = (torch.randn(n_layers, batch, sh.hidden, generator=g, device=dev) * 0.3).to(torch.bfloat16)
+        self.norm_w = (1.0 + 0.1 * torch.randn(n_layers, sh.hidden, generator=g, device=dev)).to(torch.float16)
+        self.h0 = torch.randn(batch, sh.hidden, generator=g, device=dev)
+        self.h = torch.zeros(batch, sh.hidden, dtype=torch.float32, device=dev)
+        self.x = torch.zeros(batch, sh.hidden, dtype=torch.bfloat16, device=dev)
+        self.partial = torch.zeros(batch, sh.hidden, dtype=torch.float32, device=dev)
+        self.lo, self.hi = expert_range(rank, sh.num_experts, world)
+        self.dec = MoeDecoder(model, exact_order=True)
+        self.gd = None
+        if batch > 1:
+            from .grouped import GroupedDecoder
+            self.gd = GroupedDecoder(model, max_tokens=batch)
+        self.ids_loc = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
+        self.w_loc = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
+        self.n_loc = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.launches_per_layer = (4 if batch == 1 else 8) + (1 if world > 1 else 0)
+
+    def layer(self, l: int, prev: Optional[torch.Tensor]) -> torch.Tensor:
+        from . import kernels as K
+        sh, dec = self.model.shape, self.dec
+        phys = l % self.model.n_layers
+        own_shared = shared_expert_owner(l, self.world) == self.rank
+        K.residual_rms_norm(self.h, self.attn[l], self.norm_w[l], 1e-6, self.x, delta2=prev, center=True)
+        if self.T == 1:
+            dec.route(phys, self.x[0])
+            K.select_local_experts(dec.ids, dec.weights, sh.top_k, self.lo, self.hi, self.ids_loc, self.w_loc, self.n_loc)
+            K.moe_layer_int4_paged_var(self.x[0], dec.tables[phys], sh.num_experts, dec.shared_tables[phys] if own_shared else 0,
+                                       self.ids_loc, self.w_loc, sh.top_k, 1.0, dec.act, self.partial[0], False, sh.hidden,
+                                       sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page,
+                                       self.n_loc, dec.status)
+        else:
+            self.gd.route(phys, self.x)
+            self.gd.experts(phys, self.x, out=self.partial, expert_range=(self.lo, self.hi), shared=own_shared)
+        if self.world > 1:
+            dist.all_reduce(self.partial, op=dist.ReduceOp.SUM, group=self.group)
+        return self.partial
+
+    def step(self, i: int = 0) -> torch.Tensor:
+        """One batch through the whole stack; returns the final hidden state [T, H] fp32 (replicated)."""
+        from . import kernels as K
+        self.h.copy_(self.h0)
+        prev = None
+        for l in range(self.n_layers):
+            prev = self.layer(l, prev)
+        self.h.add_(prev)
+        return self.h
+
+    def status(self) -> int:
+        return int(self.dec.status.item()) | (int(self.gd.status.item()) if self.gd is not None else 0)
+
+
+def imbalance_bound(num_experts: int, top_k: int, world: int, tokens: int, trials: int = 2000, seed: int = 1) -> dict:
+    """Monte-Carlo bound on expert-parallel speed-up from load imbalance alone (uniform routing): a step waits for
+    the rank with the most DISTINCT experts to read, so speed-up <= distinct experts of the step / that maximum."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    per = (num_experts + world - 1) // world
+    tot, worst = 0.0, 0.0
+    for _ in range(trials):
+        picks = np.concatenate([rng.choice(num_experts, top_k, replace=False) for _ in range(tokens)])
+        distinct = np.unique(picks)
+        owners = np.minimum(distinct // per, world - 1)
+        tot += len(distinct)
+        worst += np.bincount(owners, minlength=world).max()
+    return {"tokens": tokens, "distinct_experts": tot / trials, "busiest_rank_experts": worst / trials,
+            "speedup_bound": tot / worst, "efficiency_bound": tot / worst / world}
+
+
 def build_rank_model(shape: MoeShape, n_layers: int, device, seed: int, rank: int, world: int, per_page_content=False):
     from .synth import build_synthetic_moe
     return build_synthetic_moe(shape, n_layers, device, seed=seed, slot_seed=99 + rank,
                                experts=local_experts(rank, shape.num_experts, world), per_page_content=per_page_content)
+
+
+def parity_check(rank: int, world: int, dev, steps: int = 6, group=None) -> dict:
+    """Every rank decodes its own tokens through ExpertParallelDecoder on a small model and compares with the
+    single-GPU fused layer on the FULL model (same bytes: pages are derived from (seed, page id)).  top_k = 12 and
+    16 experts per rank, so that a step has up to 12 * world pairs; on odd steps a logit offset pulls every token to
+    rank 0's experts: rank 0 then owns ALL pairs (several launch windows) and the other ranks none (empty windows
+    ahead of the collective).  Collective: every rank calls this together.  Returns the worst figures over ranks."""
+    from .core_types import SCORING_SIGMOID
+    from .moe import MoeDecoder
+    from .synth import build_synthetic_moe
+    sh = MoeShape("ep-parity", 1024, 2048, 16 * world, 12, 1, SCORING_SIGMOID, 2.5, True)
+    mine = build_rank_model(sh, 2, dev, 11, rank, world, per_page_content=True)
+    full = build_synthetic_moe(sh, 2, dev, seed=11, slot_seed=3, per_page_content=True)
+    epd = ExpertParallelDecoder(mine, rank, world, group)
+    ref = MoeDecoder(full)
+    off = torch.zeros(sh.num_experts, dtype=torch.float32, device=dev)
+    off[:16] = 8.0
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    worst_abs, worst_rel, topk_equal, status, max_pairs = 0.0, 0.0, 1, 0, 0
+    for step in range(steps):
+        x = torch.randn(sh.hidden, generator=g, device=dev).to(torch.bfloat16)
+        o = off if step % 2 else None
+        layer = step % 2
+        out = epd.step(layer, x, o).clone()
+        ids_ep = epd.routing()[0].tolist()
+        want = ref.forward_layer(layer, x, logit_offset=o).clone()
+        torch.cuda.synchronize()
+        if ids_ep != ref.routing()[0].tolist():
+            topk_equal = 0
+        status |= int(ref.status.item()) | int(epd.dec.status.item())
+        max_pairs = max(max_pairs, int(epd.n_pairs.item()))
+        worst_abs = max(worst_abs, float((out - want).abs().max()))
+        worst_rel = max(worst_rel, float((out - want).norm() / want.norm()))
+    t = torch.tensor([worst_abs, worst_rel, float(1 - topk_equal), float(status), float(max_pairs)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    res = {"max_abs": float(t[0]), "rel_l2": float(t[1]), "topk_equal": bool(t[2] == 0), "status": int(t[3]),
+           "max_local_pairs": int(t[4]), "steps": steps, "collectives": epd.collectives,
+           "ok": bool(t[0] <= 2e-2 and t[1] <= 1e-3 and t[2] == 0 and t[3] == 0)}
+    del epd, ref, mine, full
+    torch.cuda.empty_cache()
+    return res
+
+
+def stack_parity_check(rank: int, world: int, dev, batch: int, n_layers: int = 5, group=None) -> dict:
+    """ExpertParallelStack on the ranks' shards against the same stack on one GPU with the full model."""
+    from .core_types import SCORING_SIGMOID
+    from .synth import build_synthetic_moe
+    sh = MoeShape("ep-stack-parity", 1024, 2048, 8 * world, 4, 1, SCORING_SIGMOID, 2.5, True)
+    mine = build_rank_model(sh, 2, dev, 13, rank, world, per_page_content=True)
+    full = build_synthetic_moe(sh, 2, dev, seed=13, slot_seed=3, per_page_content=True)
+    a = ExpertParallelStack(mine, rank, world, n_layers, batch, group=group)
+    b = ExpertParallelStack(full, 0, 1, n_layers, batch)
+    ha = a.step().clone()
+    hb = b.step().clone()
+    torch.cuda.synchronize()
+    t = torch.tensor([float((ha - hb).abs().max()), float((ha - hb).norm() / hb.norm()), float(a.status() | b.status())],
+                     dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    res = {"batch": batch, "layers": n_layers, "max_abs": float(t[0]), "rel_l2": float(t[1]), "status": int(t[2]),
+           "ok": bool(t[1] <= 2e-3 and t[2] == 0)}
+    del a, b, mine, full
+    torch.cuda.empty_cache()
+    return res
 
 
 def bench_main(args) -> None:
@@ -212,54 +374,51 @@ def bench_main(args) -> None:
     def step(i):
         ep.step(i % layers, xs[i % B.N_TOKENS])
 
+    def timed_graph(fn, chunk, min_steps, min_ms):
+        """(ms per step as the max over ranks, steps timed): one CUDA graph of `chunk` steps (kernels and NCCL
+        collectives), replayed as often as every rank needs for min_steps steps and min_ms milliseconds."""
+        stream = torch.cuda.Stream(device=dev)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                fn(i)
+            stream.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(chunk):
+                    fn(i)
+            g.replay()
+            stream.synchronize()
+            replays = max(1, -(-min_steps // chunk))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for attempt in range(2):
+                dist.barrier()
+                stream.synchronize()
+                e0.record(stream)
+                for _ in range(replays):
+                    g.replay()
+                e1.record(stream)
+                stream.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t[0])
+                if ms >= min_ms:
+                    break
+                replays = int(replays * min_ms / max(ms, 1e-3) * 1.1) + 1   # (the same on every rank: ms is the maximum)
+            del g
+        torch.cuda.current_stream().wait_stream(stream)
+        return ms / (replays * chunk), replays * chunk
+
     for i in range(W):
         step(i)
     torch.cuda.synchronize()
     dist.barrier()
-    # The step (kernels + NCCL collectives) is captured into a CUDA graph so that the 2G+1 launches
-    # per step are not bound by the host; if capture is refused the loop runs eagerly.
-    chunk = min(K, 32)
-    graph, mode = None, "eager"
-    if os.environ.get("VIB3_EP_NO_GRAPH") != "1":
-        try:
-            stream = torch.cuda.Stream(device=dev)
-            stream.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(stream):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream):
-                    for i in range(chunk):
-                        step(i)
-            torch.cuda.synchronize()
-            g.replay()
-            torch.cuda.synchronize()
-            graph, mode = g, "cuda-graph"
-        except Exception as exc:  # noqa: BLE001
-            graph, mode = None, f"eager (graph capture refused: {type(exc).__name__})"
-            torch.cuda.synchronize()
-    ok = torch.tensor([1 if graph is not None else 0], device=dev)
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    if int(ok.item()) == 0:
-        graph = None
-    dist.barrier()
     sampler = B.ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0.record()
-    if graph is not None:
-        for _ in range(K // chunk):
-            graph.replay()
-        for i in range(K % chunk):
-            step(i)
-    else:
-        for i in range(K):
-            step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    ms_local = e0.elapsed_time(e1)
-    dist.barrier()
+    chunk = max(1, min(K, 32))
+    ms_step, timed_steps = timed_graph(step, chunk, max(K, B.MIN_TIMED_STEPS), B.MIN_TIMED_MS)
     clocks = sampler.stop() if sampler else None
 
     # e2e: token from pinned host memory in, layer output back to the host, every step
@@ -271,71 +430,69 @@ def bench_main(args) -> None:
         x_dev.copy_(x_host[i % B.N_TOKENS], non_blocking=True)
         out_host.copy_(ep.step(i % layers, x_dev), non_blocking=True)
         torch.cuda.current_stream().synchronize()
-    for i in range(min(W, 4)):
+    for i in range(4):
         e2e_step(i)
     dist.barrier()
+    e2e_steps = max(K, B.MIN_TIMED_STEPS)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(K):
+    for i in range(e2e_steps):
         e2e_step(i)
     e1.record()
     torch.cuda.synchronize()
-    e2e_local = e0.elapsed_time(e1)
-
-    # where the step's time goes: each phase alone, 16 times back to back in a CUDA graph of its own
-    # (CUDA events on this rank; every rank replays the same graphs, so the collectives match up)
-    phases = {}
-    if graph is not None:
-        def time_phase(fn, reps=16):
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                gp = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gp, stream=side):
-                    for i in range(reps):
-                        fn(i)
-                gp.replay()
-                side.synchronize()
-                dist.barrier()
-                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a0.record(side)
-                for _ in range(4):
-                    gp.replay()
-                a1.record(side)
-                side.synchronize()
-            return a0.elapsed_time(a1) * 1e3 / (4 * reps)
-        phases["route"] = time_phase(lambda i: ep.route(i % layers, xs[i % B.N_TOKENS]))
-        phases["all_gather"] = time_phase(lambda i: ep.gather())
-        phases["experts"] = time_phase(lambda i: ep.experts(i % layers))
-        phases["reduce_scatter"] = time_phase(lambda i: ep.combine())
-    dist.barrier()
-
-    t = torch.tensor([ms_local, e2e_local], dtype=torch.float64, device=dev)
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    e2e_ms = float(t[0]) / e2e_steps
+
+    # where the step's time goes: each phase alone in a CUDA graph of its own
+    phases = {}
+    for name, fn in (("route", lambda i: ep.route(i % layers, xs[i % B.N_TOKENS])), ("exchange_tokens", lambda i: ep.gather()),
+                     ("experts", lambda i: ep.experts(i % layers)), ("combine", lambda i: ep.combine())):
+        phases[name] = round(timed_graph(fn, 16, 64, 5.0)[0] * 1e3, 1)
+    assert int(ep.dec.status.item()) == 0
+
+    # correctness at this world size, outside every timed region
+    parity = parity_check(rank, world, dev)
+    extras = {}
+    if not args.no_extras:
+        peak = B.measured_peaks()[0]
+        c4 = {"workload": f"C4 {B.STACK_LAYERS}-layer kimi-k2.5-shape MoE stack, experts sharded over {world} GPUs, hidden state replicated, "
+                          "partial outputs summed by NCCL all-reduce; attention = seeded bf16 residual add",
+              "layer_aliasing": f"layer l uses physical layer l mod {layers}: a rank holds {layers} x {len(local_experts(rank, sh.num_experts, world)) + 1} experts"}
+        for batch in (1, 32):
+            st = ExpertParallelStack(model, rank, world, B.STACK_LAYERS, batch)
+            ms, n = timed_graph(lambda i: st.step(i), 1, 3, 40.0)
+            assert st.status() == 0
+            bound = imbalance_bound(sh.num_experts, sh.top_k, world, batch, trials=400)
+            c4[f"batch{batch}"] = {"tokens_per_s": batch * 1e3 / ms, "ms_per_step": ms, "us_per_layer": ms * 1e3 / B.STACK_LAYERS,
+                                   "timed_steps": n, "imbalance_bound": bound,
+                                   "parity": stack_parity_check(rank, world, dev, batch)}
+            del st
+            torch.cuda.empty_cache()
+        extras["c4"] = c4
+
     if rank == 0:
         b_gu, b_dn, b_r = B.algorithmic_bytes(sh)
+        peak = B.measured_peaks()[0]
+        per_step = (b_gu + b_dn + b_r) / (ms_step * 1e-3) / 1e9
         line = {
-            "metric": B.METRIC, "value": world * K / (ms * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int4 weights, 16-bit fixed-point activations, int32/fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "C1 kimi-k2.5-shape MoE layer, batch-1 decode per rank, experts sharded expert-parallel",
-                       "hidden": sh.hidden, "experts": sh.num_experts, "experts_per_gpu": sh.num_experts // world,
-                       "top_k": sh.top_k, "shared_experts": 1, "intermediate": sh.intermediate, "tokens_per_step": world,
-                       "physical_layers": layers, "launch_mode": mode, "l2_policy": "inputs larger than L2: layers and tokens rotate",
-                       "parallelism": f"ep{world}: exchange of (token, routing) + exchange and sum of partial sums, NCCL ({ep.collectives})"},
-            "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": world * sh.hidden * 2,
-                    "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms / K},
-            "gpu_launches": K * ep.launches_per_step * world,
-            "phase_us_rank0": {k: round(v, 1) for k, v in phases.items()},
+            "metric": B.METRIC, "value": world / (ms_step * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": B.DTYPE,
+            "data": "synthetic", "config": B.workload_config(world),
+            "timed": {"steps": timed_steps, "graph_steps": chunk, "physical_layers": layers, "launch_mode": "cuda-graph",
+                      "collectives": f"NCCL ({ep.collectives})", "experts_per_gpu": sh.num_experts // world},
+            "e2e": {"value": world / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": world * sh.hidden * 2,
+                    "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": timed_steps * ep.launches_per_step * world,
+            "phase_us_rank0": phases, "parity": parity,
+            "imbalance_bound": imbalance_bound(sh.num_experts, sh.top_k, world, world, trials=400),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": world * (b_gu + b_dn + b_r) / (ms * 1e-3 / K) / 1e9,
-                         "peak": world * B.measured_peaks()[0], "unit": "GB/s",
-                         "frac": (b_gu + b_dn + b_r) / (ms * 1e-3 / K) / 1e9 / B.measured_peaks()[0],
-                         "traffic": None, "note": "whole step over all ranks (per-kernel roofline is reported at N=1)"},
+            "roofline": {"bound": "hbm", "achieved": world * per_step, "peak": world * peak, "unit": "GB/s", "frac": per_step / peak,
+                         "traffic": None, "note": "whole step over all ranks, one layer-token per rank (the per-kernel roofline is reported at N=1)"},
         }
+        line.update(extras)
         print(json.dumps(line))
-    # leave without tearing the communicator down under a live CUDA graph that holds its kernels
-    graph = None
+    # leave without tearing the communicator down under live CUDA graphs that hold its kernels
     torch.cuda.synchronize()
     import sys
     sys.stdout.flush()

@@ -87,6 +87,24 @@ def residual_add_f32_f32(accumulator, layer_output, dim: int, stream: Optional[i
     check("residual_add_f32_f32", lib().vib3_launch_residual_add_f32_f32(_ptr(accumulator), _ptr(layer_output), dim, _stream(stream)))
 
 
+def rms_norm_f32(input_f32, output_f32, weight_f16, hidden_dim: int, eps: float, stream: Optional[int] = None) -> None:
+    """kernels.rs:2560-2603 (GPU arm): fp32 in, fp32 out, fp16 weight."""
+    check("rms_norm_f32", lib().vib3_launch_rms_norm_f32(_ptr(input_f32), _ptr(output_f32), _ptr(weight_f16), hidden_dim, eps,
+                                                        _stream(stream)))
+
+
+def residual_rms_norm(hidden: torch.Tensor, delta, weight_f16, eps: float, x_out: torch.Tensor, stream: Optional[int] = None,
+                      delta2=None, center: bool = False) -> None:
+    """hidden [T, H] fp32 += delta [T, H] + delta2 [T, H] fp32 (either may be None); x_out [T, H] = cast(rms_norm(hidden) *
+    weight): one launch."""
+    T, H = hidden.shape
+    check("residual_rms_norm", lib().vib3_launch_residual_rms_norm(
+        _ptr(hidden), hidden.stride(0), _ptr(delta), x_dtype_code(delta) if delta is not None else 0,
+        delta.stride(0) * delta.element_size() if delta is not None else 0, _ptr(delta2),
+        delta2.stride(0) if delta2 is not None else 0, _ptr(weight_f16), eps, int(center), _ptr(x_out),
+        x_dtype_code(x_out), x_out.stride(0) * x_out.element_size(), H, T, _stream(stream)))
+
+
 def router_gemv_f32(hidden_state, router_weights_f16, scores, hidden_dim: int, num_experts: int,
                     stream: Optional[int] = None) -> None:
     check("router_gemv_f32", lib().vib3_launch_router_gemv_f32(_ptr(hidden_state), _ptr(router_weights_f16), _ptr(scores),

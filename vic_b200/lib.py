@@ -67,14 +67,20 @@ SIGNATURES = {
     "vib3_launch_select_local_pairs": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "vib3_moe_layer_step_host": (_i, [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _f, _vp,
                                       _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "vib3_moe_step_create": (_i, [_i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _i,
+                                  _i, _i, _i, _i, _vp, _vp, C.POINTER(_vp)]),
+    "vib3_moe_step_run": (_i, [_vp, _vp, _vp]),
+    "vib3_moe_step_destroy": (None, [_vp]),
     "vib3_launch_sum_rows_f32": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "vib3_launch_select_local_experts": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
-    "vib3_moe_grouped_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i, _i]),
+    "vib3_moe_grouped_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i, _i, _i, _i]),
     "vib3_moe_grouped_prewarm": (_i, [_vp, C.c_size_t, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, C.c_size_t, C.POINTER(_vp)]),
     "vib3_moe_grouped_destroy": (None, [_vp]),
-    "vib3_launch_moe_grouped_int4": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _i, _vp, _i, _i, _vp, _vp]),
+    "vib3_launch_moe_grouped_int4": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _i, _i, _i, _vp, _i, _i, _vp, _vp]),
     "vib3_launch_router_topk_batch": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _f, _i,
                                            _i, _vp, _vp]),
+    "vib3_launch_rms_norm_f32": (_i, [_vp, _vp, _vp, _i, _f, _vp]),
+    "vib3_launch_residual_rms_norm": (_i, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _i, _vp, _i, _i, _i, _i, _vp]),
     "vib3_config_set": (_i, [_i, _i]),
     "vib3_pool_create": (_vp, [_vp, C.c_size_t, C.c_uint64]),
     "vib3_pool_destroy": (None, [_vp]),
@@ -88,6 +94,19 @@ SIGNATURES = {
     "vib3_pool_device_page_table": (_i, [_vp, C.c_uint16, _i, _i, _i, C.POINTER(_vp)]),
     "vib3_page_key": (C.c_uint64, [C.c_uint16] * 4),
     "vib3_planner_plan_layer": (_i, [_vp, C.c_uint16, _vp, _i, _i, _vp, _i]),
+    "vib3_int4_matrix_bytes": (C.c_size_t, [_i, _i]),
+    "vib3_quantize_int4": (_i, [_vp, _i, _i, _i, _vp]),
+    "vib3_writer_create": (_vp, [C.c_char_p, C.c_char_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "vib3_writer_add_int4_matrix": (_i, [_vp, C.c_uint16, C.c_uint16, C.c_uint16, _i, _i, _vp]),
+    "vib3_writer_finalize": (_i, [_vp]),
+    "vib3_writer_destroy": (None, [_vp]),
+    "vib3_file_open": (_vp, [C.c_char_p, C.POINTER(_i)]),
+    "vib3_file_close": (None, [_vp]),
+    "vib3_file_page_count": (_i, [_vp]),
+    "vib3_file_summary": (_i, [_vp] + [C.POINTER(C.c_uint32)] * 6 + [C.POINTER(C.c_uint64)]),
+    "vib3_file_page_info": (_i, [_vp, _i, _vp]),
+    "vib3_file_read_page": (_i, [_vp, _i, _vp, C.c_size_t]),
+    "vib3_file_load_into_pool": (C.c_longlong, [_vp, _vp, _i, _i, _i, _i]),
     "vib3_b200_version": (C.c_char_p, []),
 }
 

@@ -132,6 +132,45 @@ class MoeDecoder:
                                     sh.down.rows_per_page, self.status, stream.cuda_stream)
         return out_pin
 
+    def forward_host_bound(self, layer: int, x_host: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """forward_host_call with the layer bound once as a CUDA graph inside the library (vib3_moe_step_create /
+        vib3_moe_step_run): per token one C call with three arguments.  The first call for a (layer, dtype) builds the
+        graph and must not happen inside a stream capture; ``stream`` must be a non-default stream.  Returns the
+        pinned fp32 [H] result buffer of that (layer, dtype), valid until the next call."""
+        import ctypes as C
+        from .lib import check, lib
+        sh = self.model.shape
+        stream = stream or torch.cuda.current_stream()
+        if x_host.is_cuda:
+            raise ValueError("host tensor expected")
+        if not hasattr(self, "_bound"):
+            self._bound = {}
+        key = (layer, x_host.dtype)
+        ent = self._bound.get(key)
+        if ent is None:
+            x_dev = torch.zeros(sh.hidden, dtype=x_host.dtype, device=self.out.device)
+            out_pin = torch.zeros(sh.hidden, dtype=torch.float32).pin_memory()
+            w = self.model.router_w[layer]
+            h = C.c_void_p()
+            check("moe_step_create", lib().vib3_moe_step_create(
+                kernels.x_dtype_code(x_host), x_dev.data_ptr(), w.data_ptr(), {torch.float16: 0, torch.float32: 1}[w.dtype],
+                self.scores.data_ptr(), None, self.ids.data_ptr(), self.weights.data_ptr(), sh.num_experts, sh.top_k, sh.scoring,
+                sh.scaling_factor, int(sh.normalize), int(self.exact_order), self.workspace.data_ptr(), self.tables[layer],
+                self.shared_tables[layer] or None, 1.0, self.act.data_ptr(), out_pin.data_ptr(), sh.hidden, sh.intermediate,
+                sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, 32, self.status.data_ptr(),
+                stream.cuda_stream, C.byref(h)))
+            ent = (h, x_dev, out_pin, lib().vib3_moe_step_run)
+            self._bound[key] = ent
+        h, _, out_pin, run = ent
+        check("moe_step_run", run(h, x_host.data_ptr(), stream.cuda_stream))
+        return out_pin
+
+    def close(self) -> None:
+        from .lib import lib
+        for h, *_ in getattr(self, "_bound", {}).values():
+            lib().vib3_moe_step_destroy(h)
+        self._bound = {}
+
     def forward_tokens(self, layer: int, xs: torch.Tensor, outs: Optional[torch.Tensor] = None,
                        logit_offset: Optional[torch.Tensor] = None, routing_out=None) -> torch.Tensor:
         """Multi-token decode, xs [T, H] -> [T, H] fp32: every token takes the batch-1 path in turn
