@@ -43,24 +43,30 @@
 
 namespace vib3 {
 
-constexpr int kGrpConvWarps = 16;               // converting warps: TMEM lane quarter = warp & 3, K quarter of the slab = (warp - 6) >> 2
-constexpr int kGrpFirstConvWarp = 6;            // warp 0 TMA, 1 MMA, 2..5 epilogue, 6..21 converting
-constexpr int kGrpThreads = (kGrpFirstConvWarp + kGrpConvWarps) * 32;
-constexpr int kGrpStages = 3;
+constexpr int kGrpConvWarps = 16;               // converting warps: two teams of 8; TMEM lane quarter = warp & 3
+constexpr int kGrpMmaWarps = 4;                 // MMA-issuing warps: a thread issues one tcgen05.mma per ~100 cycles whatever its
+                                                // size (measured), four issuers reach the tensor pipe's own rate
+constexpr int kGrpFirstEpiWarp = 1 + kGrpMmaWarps;          // warp 0 TMA, 1..4 MMA, 5..8 epilogue, 9..24 converting
+constexpr int kGrpFirstConvWarp = kGrpFirstEpiWarp + 4;
+constexpr int kGrpXWarp = kGrpFirstConvWarp + kGrpConvWarps;   // issues the token tiles' copies
+constexpr int kGrpThreads = (kGrpXWarp + 1) * 32;
+constexpr int kGrpStages = 8;                   // weight ring
 constexpr int kGrpSlabK = 256;                  // columns of K per pipeline step
-constexpr int kGrpMaxN = 32;                    // tokens of one expert per pass over its tile
-constexpr int kGrpRawBytes = 16 * 1024;         // codes of 128 rows x 256 columns per stage
-constexpr int kGrpStageBytes = kGrpRawBytes + kGrpMaxN * kGrpSlabK * 2;   // + the tokens' slab: 32 KB
-constexpr int kGrpMaxScaleRow = 448;            // bytes of group scales per row the scale buffers are sized for (K <= 7168)
+constexpr int kGrpMaxN = 16;                    // tokens of one expert per pass over its tile
+constexpr int kGrpABufs = 3;                    // A-operand buffers in tensor memory: the converting warps run up to two slabs ahead
+constexpr int kGrpXStages = kGrpABufs;          // token ring: stage i is released together with A buffer i (one commit frees both)
+constexpr int kGrpRawBytes = 18 * 1024;         // a weight stage: codes 16 KB + scales 2 KB of 128 rows x 256 columns
+constexpr int kGrpXBytes = kGrpMaxN * kGrpSlabK * 2;   // a token stage: 16 tokens x 256 columns fp16 = 8 KB
 constexpr int kGrpTmemCols = 512;
 constexpr int kGrpACols = kGrpSlabK / 2;        // 128 columns: 256 fp16 per row
-constexpr int kGrpDCol0 = 2 * kGrpACols;        // two A buffers, then two D buffers of kGrpMaxN columns
+constexpr int kGrpDCol0 = kGrpABufs * kGrpACols;   // the A buffers, then two D buffers of kGrpMmaWarps partial accumulators of kGrpMaxN columns
+static_assert(kGrpDCol0 + 2 * kGrpMmaWarps * kGrpMaxN <= kGrpTmemCols, "tensor memory budget");
 constexpr int kGrpMaxTokens = 128;
 constexpr int kRouterMaxExpertsGrouped = 512;   // MAX_EXPERTS, src/core/types.rs:20
 
 struct GroupedMaps {
     CUtensorMap gu_codes, gu_scales_full, gu_scales_last, dn_codes, dn_scales_full, dn_scales_last;
-    CUtensorMap xg16, xg64, act16, act64;
+    CUtensorMap xg16, act16;
 };
 
 // Device-side description of the step, written by group_pairs_kernel.
@@ -81,7 +87,6 @@ struct GroupedArgs {
     const int* offsets;      // [E + 1] first sorted pair of the expert
     __half* act;             // [pairs][I], K order permuted
     __half* y;               // [pairs][H]
-    int sc_inner_gu, sc_inner_dn;   // bytes per row of one scale box (a row's scales are cut into boxes of at most 256 bytes)
     const Unit* units_gu;    // [n_active * tiles_gu]
     const Unit* units_dn;    // [n_active * tiles_dn]
     int tiles_gu, tiles_dn;
@@ -90,13 +95,23 @@ struct GroupedArgs {
     int* status;
 };
 
+// mbar_wait for the roles that wait long: a failed poll sleeps, so that the polling loop does not take issue slots from
+// the converting warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, unsigned parity, unsigned ns) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned it = 0; it < kSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        __nanosleep(ns);
+    }
+    return false;
+}
+
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -193,28 +208,28 @@ struct UnitWalk {
     }
 };
 
-template <bool DOWN>
-__device__ __forceinline__ int K_of(const GroupedArgs& a) { return DOWN ? a.I : a.H; }
-
 // DOWN = false: act[pair][perm(row)] = f16(silu(f16(Wg x)) * f16(Wu x)); DOWN = true: y[pair][row] = f16(Wd act).
+//
+// Warp roles: warp 0 issues the weights' TMA copies and the last warp the tokens'; warps 1..4 issue the MMAs (a quarter of a slab's K steps each, into a
+// partial accumulator of their own); warps 5..8 run the epilogue; warps 9..24 convert codes into the A operand.
+// Three rings decouple them: the weight ring (codes and scales of a slab; released as soon as the converting warps
+// hold the slab in registers), the token ring (the slab's B tile; released by the MMAs' completion) and the A
+// buffers in tensor memory (filled by the converting warps, released by the MMAs' completion).  A stage's life in
+// the weight ring is then one memory latency plus one conversion, whatever the MMAs' lag.
 template <bool DOWN>
 __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __grid_constant__ GroupedMaps maps, GroupedArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
-    unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-    unsigned char* scbuf = stages + kGrpStages * kGrpStageBytes;                               // two buffers of 128 rows of scales
-    float* exch = reinterpret_cast<float*>(scbuf + 2 * 128 * kGrpMaxScaleRow);                 // [64][kGrpMaxN + 1]
+    unsigned char* wring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* xring = wring + kGrpStages * kGrpRawBytes;
+    float* exch = reinterpret_cast<float*>(xring + kGrpXStages * kGrpXBytes);                  // [64][kGrpMaxN + 1]
     uint64_t* full = reinterpret_cast<uint64_t*>(exch + 64 * (kGrpMaxN + 1));
     uint64_t* empty = full + kGrpStages;
-    uint64_t* a_full = empty + kGrpStages;
-    uint64_t* a_empty = a_full + 2;
-    uint64_t* d_full = a_empty + 2;
+    uint64_t* xfull = empty + kGrpStages;
+    uint64_t* a_full = xfull + kGrpXStages;
+    uint64_t* a_empty = a_full + kGrpABufs;
+    uint64_t* d_full = a_empty + kGrpABufs;
     uint64_t* d_empty = d_full + 2;
-    uint64_t* sc_full = d_empty + 2;
-    uint64_t* sc_empty = sc_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_empty + 2);
-    const int scale_row = K_of<DOWN>(a) / 16;                       // bytes of scales per row
-    const int sc_inner = DOWN ? a.sc_inner_dn : a.sc_inner_gu;
-    const int sc_boxes = scale_row / sc_inner;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = DOWN ? a.I : a.H;
@@ -222,15 +237,18 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
     if (tid == 0) {
         for (int s = 0; s < kGrpStages; ++s) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, kGrpConvWarps + 1);       // the converting warps and the MMA's commit
+            mbar_init(empty + s, kGrpConvWarps / 2);
+        }
+        for (int s = 0; s < kGrpXStages; ++s) {
+            mbar_init(xfull + s, 1);
+        }
+        for (int s = 0; s < kGrpABufs; ++s) {
+            mbar_init(a_full + s, kGrpConvWarps / 2);
+            mbar_init(a_empty + s, kGrpMmaWarps);
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(a_full + s, kGrpConvWarps);
-            mbar_init(a_empty + s, 1);
-            mbar_init(d_full + s, 1);
+            mbar_init(d_full + s, kGrpMmaWarps);
             mbar_init(d_empty + s, 4);
-            mbar_init(sc_full + s, 1);
-            mbar_init(sc_empty + s, kGrpConvWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -245,100 +263,98 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
     pdl_wait();   // the work lists, the gathered tokens and (down) the intermediate are earlier kernels' outputs
     UnitWalk walk(DOWN ? a.units_dn : a.units_gu, a.work->n_active * (DOWN ? a.tiles_dn : a.tiles_gu));
 
-    // Every role walks the same sequence: units blockIdx.x, + gridDim.x, ...; per unit ceil(n_tok / 64) passes;
-    // per pass nslab slabs.  `it` counts slabs (ring stage it % 4, A buffer it & 1), `pc` passes (D buffer pc & 1).
+    // Every role walks the same sequence: units blockIdx.x, + gridDim.x, ...; per unit ceil(n_tok / 16) passes;
+    // per pass nslab slabs.  `it` counts slabs (weight stage it % 8, token stage it % 8, A buffer it % 3), `pc`
+    // passes (D buffer pc & 1).
     bool ok = true;
     if (warp == 0) {
-        // ── TMA producer ──
-        int it = 0, uc = 0;
+        // ── TMA producer of the weight ring ──
+        int it = 0;
         Unit t;
         while (ok && walk.next(t)) {
             const CUtensorMap* codes = DOWN ? &maps.dn_codes : &maps.gu_codes;
             const CUtensorMap* scales = DOWN ? (t.scales_last ? &maps.dn_scales_last : &maps.dn_scales_full)
                                              : (t.scales_last ? &maps.gu_scales_last : &maps.gu_scales_full);
-            {
-                // the tile's scales for all of K: buffer uc & 1; lanes 0 .. issue one box each
-                const int sbi = uc & 1;
-                if (uc >= 2) ok = mbar_wait(sc_empty + sbi, ((uc >> 1) - 1) & 1);
+            const int total = ((t.n_tok + kGrpMaxN - 1) / kGrpMaxN) * nslab;
+            // One instruction for all issuing lanes (each lane's copy is a different box): the same copies issued
+            // from one branch per lane cost four times as much of the warp's time.
+            //   gate/up: lane 0/1 codes of gate/up, lane 2/3 their scales;   down: lane 0 codes, lane 1 scales
+            const int nw = DOWN ? 2 : 4;
+            const bool is_scale = lane >= nw / 2;
+            const bool second = !DOWN && (lane & 1);   // the up matrix
+            const CUtensorMap* m = is_scale ? scales : codes;
+            const uint32_t dst_off = is_scale ? 16384 + (second ? 1024 : 0) : (second ? 8192 : 0);
+            const int c2 = second ? t.slot_b : t.slot_a;
+            for (int i = 0; i < total; ++i, ++it) {
+                const int s = i % nslab;
+                const int st = it % kGrpStages;
+                if (it >= kGrpStages) ok = mbar_wait_sleep(empty + st, ((it / kGrpStages) - 1) & 1, 100);
                 if (!ok) break;
-                unsigned char* dst = scbuf + (size_t)sbi * 128 * kGrpMaxScaleRow;
-                const int half_rows = DOWN ? 128 : 64;
-                if (lane == 0) mbar_expect_tx(sc_full + sbi, 128 * scale_row);
+                if (lane == 0) mbar_expect_tx(full + st, kGrpRawBytes);
                 __syncwarp();
-                const int nops = (DOWN ? 1 : 2) * sc_boxes;
-                for (int o = lane; o < nops; o += 32) {
-                    const int mat = o / sc_boxes, j = o - mat * sc_boxes;
-                    tma_load_3d(dst + (size_t)mat * half_rows * scale_row + (size_t)j * half_rows * sc_inner, scales, j * sc_inner, t.row0,
-                                mat ? t.slot_b : t.slot_a, sc_full + sbi);
-                }
+                if (lane < nw) tma_load_3d(wring + (size_t)st * kGrpRawBytes + dst_off, m, is_scale ? s * 16 : s * 128, t.row0, c2, full + st);
                 __syncwarp();
-                ++uc;
             }
+        }
+        if (!ok && lane == 0) flag(a.status, kStatusTimeout);
+        // drain: every issued copy must have landed before the CTA's shared memory goes away
+        if (lane == 0)
+            for (int k = max(0, it - kGrpStages); k < it; ++k)
+                if (!mbar_wait(full + (k % kGrpStages), (k / kGrpStages) & 1)) flag(a.status, kStatusTimeout);
+    } else if (warp == kGrpXWarp) {
+        // ── TMA producer of the token ring: one copy per slab (four K-major tiles of 64 columns) ──
+        int it = 0;
+        Unit t;
+        const CUtensorMap* xmap = DOWN ? &maps.act16 : &maps.xg16;
+        while (ok && walk.next(t)) {
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN) {
-                const int ntok = min(kGrpMaxN, t.n_tok - p0);
-                const bool small = ntok <= 16;
-                const CUtensorMap* xmap = DOWN ? (small ? &maps.act16 : &maps.act64) : (small ? &maps.xg16 : &maps.xg64);
-                const int nb = small ? 16 : kGrpMaxN;
                 for (int s = 0; s < nslab; ++s, ++it) {
-                    const int st = it % kGrpStages;
-                    if (it >= kGrpStages) ok = mbar_wait(empty + st, ((it / kGrpStages) - 1) & 1);
+                    const int xs = it % kGrpXStages;
+                    if (it >= kGrpXStages) ok = mbar_wait_sleep(a_empty + xs, ((it / kGrpXStages) - 1) & 1, 100);
                     if (!ok) break;
-                    // one lane arms the barrier, then eight lanes issue one copy each (a copy costs its issuing
-                    // thread a few hundred cycles: one lane alone would bound the ring)
-                    unsigned char* sb = stages + (size_t)st * kGrpStageBytes;
-                    if (lane == 0) mbar_expect_tx(full + st, kGrpRawBytes + nb * kGrpSlabK * 2);
-                    __syncwarp();
-                    if (DOWN) {
-                        if (lane == 0) tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
-                    } else {
-                        if (lane == 0) tma_load_3d(sb, codes, s * 128, t.row0, t.slot_a, full + st);
-                        if (lane == 1) tma_load_3d(sb + 8192, codes, s * 128, t.row0, t.slot_b, full + st);
+                    if (lane == 0) {
+                        mbar_expect_tx(xfull + xs, kGrpXBytes);
+                        tma_load_3d(xring + (size_t)xs * kGrpXBytes, xmap, 0, t.pair_off + p0, s * (kGrpSlabK / 64), xfull + xs);
                     }
-                    if (lane >= 4 && lane < 8)
-                        tma_load_2d(sb + kGrpRawBytes + (lane - 4) * nb * 128, xmap, s * kGrpSlabK + 64 * (lane - 4), t.pair_off + p0, full + st);
                     __syncwarp();
                 }
             }
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
-        // drain: every issued copy must have landed before the CTA's shared memory goes away
-        if (lane == 0) {
-            for (int k = max(0, it - kGrpStages); k < it; ++k)
-                if (!mbar_wait(full + (k % kGrpStages), (k / kGrpStages) & 1)) flag(a.status, kStatusTimeout);
-            for (int k = max(0, uc - 2); k < uc; ++k)
-                if (!mbar_wait(sc_full + (k & 1), (k >> 1) & 1)) flag(a.status, kStatusTimeout);
-        }
-    } else if (warp == 1) {
-        // ── MMA issuer ──
+        if (lane == 0)
+            for (int k = max(0, it - kGrpXStages); k < it; ++k)
+                if (!mbar_wait(xfull + (k % kGrpXStages), (k / kGrpXStages) & 1)) flag(a.status, kStatusTimeout);
+    } else if (warp <= kGrpMmaWarps) {
+        // ── MMA issuers: warp w takes the K steps 4 (w - 1) .. 4 (w - 1) + 3 of every slab and accumulates them into
+        // its own partial accumulator; the epilogue adds the four ──
+        const int mw = warp - 1;
         int it = 0, pc = 0;
         Unit t;
         while (ok && walk.next(t)) {
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
-                const int ntok = min(kGrpMaxN, t.n_tok - p0);
-                const int nb = ntok <= 16 ? 16 : kGrpMaxN;
-                const int n_mma = (ntok + 15) & ~15;
-                const uint32_t idesc = (1u << 4) | ((uint32_t)(n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(kGrpMaxN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
                 const int db = pc & 1;
-                if (pc >= 2) ok = mbar_wait(d_empty + db, ((pc >> 1) - 1) & 1);
+                if (pc >= 2) ok = mbar_wait_sleep(d_empty + db, ((pc >> 1) - 1) & 1, 100);
                 for (int s = 0; ok && s < nslab; ++s, ++it) {
-                    const int st = it % kGrpStages, ab = it & 1;
-                    ok = mbar_wait(full + st, (it / kGrpStages) & 1) && mbar_wait(a_full + ab, (it >> 1) & 1);
+                    const int xs = it % kGrpXStages, ab = it % kGrpABufs;
+                    ok = mbar_wait_sleep(xfull + xs, (it / kGrpXStages) & 1, 20) && mbar_wait_sleep(a_full + ab, (it / kGrpABufs) & 1, 20);
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
-                        const uint32_t xs = smem_u32(stages + (size_t)st * kGrpStageBytes + kGrpRawBytes);
+                        const uint32_t xaddr = smem_u32(xring + (size_t)xs * kGrpXBytes);
 #pragma unroll
-                        for (int k = 0; k < kGrpSlabK / 16; ++k) {
-                            const uint32_t baddr = xs + (k >> 2) * nb * 128 + (k & 3) * 32;
+                        for (int kk = 0; kk < kGrpSlabK / 16 / kGrpMmaWarps; ++kk) {
+                            const int k = mw * (kGrpSlabK / 16 / kGrpMmaWarps) + kk;
+                            const uint32_t baddr = xaddr + (k >> 2) * kGrpMaxN * 128 + (k & 3) * 32;
                             const uint64_t bdesc = (uint64_t)((baddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
                                                    ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-                            const uint32_t acc = (s > 0 || k > 0) ? 1u : 0u;
+                            const uint32_t acc = (s > 0 || kk > 0) ? 1u : 0u;
                             asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                                         ::"r"(tmem + kGrpDCol0 + db * kGrpMaxN), "r"(tmem + ab * kGrpACols + 8 * k), "l"(bdesc), "r"(idesc), "r"(acc)
+                                         ::"r"(tmem + kGrpDCol0 + (db * kGrpMmaWarps + mw) * kGrpMaxN), "r"(tmem + ab * kGrpACols + 8 * k), "l"(bdesc),
+                                         "r"(idesc), "r"(acc)
                                          : "memory");
                         }
                         umma_commit(a_empty + ab);
-                        umma_commit(empty + st);
                         if (s == nslab - 1) umma_commit(d_full + db);
                     }
                     __syncwarp();
@@ -347,62 +363,68 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
     } else if (warp >= kGrpFirstConvWarp) {
-        // ── converting warps: row m = 32 (warp % 4) + lane of the A tile, K quarter (warp - 6) / 4 of the slab ──
-        const int q = warp & 3, kq = (warp - kGrpFirstConvWarp) >> 2;
+        // ── converting warps: two teams of eight take alternate slabs, so that one team's waits (for the copy, for
+        // the A buffer, for its stores into tensor memory) overlap the other team's arithmetic.  Within a team: row
+        // m = 32 (warp % 4) + lane of the A tile, K half (128 columns) of the slab ──
+        const int cw = warp - kGrpFirstConvWarp;
+        const int q = warp & 3, team = cw >> 3, kh = (cw >> 2) & 1;
         const int m = 32 * q + lane;
         // where row m's codes and scales sit in a stage
         const int src_row = DOWN ? m : (m & 63);
         const uint32_t code_off = (DOWN ? 0u : (m >= 64 ? 8192u : 0u)) + (uint32_t)src_row * 128u;
-        const int half_rows = DOWN ? 128 : 64;
-        // row m's scales in a scale buffer: matrix block, then box j of sc_inner bytes per row
-        const uint32_t sc_row_off = (DOWN ? 0u : (m >= 64 ? (uint32_t)(64 * scale_row) : 0u)) + (uint32_t)src_row * (uint32_t)sc_inner;
+        const uint32_t scale_off = 16384u + (DOWN ? 0u : (m >= 64 ? 1024u : 0u)) + (uint32_t)src_row * 16u + (uint32_t)kh * 8u;
         const int first_row = DOWN ? 32 * q : 32 * (q & 1);   // first row (of the matrix half) among this warp's 32
         const uint32_t sw = (uint32_t)(src_row & 7);
-        int it = 0, uc = 0;
+        int it = 0;
         Unit t;
         while (ok && walk.next(t)) {
             const int total = ((t.n_tok + kGrpMaxN - 1) / kGrpMaxN) * nslab;
-            const int sbi = uc & 1;
-            ok = mbar_wait(sc_full + sbi, (uc >> 1) & 1);
-            const uint32_t sc_base = smem_u32(scbuf + (size_t)sbi * 128 * kGrpMaxScaleRow) + sc_row_off;
+            // a warp whose 32 rows all lie beyond the tile's last row has nothing to convert: its lanes of the
+            // accumulator are never read
+            const bool work = first_row < t.rows;
             for (int i = 0; ok && i < total; ++i, ++it) {
-                const int s = i % nslab;
-                const int st = it % kGrpStages, ab = it & 1;
+                if ((it & 1) != team) continue;
+                const int st = it % kGrpStages, ab = it % kGrpABufs;
                 ok = mbar_wait(full + st, (it / kGrpStages) & 1);
-                if (ok && it >= 2) ok = mbar_wait(a_empty + ab, ((it >> 1) - 1) & 1);
+                if (!ok) break;
+                const uint32_t sb = smem_u32(wring + (size_t)st * kGrpRawBytes);
+                const uint32_t cb = sb + code_off;
+                const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + ab * kGrpACols + kh * 64;
+                uint32_t h0[16], h1[16];
+                uint32_t sc0 = 0, sc1 = 0;   // four group scales
+                if (work) {
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(sc0), "=r"(sc1) : "r"(sb + scale_off));
+                    const uint4 c0 = lds128(cb + (((uint32_t)(4 * kh) ^ sw) * 16u));
+                    const uint4 c1 = lds128(cb + (((uint32_t)(4 * kh + 1) ^ sw) * 16u));
+                    dequant_chunk(c0, __byte_perm(sc0, 0, 0x1010), h0);
+                    dequant_chunk(c1, __byte_perm(sc0, 0, 0x3232), h1);
+                }
+                if (it >= kGrpABufs) ok = mbar_wait(a_empty + ab, ((it / kGrpABufs) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                // a warp whose 32 rows all lie beyond the tile's last row has nothing to convert: its lanes of the
-                // accumulator are never read
-                if (first_row < t.rows) {
-                    const uint32_t sb = smem_u32(stages + (size_t)st * kGrpStageBytes);
-                    uint32_t sc;   // two group scales: bytes 16 s + 4 kq of the row's scales
-                    const int sbyte = 16 * s + 4 * kq, sj = sbyte / sc_inner;
-                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc) : "r"(sc_base + (uint32_t)(sj * half_rows * sc_inner + (sbyte - sj * sc_inner))));
-                    const uint32_t sc2[2] = {__byte_perm(sc, 0, 0x1010), __byte_perm(sc, 0, 0x3232)};
-                    const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + ab * kGrpACols + kq * 32;
-                    const uint4 codes0 = lds128(sb + code_off + (((uint32_t)(2 * kq) ^ sw) * 16u));
-                    const uint4 codes1 = lds128(sb + code_off + (((uint32_t)(2 * kq + 1) ^ sw) * 16u));
-                    uint32_t h[16];
-                    dequant_chunk(codes0, sc2[0], h);
-                    tmem_st16(taddr, h);
-                    dequant_chunk(codes1, sc2[1], h);
-                    tmem_st16(taddr + 16, h);
+                uint4 c2 = make_uint4(0, 0, 0, 0), c3 = c2;
+                if (work) {
+                    tmem_st16(taddr, h0);
+                    tmem_st16(taddr + 16, h1);
+                    c2 = lds128(cb + (((uint32_t)(4 * kh + 2) ^ sw) * 16u));
+                    c3 = lds128(cb + (((uint32_t)(4 * kh + 3) ^ sw) * 16u));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + st);   // the slab is in registers: the stage may be refilled
+                if (work) {
+                    dequant_chunk(c2, __byte_perm(sc1, 0, 0x1010), h0);
+                    dequant_chunk(c3, __byte_perm(sc1, 0, 0x3232), h1);
+                    tmem_st16(taddr + 32, h0);
+                    tmem_st16(taddr + 48, h1);
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(empty + st);
-                    mbar_arrive(a_full + ab);
-                }
+                if (lane == 0) mbar_arrive(a_full + ab);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sc_empty + sbi);
-            ++uc;
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
-    } else if (warp >= 2) {
+    } else if (warp >= kGrpFirstEpiWarp) {
         // ── epilogue warps: TMEM lanes 32 (warp % 4) .. + 31 ──
         const int q = warp & 3;
         const int m = 32 * q + lane;
@@ -412,45 +434,56 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
                 const int ntok = min(kGrpMaxN, t.n_tok - p0);
                 const int db = pc & 1;
-                ok = mbar_wait(d_full + db, (pc >> 1) & 1);
+                ok = mbar_wait_sleep(d_full + db, (pc >> 1) & 1, 500);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + kGrpDCol0 + db * kGrpMaxN;
-                for (int n0 = 0; n0 < ntok; n0 += 16) {
-                    uint32_t d[16];
-                    tmem_ld16(taddr + n0, d);
+                const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + kGrpDCol0 + db * kGrpMmaWarps * kGrpMaxN;
+                uint32_t d[16];
+                {
+                    // the four issuers' partial sums, added pairwise: (p0 + p1) + (p2 + p3)
+                    uint32_t p[16], r[16];
+                    tmem_ld16(taddr, d);
+                    tmem_ld16(taddr + kGrpMaxN, p);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (DOWN) {
-                        if (m < t.rows) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (n0 + j < ntok)
-                                    a.y[(size_t)(t.pair_off + p0 + n0 + j) * a.H + t.mrow0 + m] = __float2half_rn(__uint_as_float(d[j]));
-                        }
-                    } else {
-                        // the up half hands its values to the gate half of the same rows
-                        if (m >= 64) {
+                    for (int j = 0; j < 16; ++j) d[j] = __float_as_uint(__uint_as_float(d[j]) + __uint_as_float(p[j]));
+                    tmem_ld16(taddr + 2 * kGrpMaxN, r);
+                    tmem_ld16(taddr + 3 * kGrpMaxN, p);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) exch[(m - 64) * (kGrpMaxN + 1) + n0 + j] = __uint_as_float(d[j]);
-                        }
-                        asm volatile("bar.sync 3, 128;" ::: "memory");
-                        if (m < 64 && m < t.rows) {
-                            const int col = perm8(t.mrow0 + m);
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                if (n0 + j < ntok) {
-                                    const float g16 = __half2float(__float2half_rn(__uint_as_float(d[j])));
-                                    const float u16 = __half2float(__float2half_rn(exch[m * (kGrpMaxN + 1) + n0 + j]));
-                                    a.act[(size_t)(t.pair_off + p0 + n0 + j) * a.I + col] = __float2half_rn(silu_mul_f32(g16, u16));
-                                }
-                            }
-                        }
-                        asm volatile("bar.sync 3, 128;" ::: "memory");
-                    }
+                    for (int j = 0; j < 16; ++j)
+                        d[j] = __float_as_uint(__uint_as_float(d[j]) + (__uint_as_float(r[j]) + __uint_as_float(p[j])));
                 }
+                // the accumulators are in registers: the MMAs of the pass after next may overwrite them
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(d_empty + db);
+                if (DOWN) {
+                    if (m < t.rows) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < ntok) a.y[(size_t)(t.pair_off + p0 + j) * a.H + t.mrow0 + m] = __float2half_rn(__uint_as_float(d[j]));
+                    }
+                } else {
+                    // the up half hands its values to the gate half of the same rows
+                    if (m >= 64) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) exch[(m - 64) * (kGrpMaxN + 1) + j] = __uint_as_float(d[j]);
+                    }
+                    asm volatile("bar.sync 3, 128;" ::: "memory");
+                    if (m < 64 && m < t.rows) {
+                        const int col = perm8(t.mrow0 + m);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (j < ntok) {
+                                const float g16 = __half2float(__float2half_rn(__uint_as_float(d[j])));
+                                const float u16 = __half2float(__float2half_rn(exch[m * (kGrpMaxN + 1) + j]));
+                                a.act[(size_t)(t.pair_off + p0 + j) * a.I + col] = __float2half_rn(silu_mul_f32(g16, u16));
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 3, 128;" ::: "memory");
+                }
             }
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
@@ -484,13 +517,16 @@ struct GroupPairsArgs {
 };
 
 __global__ void __launch_bounds__(1024) group_pairs_kernel(GroupPairsArgs g) {
-    __shared__ int cnt[kRouterMaxExpertsGrouped + 1];
+    constexpr int kWords = kGrpMaxTokens / 32;
+    __shared__ __align__(16) int cnt[kRouterMaxExpertsGrouped + 4];
     __shared__ int off[kRouterMaxExpertsGrouped + 2];
+    __shared__ unsigned mask[kRouterMaxExpertsGrouped][kWords];   // bit t of expert e: token t chose e
+    __shared__ int warp_total[32];
     __shared__ int nact;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NE = g.E + 1;
     pdl_wait();
-    for (int e = tid; e < NE; e += blockDim.x) cnt[e] = 0;
+    for (int i = tid; i < g.E * kWords; i += blockDim.x) (&mask[0][0])[i] = 0;
     if (tid == 0) nact = 0;
     __syncthreads();
     const int total = g.T * g.top_k;
@@ -498,53 +534,73 @@ __global__ void __launch_bounds__(1024) group_pairs_kernel(GroupPairsArgs g) {
         const int t = i / g.top_k, s = i - t * g.top_k;
         const unsigned e = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(g.ids) + (size_t)t * g.ids_stride)[s];
         if (e >= (unsigned)g.E) flag(g.status, kStatusBadExpert);
-        else if ((int)e >= g.expert_lo && (int)e < g.expert_hi) atomicAdd(&cnt[e], 1);
-        g.pos[t * (g.top_k + 1) + s] = -1;   // (overwritten below for the pairs that are taken)
+        else if ((int)e >= g.expert_lo && (int)e < g.expert_hi) atomicOr(&mask[e][t >> 5], 1u << (t & 31));
     }
-    if (tid == 0) cnt[g.E] = g.has_shared ? g.T : 0;
     __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int e = 0; e < NE; ++e) {
-            off[e] = run;
-            run += cnt[e];
+    // counts, then their exclusive prefix sum (one value per thread: warp scans, then a scan of the warps' totals)
+    int c = 0;
+    if (tid < g.E) {
+#pragma unroll
+        for (int w = 0; w < kWords; ++w) c += __popc(mask[tid][w]);
+    } else if (tid == g.E) {
+        c = g.has_shared ? g.T : 0;
+    }
+    for (int e = tid; e < kRouterMaxExpertsGrouped + 4; e += blockDim.x) cnt[e] = e == tid ? c : 0;
+    int incl = c;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += v;
+    }
+    if (lane == 31) warp_total[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int v = warp_total[lane], iv = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, iv, d);
+            if (lane >= d) iv += u;
         }
-        off[NE] = run;
-        g.work->n_pairs = run;
+        warp_total[lane] = iv - v;
+        if (lane == 31) g.work->n_pairs = iv;
     }
     __syncthreads();
-    for (int e = tid; e < NE; e += blockDim.x) {
-        g.counts[e] = cnt[e];
-        g.offsets[e] = off[e];
-        if (cnt[e] > 0) {
+    if (tid <= NE) off[tid] = warp_total[warp] + incl - c;   // (off[NE] = the total: the threads past NE hold zero counts)
+    __syncthreads();
+    if (tid < NE) {
+        g.counts[tid] = c;
+        g.offsets[tid] = off[tid];
+        if (c > 0) {
+            // position among the active experts, most tokens first (ties: lower id)
             int rank = 0;
-            for (int o = 0; o < NE; ++o)
-                if (cnt[o] > cnt[e] || (cnt[o] == cnt[e] && o < e && cnt[o] > 0)) ++rank;
-            g.active[rank] = e;
+            const int4* c4 = reinterpret_cast<const int4*>(cnt);
+            for (int o4 = 0; o4 < (NE + 3) / 4; ++o4) {
+                const int4 v = c4[o4];
+                const int o = 4 * o4;
+                rank += (v.x > c || (v.x == c && o < tid)) + (v.y > c || (v.y == c && o + 1 < tid)) + (v.z > c || (v.z == c && o + 2 < tid)) +
+                        (v.w > c || (v.w == c && o + 3 < tid));
+            }
+            g.active[rank] = tid;
             atomicAdd(&nact, 1);
         }
     }
-    // stable placement: thread e walks the pairs in token order (T * top_k <= 2048 entries, read from L1/L2)
-    for (int e = tid; e < g.E; e += blockDim.x) {
-        if (cnt[e] == 0) continue;
-        int p = off[e];
-        for (int t = 0; t < g.T; ++t) {
-            const unsigned short* row = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(g.ids) + (size_t)t * g.ids_stride);
-            for (int s = 0; s < g.top_k; ++s)
-                if (row[s] == e) {
-                    g.pair_token[p] = (unsigned short)t;
-                    g.pos[t * (g.top_k + 1) + s] = p;
-                    ++p;
-                }
+    // placement, stable in token order: a pair's position is its expert's offset plus the number of earlier tokens
+    // that chose the expert
+    for (int i = tid; i < total; i += blockDim.x) {
+        const int t = i / g.top_k, s = i - t * g.top_k;
+        const unsigned e = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(g.ids) + (size_t)t * g.ids_stride)[s];
+        int p = -1;   // a pair of another rank's expert
+        if (e < (unsigned)g.E && (int)e >= g.expert_lo && (int)e < g.expert_hi) {
+            p = off[e] + __popc(mask[e][t >> 5] & ((1u << (t & 31)) - 1u));
+            for (int w = 0; w < (t >> 5); ++w) p += __popc(mask[e][w]);
+            g.pair_token[p] = (unsigned short)t;
         }
+        g.pos[t * (g.top_k + 1) + s] = p;
     }
-    if (g.has_shared)
-        for (int t = tid; t < g.T; t += blockDim.x) {
-            g.pair_token[off[g.E] + t] = (unsigned short)t;
-            g.pos[t * (g.top_k + 1) + g.top_k] = off[g.E] + t;
-        }
-    else
-        for (int t = tid; t < g.T; t += blockDim.x) g.pos[t * (g.top_k + 1) + g.top_k] = -1;
+    for (int t = tid; t < g.T; t += blockDim.x) {
+        if (g.has_shared) g.pair_token[off[g.E] + t] = (unsigned short)t;
+        g.pos[t * (g.top_k + 1) + g.top_k] = g.has_shared ? off[g.E] + t : -1;
+    }
     __syncthreads();
     if (tid == 0) g.work->n_active = nact;
     pdl_trigger();
@@ -630,23 +686,31 @@ __global__ void __launch_bounds__(256) gather_tokens_kernel(const void* x, int x
 __global__ void __launch_bounds__(256) combine_pairs_kernel(const __half* y, const int* pos, const float* weights, int w_stride,
                                                             int T, int top_k, int has_shared, float shared_weight, float* out,
                                                             int out_stride, int out_accumulate, int H) {
+    __shared__ int sp[17];
+    __shared__ float sw[17];
     pdl_wait();
     const int t = blockIdx.y;
-    const float* wrow = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(weights) + (size_t)t * w_stride);
-    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) * 2; r < H; r += gridDim.x * blockDim.x * 2) {
+    if ((int)threadIdx.x <= top_k) {
+        const int s = threadIdx.x;
+        const float* wrow = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(weights) + (size_t)t * w_stride);
+        sp[s] = (s < top_k || has_shared) ? pos[t * (top_k + 1) + s] : -1;
+        sw[s] = s < top_k ? wrow[s] : shared_weight;
+    }
+    __syncthreads();
+    const int r = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (r < H) {
+        // all loads first, then the sum in plan order (the shared expert last)
+        __half2 v[17];
+#pragma unroll
+        for (int s = 0; s < 17; ++s)
+            if (s <= top_k && sp[s] >= 0) v[s] = *reinterpret_cast<const __half2*>(y + (size_t)sp[s] * H + r);
         float o0 = 0.f, o1 = 0.f;
-        for (int s = 0; s < top_k; ++s) {
-            const int p = pos[t * (top_k + 1) + s];
-            if (p < 0) continue;   // a pair of another rank's expert
-            const __half2 v = *reinterpret_cast<const __half2*>(y + (size_t)p * H + r);
-            o0 = fmaf(wrow[s], __low2float(v), o0);
-            o1 = fmaf(wrow[s], __high2float(v), o1);
-        }
-        if (has_shared) {
-            const __half2 v = *reinterpret_cast<const __half2*>(y + (size_t)pos[t * (top_k + 1) + top_k] * H + r);
-            o0 = fmaf(shared_weight, __low2float(v), o0);
-            o1 = fmaf(shared_weight, __high2float(v), o1);
-        }
+#pragma unroll
+        for (int s = 0; s < 17; ++s)
+            if (s <= top_k && sp[s] >= 0) {
+                o0 = fmaf(sw[s], __low2float(v[s]), o0);
+                o1 = fmaf(sw[s], __high2float(v[s]), o1);
+            }
         float* o = out + (size_t)t * out_stride + r;
         if (out_accumulate) {
             o[0] += o0;
@@ -679,7 +743,6 @@ struct GroupedHandle {
     __half *xg, *act, *y;
     Unit *units_gu, *units_dn;
     int tiles_gu, tiles_dn, tiles_per_page_gu, tiles_per_page_dn;
-    int sc_inner_gu, sc_inner_dn;
     int max_pairs;
 };
 
@@ -709,25 +772,20 @@ int make_pool_map(CUtensorMap* m, void* base, size_t row_bytes, int rows, size_t
     return r == CUDA_SUCCESS ? 0 : VIB3_ERR_STATE;
 }
 
-// 2-D fp16 map [rows][cols], box 64 columns x box_rows, 128-byte swizzle (the K-major operand layout).
+// fp16 rows [rows][cols] seen as x = column within a block of 64, y = row, z = block of 64 columns; a box is 64 columns x
+// box_rows x 4 blocks, 128-byte swizzle: one copy brings a slab of 256 columns as four K-major operand tiles
+// [box_rows][128 bytes].
 int make_rows_map(CUtensorMap* m, void* base, int cols, int rows, int box_rows) {
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    const cuuint32_t es[2] = {1, 1};
-    CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)(kGrpSlabK / 64)};
+    const cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : VIB3_ERR_STATE;
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
-// A row's scales (row_bytes) are fetched as equal boxes of at most 256 bytes, each a multiple of 16 bytes; 0: impossible.
-int scale_box_bytes(int row_bytes) {
-    for (int n = (row_bytes + 255) / 256; n <= row_bytes / 16; ++n)
-        if (row_bytes % n == 0 && (row_bytes / n) % 16 == 0) return row_bytes / n;
-    return 0;
-}
 
 struct Carve {
     size_t work, active, counts, offsets, pos, pair_token, units_gu, units_dn, xg, act, y, total;
@@ -777,8 +835,8 @@ int launch_pdl(K kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, A
     return (int)cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-constexpr size_t kGrpSmem = 1024 + (size_t)kGrpStages * kGrpStageBytes + 2 * 128 * kGrpMaxScaleRow + 64 * (kGrpMaxN + 1) * sizeof(float) +
-                            40 * sizeof(uint64_t);
+constexpr size_t kGrpSmem = 1024 + (size_t)kGrpStages * kGrpRawBytes + (size_t)kGrpXStages * kGrpXBytes +
+                            64 * (kGrpMaxN + 1) * sizeof(float) + 48 * sizeof(uint64_t);
 
 }  // namespace
 
@@ -827,25 +885,17 @@ extern "C" int vib3_moe_grouped_prewarm(void* pool_base, size_t capacity_pages, 
     const size_t dn_code_row = expert_hidden_dim / 2, dn_scale_row = expert_hidden_dim / 16;
     int e = 0;
     e |= make_pool_map(&h->maps.gu_codes, pb, gu_code_row, rows_per_page_gate_up, capacity_pages, 128, 64, true);
-    h->sc_inner_gu = scale_box_bytes((int)gu_scale_row);
-    h->sc_inner_dn = scale_box_bytes((int)dn_scale_row);
-    if (!h->sc_inner_gu || !h->sc_inner_dn || gu_scale_row > (size_t)kGrpMaxScaleRow || dn_scale_row > (size_t)kGrpMaxScaleRow) {
-        delete h;
-        return VIB3_ERR_UNSUPPORTED;
-    }
     e |= make_pool_map(&h->maps.gu_scales_full, pb + (size_t)rows_per_page_gate_up * gu_code_row, gu_scale_row, rows_per_page_gate_up,
-                       capacity_pages, h->sc_inner_gu, 64, false);
+                       capacity_pages, 16, 64, false);
     e |= make_pool_map(&h->maps.gu_scales_last, pb + (size_t)last_page_rows_gate_up * gu_code_row, gu_scale_row, last_page_rows_gate_up,
-                       capacity_pages, h->sc_inner_gu, 64, false);
+                       capacity_pages, 16, 64, false);
     e |= make_pool_map(&h->maps.dn_codes, pb, dn_code_row, rows_per_page_down, capacity_pages, 128, 128, true);
     e |= make_pool_map(&h->maps.dn_scales_full, pb + (size_t)rows_per_page_down * dn_code_row, dn_scale_row, rows_per_page_down,
-                       capacity_pages, h->sc_inner_dn, 128, false);
+                       capacity_pages, 16, 128, false);
     e |= make_pool_map(&h->maps.dn_scales_last, pb + (size_t)last_page_rows_down * dn_code_row, dn_scale_row, last_page_rows_down,
-                       capacity_pages, h->sc_inner_dn, 128, false);
+                       capacity_pages, 16, 128, false);
     e |= make_rows_map(&h->maps.xg16, h->xg, hidden_dim, h->max_pairs, 16);
-    e |= make_rows_map(&h->maps.xg64, h->xg, hidden_dim, h->max_pairs, kGrpMaxN);
     e |= make_rows_map(&h->maps.act16, h->act, expert_hidden_dim, h->max_pairs, 16);
-    e |= make_rows_map(&h->maps.act64, h->act, expert_hidden_dim, h->max_pairs, kGrpMaxN);
     if (e) {
         delete h;
         return VIB3_ERR_STATE;
@@ -902,7 +952,6 @@ extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_d
 
     GroupedArgs a;
     a.units_gu = h->units_gu; a.units_dn = h->units_dn; a.tiles_gu = h->tiles_gu; a.tiles_dn = h->tiles_dn;
-    a.sc_inner_gu = h->sc_inner_gu; a.sc_inner_dn = h->sc_inner_dn;
     a.page_table = (const PageEntry*)page_table; a.shared_pages = (const PageEntry*)shared_pages; a.pool_base = h->pool_base;
     a.work = h->work; a.active = h->active; a.counts = h->counts; a.offsets = h->offsets; a.act = h->act; a.y = h->y;
     a.E = h->E; a.P = pages_per_segment; a.H = h->H; a.I = h->I; a.rpp_gu = h->rpp_gu; a.rpp_dn = h->rpp_dn; a.status = status;
@@ -910,6 +959,6 @@ extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_d
     if (err) return err;
     err = launch_pdl(moe_grouped_kernel<true>, dim3(sm_count()), kGrpThreads, kGrpSmem, st, h->maps, a);
     if (err) return err;
-    return launch_pdl(combine_pairs_kernel, dim3(4, n_tokens), 256, 0, st, (const __half*)h->y, (const int*)h->pos, weights,
+    return launch_pdl(combine_pairs_kernel, dim3((h->H / 2 + 255) / 256, n_tokens), 256, 0, st, (const __half*)h->y, (const int*)h->pos, weights,
                       weights_stride_bytes, n_tokens, h->top_k, has_shared, shared_weight, out, out_stride, out_accumulate, h->H);
 }
