@@ -82,25 +82,28 @@ int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_
 
 /* ── Entry points added for the fused, paged path ───────────────────────────────────────── */
 
-/* Single-launch router (no counterpart signature in the reference; semantics of
+/* Router in one call, results left on the device (no counterpart signature in the reference; semantics of
  * run_router_with_scoring_and_bias, src/compute/kernels.rs:2307-2440).  x_dtype VIB3_X_*,
  * w_dtype VIB3_W_*.  bias: added to the score for selection only (the reference's correction bias);
  * logit_offset: added to the logit before scoring.  scores_buf: 3 * num_experts floats; the first
  * num_experts receive the logits, the rest is scratch.
  * exact_order != 0 makes the selected indices equal to those of the reference's CPU router
  * (sequential fp32 summation) even for near-tied experts.  workspace: four uint32, zero before
- * the first call; [0] is left zero by every call, [1] counts near-tie recomputations, [2] and [3] are
- * used by vib3_launch_moe_layer_routed_int4_paged; calls sharing a workspace must not overlap. */
+ * the first call; [0] is left zero by every call, [1] counts near-tie recomputations, [2] is used by
+ * vib3_launch_moe_layer_routed_int4_paged, [3] is set if a bounded wait in the kernels ran out; calls
+ * sharing a workspace must not overlap.  The launches carry the programmatic-dependent-launch attribute:
+ * the router's weights are requested while the preceding kernel of the stream is still finishing. */
 int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void* W, int w_dtype, float* scores_buf,
                                const float* bias_or_null, const float* logit_offset_or_null,
                                unsigned short* out_ids, float* out_weights,
                                int hidden_dim, int num_experts, int top_k, int scoring_mode, float scaling_factor,
                                int normalize, int exact_order, unsigned int* workspace, void* stream);
 
-/* vib3_launch_router_topk_ex for n_tokens tokens in one launch (no counterpart in the reference, whose
+/* vib3_launch_router_topk_ex for n_tokens tokens in one call (no counterpart in the reference, whose
  * prefill routes token by token): token t reads x + t * x_stride_bytes and writes scores_buf + t *
  * scores_stride (floats, >= 3 * num_experts), out_ids + t * ids_stride, out_weights + t * weights_stride
- * (entries, >= top_k); workspace: 4 * n_tokens uint32, zero before the first call. */
+ * (entries, >= top_k); workspace: 4 * n_tokens uint32, zero before the first call (word 3 of a token's four is
+ * set if a bounded wait in the kernels ran out).  The router's weights are read once per call. */
 int vib3_launch_router_topk_batch(const void* x, int x_dtype, int x_stride_bytes, int n_tokens, const void* W,
                                   int w_dtype, float* scores_buf, int scores_stride, const float* bias_or_null,
                                   const float* logit_offset_or_null, unsigned short* out_ids, int ids_stride,

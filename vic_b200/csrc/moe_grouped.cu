@@ -727,6 +727,14 @@ __global__ void __launch_bounds__(256) combine_pairs_kernel(const __half* y, con
 
 using namespace vib3;
 
+extern "C" int vib3_launch_moe_layer_int4_paged(const void* x, int x_dtype, const void* page_table, int num_experts,
+                                                const void* shared_pages, const unsigned short* expert_ids,
+                                                const float* expert_weights, int top_k, float shared_weight,
+                                                void* act_scratch, float* out, int out_accumulate, int hidden_dim,
+                                                int expert_hidden_dim, int pages_per_segment,
+                                                int rows_per_page_gate_up, int rows_per_page_down, int group_size,
+                                                int* status, void* stream);
+
 // ── host side ────────────────────────────────────────────────────────────────────────────────
 
 namespace {
@@ -929,6 +937,14 @@ extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_d
         return VIB3_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
     const int has_shared = shared_pages ? 1 : 0;
+    // One token with all of its experts here: the batch-1 kernels stream the nine experts faster than tensor-core
+    // tiles that are fifteen sixteenths padding.
+    if (n_tokens == 1 && expert_lo == 0 && expert_hi == h->E) {
+        const int e = vib3_launch_moe_layer_int4_paged(x, x_dtype, page_table, h->E, shared_pages, ids, weights, h->top_k, shared_weight,
+                                                       h->act, out, out_accumulate, h->H, h->I, pages_per_segment, h->rpp_gu, h->rpp_dn,
+                                                       kGroupSize, status, stream);
+        if (e != VIB3_ERR_UNSUPPORTED && e != VIB3_ERR_ALIGN) return e;
+    }
 
     GroupPairsArgs g;
     g.ids = ids; g.ids_stride = ids_stride_bytes; g.T = n_tokens; g.top_k = h->top_k; g.E = h->E; g.has_shared = has_shared;

@@ -6,15 +6,21 @@
 //   vib3_launch_router_topk       cuda/src/kernels.cu:4075  (GEMV + top-k, results stay on device)
 // and one extended launcher, vib3_launch_router_topk_ex, that also accepts fp32 router weights
 // and fp16/bf16 activations, any expert count up to 512 (the reference's bitonic kernel needs a
-// power of two, kernels.cu:3899), and finishes in a single launch.
+// power of two, kernels.cu:3899), and leaves ids and weights on the device in one call.
 //
 // Summation order of the logits: exactly the reference CUDA kernel's (kernels.cu:665-707) — 128
 // chains per expert, chain t adds d = t, t+128, ... with fused multiply-add, a shfl_down tree
 // per group of 32 chains, then (s0+s2)+(s1+s3) — so logits are bit-identical to the reference's on
 // a GPU.  The work split is different: ONE warp per expert row, lane l owns the four chains
-// 4l .. 4l+3, so that a lane's loads are 16 bytes wide (fp32 weights) and a warp's load covers 512
-// contiguous bytes; a lane keeps 28 such loads in flight, and a CTA is three warps, so that the
-// 384-expert router is one wave of 128 small CTAs that fit beside the expert kernel on an SM.
+// 4l .. 4l+3, so that a lane's accesses are 16 bytes wide (fp32 weights) and a warp's cover 512
+// contiguous bytes.  Two implementations of that split:
+//   * rows-resident (the usual case: H a multiple of 8, aligned operands): a CTA brings three
+//     expert rows into shared memory with one bulk copy each — requested before the kernel waits
+//     for the producer of the token, so the weights travel under the previous kernel's tail — and
+//     forms the logits of every token of the launch from there; a second launch (one CTA per token)
+//     scores and selects.  The weights cross the memory system once per launch, not once per token.
+//   * direct (any H, any alignment): rows read straight from global memory, 28 loads of a lane in
+//     flight; the CTA that finishes last scores and selects.
 //
 // Scoring and selection follow the reference's CPU router (src/compute/kernels.rs:2364-2437),
 // which is the only well-defined reference for 384 experts: softmax over the selected k only;
@@ -28,6 +34,7 @@
 // difference, the near-tied experts' logits are recomputed with one sequential multiply-then-add
 // chain per expert (the CPU order) before the final selection (router_core.cuh).  This costs about
 // 20 microseconds and happens for a few percent of tokens.
+#include "pipe_common.cuh"
 #include "router_core.cuh"
 
 namespace vib3 {
@@ -39,7 +46,7 @@ constexpr int kGroupLoads = 7;          // ... and 16-byte loads per group
 constexpr int kInFlight = kLoadGroups * kGroupLoads;  // 28: half a 7168-wide fp32 row
 
 // GEMV: one warp per expert row, kRouterWarps rows per CTA.  When `a.counter` is set, the CTA that
-// finishes last also does the scoring and selection (single launch).
+// finishes last also does the scoring and selection (one launch).  The direct path; see the rows-resident one below.
 // XD >= 0: the vector path — H a multiple of 8 (fp32 x: of 4) and at most kRouterXMax, x and the rows of W
 // 16-byte (fp16 W: 8-byte) aligned.  A lane first requests kInFlight weight items; the CTA then copies the
 // activation vector as it is into shared memory with asynchronous 16-byte copies (no registers, nothing
@@ -162,8 +169,144 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(RouterArgs 
     router_finish(a, sm, ring, threadIdx.x, kRouterThreads, false, true, nullptr, nullptr);
 }
 
+// ── rows-resident router ─────────────────────────────────────────────────────────────────────
+// The vector path of the router as two launches that follow one another by programmatic dependent launch.
+//
+// router_rows_kernel: a CTA takes kRowsPerCta expert rows.  Its first thread requests the rows with one bulk
+// copy each into shared memory BEFORE the kernel waits for its predecessor (the router's weights are constants:
+// the copies run under the tail of the kernel that produces the token), so every byte of a row is in flight at
+// once and a logit costs one memory round trip.  The tokens' vectors are staged with asynchronous 16-byte
+// copies, tok_chunk tokens at a time in two buffers; warp (row, slot) forms the logit of its row for token
+// slot of the chunk, in the reference kernel's order (row_logit_smem).  With several tokens the rows stay in
+// shared memory: the router's weights cross the memory system once per launch, not once per token.
+// The kernel needs most of an SM's shared memory, so it does not share an SM with the expert kernel; it is
+// short, and the expert kernel's CTAs start as its CTAs leave.
+//
+// router_select_kernel: one CTA per token scores, selects and writes ids and weights (router_finish).  It lets
+// its own dependents start at once — the expert kernel streams the shared expert meanwhile — and then waits
+// for the logits.
+//
+// A wait that runs out sets workspace word 3 (when a workspace is given) and leaves.
+constexpr int kRowsPerCta = 3;
+constexpr int kTokSlots = 4;            // tokens of a chunk worked on side by side
+constexpr int kRowsThreads = kRowsPerCta * kTokSlots * 32;
+
+template <int XD, int WD>
+__global__ void __launch_bounds__(kRowsThreads) router_rows_kernel(RouterArgs a, int n_tokens, int tok_chunk) {
+    extern __shared__ __align__(128) unsigned char rsm[];
+    const unsigned row_bytes = (unsigned)a.H * (WD == W_F32 ? 4u : 2u);
+    const unsigned xbytes = (unsigned)a.H * (XD == X_F32 ? 4u : 2u);
+    unsigned char* rows = rsm;
+    unsigned char* xb = rows + kRowsPerCta * row_bytes;                             // [2][tok_chunk][xbytes]
+    uint64_t* full = reinterpret_cast<uint64_t*>(xb + 2u * tok_chunk * xbytes);     // one barrier per row
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int e0 = blockIdx.x * kRowsPerCta;
+    const int nrows = min(kRowsPerCta, a.E - e0);
+    if (tid == 0) {
+        pdl_trigger();
+        for (int r = 0; r < nrows; ++r) mbar_init(full + r, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int r = 0; r < nrows; ++r) {
+            mbar_expect_tx(full + r, row_bytes);
+            bulk_load(rows + (size_t)r * row_bytes, reinterpret_cast<const unsigned char*>(a.W) + (size_t)(e0 + r) * row_bytes, row_bytes, full + r);
+        }
+    }
+    __syncthreads();
+    pdl_wait();   // the tokens are the predecessor's output
+    const int nchunks = (n_tokens + tok_chunk - 1) / tok_chunk;
+    const int n16 = (int)(xbytes >> 4);
+    auto stage = [&](int c) {
+        const int t0 = c * tok_chunk, nt = min(tok_chunk, n_tokens - t0);
+        const uint32_t dst = smem_u32(xb + (size_t)(c & 1) * tok_chunk * xbytes);
+        for (int i = tid; i < nt * n16; i += kRowsThreads) {
+            const int tk = i / n16, j = i - tk * n16;
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(a.x) + (size_t)(t0 + tk) * a.x_stride + 16 * (size_t)j;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + tk * xbytes + 16 * j), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0);
+    const int ri = warp / kTokSlots, ts = warp % kTokSlots;
+    for (int c = 0; c < nchunks; ++c) {
+        if (c + 1 < nchunks) {
+            stage(c + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int t = c * tok_chunk + ts;
+        if (ri < nrows && ts < tok_chunk && t < n_tokens) {
+            if (mbar_wait(full + ri, 0)) {
+                float logit, absum;
+                row_logit_smem<XD, WD>(rows + (size_t)ri * row_bytes, xb + ((size_t)(c & 1) * tok_chunk + ts) * xbytes, a.H, lane, logit, absum);
+                if (lane == 0) {
+                    const int e = e0 + ri;
+                    float* sc = a.scores + (size_t)t * a.scores_stride;
+                    if (a.logit_offset) logit = __fadd_rn(logit, a.logit_offset[e]);
+                    sc[e] = logit;
+                    if (a.exact_order) sc[a.E + e] = absum;
+                    // single launch, sigmoid scoring: the double-precision exponential runs here, in parallel
+                    if (a.counter != nullptr && a.mode != 0) sc[2 * a.E + e] = sigmoid_ref(logit);
+                }
+            } else if (lane == 0 && a.counter) {
+                a.counter[(size_t)t * a.counter_stride + 3] = 1u;
+            }
+        }
+        __syncthreads();   // the buffer is staged again two chunks later
+    }
+}
+
+__global__ void __launch_bounds__(kRouterThreads) router_select_kernel(RouterArgs a) {
+    __shared__ TopKSmem sm;
+    __shared__ __align__(16) float ring[kSeqRingFloats];
+    if (threadIdx.x == 0) {
+        pdl_trigger();
+        topk_smem_init(sm, kRouterWarps - 1);
+    }
+    router_args_of_token(a, blockIdx.x);
+    pdl_wait();   // the logits are the rows kernel's output
+    __syncthreads();
+    router_finish(a, sm, ring, threadIdx.x, kRouterThreads, a.mode != 0, true, nullptr, nullptr);
+}
+
+template <class K, class... Args>
+static int launch_router_pdl(K kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// The rows-resident pair of launches; VIB3_ERR_UNSUPPORTED when the rows and two token buffers do not fit.
+template <int XD, int WD>
+static int launch_rows_t(const RouterArgs& a, cudaStream_t st, int n_tokens) {
+    const size_t row_bytes = (size_t)a.H * (WD == W_F32 ? 4 : 2), xbytes = (size_t)a.H * (XD == X_F32 ? 4 : 2);
+    int tok_chunk = n_tokens < kTokSlots ? n_tokens : kTokSlots;
+    while (tok_chunk > 1 && kRowsPerCta * row_bytes + 2 * tok_chunk * xbytes + 64 > kSmemBudget) --tok_chunk;
+    const size_t smem = kRowsPerCta * row_bytes + 2 * tok_chunk * xbytes + 64;
+    if (smem > kSmemBudget) return VIB3_ERR_UNSUPPORTED;
+    static const cudaError_t attr = cudaFuncSetAttribute(router_rows_kernel<XD, WD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+    if (attr != cudaSuccess) return (int)attr;
+    const dim3 grid((a.E + kRowsPerCta - 1) / kRowsPerCta);
+    if (int e = launch_router_pdl(router_rows_kernel<XD, WD>, grid, kRowsThreads, smem, st, a, n_tokens, tok_chunk)) return e;
+    if (a.counter == nullptr) return VIB3_OK;   // logits only
+    return launch_router_pdl(router_select_kernel, dim3(n_tokens), kRouterThreads, 0, st, a);
+}
+
 template <int XD, int WD>
 static int launch_router_t(const RouterArgs& a, cudaStream_t st, int n_tokens) {
+    if (XD >= 0) {
+        const int e = launch_rows_t<XD < 0 ? 0 : XD, WD>(a, st, n_tokens);
+        if (e != VIB3_ERR_UNSUPPORTED) return e;
+    }
     // The largest shared-memory carve-out: the gate/up kernel that follows sizes itself to fit beside one
     // router CTA on an SM, which only works if both want the same SM configuration.
     static const cudaError_t carve = cudaFuncSetAttribute(router_kernel<XD, WD>, cudaFuncAttributePreferredSharedMemoryCarveout,
@@ -267,7 +410,7 @@ int make_router_args(const void* x, int x_dtype, const void* W, int w_dtype, flo
 }
 }  // namespace vib3
 
-// Extended launcher: one launch.  scores_buf holds 3E floats ([0, E) receives the logits, the rest is scratch);
+// Extended launcher: one call (two launches chained by programmatic dependent launch; one on the direct path).  scores_buf holds 3E floats ([0, E) receives the logits, the rest is scratch);
 // workspace is four 32-bit words, zero before the first call: [0] is an arrival counter that every
 // call leaves at zero, [1] counts the near-tie recomputations done so far (diagnostics), [2] is used by
 // vib3_launch_moe_layer_routed_int4_paged, [3] is spare.
@@ -283,10 +426,10 @@ extern "C" int vib3_launch_router_topk_ex(const void* x, int x_dtype, const void
     return launch_router(a, (cudaStream_t)stream);
 }
 
-// The single-launch router for n_tokens tokens in one launch (grid y = token): token t reads x + t * x_stride_bytes
+// The extended launcher for n_tokens tokens in one call: token t reads x + t * x_stride_bytes
 // and writes scores_buf + t * scores_stride (3E floats each), out_ids + t * ids_stride, out_weights + t *
-// weights_stride, and uses the four workspace words at workspace + 4 t.  The router's weights are read from
-// HBM once and by the other tokens from L2.
+// weights_stride, and uses the four workspace words at workspace + 4 t.  The router's weights are read once
+// per call (rows-resident path; the direct path reads them from L2 for every token after the first).
 extern "C" int vib3_launch_router_topk_batch(const void* x, int x_dtype, int x_stride_bytes, int n_tokens, const void* W, int w_dtype,
                                              float* scores_buf, int scores_stride, const float* bias, const float* logit_offset,
                                              unsigned short* out_ids, int ids_stride, float* out_weights, int weights_stride,

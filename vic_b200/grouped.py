@@ -56,6 +56,7 @@ class GroupedDecoder:
         # views into the workspace for inspection: GroupedWork {n_active, n_pairs}
         off = ws_ptr - self.workspace.data_ptr()
         self._work = self.workspace[off:off + 16].view(torch.int32)
+        self._single = None
 
     def close(self) -> None:
         if self._h:
@@ -70,7 +71,10 @@ class GroupedDecoder:
 
     @property
     def n_distinct(self) -> torch.Tensor:
-        """Distinct experts of the last step (the shared expert counts as one)."""
+        """Distinct experts of the last step (the shared expert counts as one).  A single token with all experts
+        goes through the batch-1 kernels, which keep no work list: its count is top_k (+ 1)."""
+        if self._single is not None:
+            return torch.tensor(self._single, dtype=torch.int32, device=self._work.device)
         return self._work[0]
 
     def route(self, layer: int, xs: torch.Tensor, logit_offset: Optional[torch.Tensor] = None,
@@ -87,6 +91,8 @@ class GroupedDecoder:
         T = xs.shape[0]
         out = self.out[:T] if out is None else out
         lo, hi = expert_range if expert_range is not None else (0, sh.num_experts)
+        has_shared = bool(self.shared_tables[layer]) and shared
+        self._single = (sh.top_k + int(has_shared)) if (T == 1 and lo == 0 and hi == sh.num_experts) else None
         check("moe_grouped_int4", lib().vib3_launch_moe_grouped_int4(
             self._h, xs.data_ptr(), kernels.x_dtype_code(xs), xs.stride(0) * xs.element_size(), T, self.ids.data_ptr(),
             self.ids.stride(0) * 2, self.weights.data_ptr(), self.weights.stride(0) * 4, self.tables[layer],

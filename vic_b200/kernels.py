@@ -153,7 +153,7 @@ def router_topk_ex(x: torch.Tensor, W: torch.Tensor, scores_buf, bias, out_ids, 
 def router_topk_batch(xs: torch.Tensor, W: torch.Tensor, scores_buf: torch.Tensor, bias, logit_offset, out_ids: torch.Tensor,
                       out_weights: torch.Tensor, top_k: int, scoring_mode: int, scaling_factor: float, normalize: bool,
                       exact_order: bool, workspace: torch.Tensor, stream: Optional[int] = None) -> None:
-    """The single-launch router for T tokens in ONE launch (grid y = token): xs [T, H]; scores_buf [T, 3E] fp32,
+    """The router for T tokens in ONE call (the weights are read once): xs [T, H]; scores_buf [T, 3E] fp32,
     out_ids [T, >= top_k] int16, out_weights [T, >= top_k] fp32, workspace [T, 4] int32 (zero before the first call)."""
     E, H = W.shape
     T = xs.shape[0]
