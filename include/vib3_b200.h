@@ -245,6 +245,37 @@ int vib3_launch_select_local_pairs(const unsigned short* ids, int ids_stride_byt
 /* out[c] = sum over r of in[r * row_stride + c], rows added in order (fp32; 16-byte aligned pointers,
  * row_stride a multiple of 4): combines the partial sums an expert-parallel rank has received. */
 int vib3_launch_sum_rows_f32(const float* in, int rows, int cols, int row_stride, float* out, void* stream);
+/* ── Expert-parallel exchange over peer memory (one process per GPU, same node) ──────────────────────
+ * No counterpart in the reference (single GPU).  vib3_peer_alloc: a zero-filled device allocation that other
+ * processes can map, and its 64-byte inter-process handle; vib3_peer_open maps a peer's allocation from its
+ * handle (the handles travel between the processes by any host transport); vib3_peer_close / vib3_peer_free
+ * undo them.  Only plain peer loads and stores are used on these buffers. */
+int vib3_peer_alloc(size_t bytes, void** ptr_out, unsigned char* handle_out_64);
+int vib3_peer_open(const unsigned char* handle_64, void** ptr_out);
+int vib3_peer_close(void* ptr);
+int vib3_peer_free(void* ptr);
+/* Store `bytes` bytes (may be 0: a bare signal) from src + d * src_stride_bytes into dst_table[d] + rank *
+ * dst_stride_bytes for every destination d < world, then make them visible system-wide and store the step number
+ * (*step_counter + step_offset) into flag_table[d][rank].  dst_table / flag_table: device arrays of `world` pointers, entry
+ * r = rank r's buffer (the caller's own allocation for r == rank).  16-byte aligned pointers and strides. */
+int vib3_launch_peer_publish(const void* src, size_t src_stride_bytes, int bytes, void* const* dst_table,
+                             size_t dst_stride_bytes, unsigned int* const* flag_table, const unsigned int* step_counter,
+                             int step_offset, int rank, int world, void* stream);
+/* Wait (bounded: about two seconds, then VIB3_STATUS_TIMEOUT in *status) until each of flags[0 .. world) has
+ * reached *step_counter + 1; advance != 0 then stores that step into *step_counter.  Kernels launched after this
+ * one read what the peers stored before their flags. */
+int vib3_launch_peer_wait(const unsigned int* flags, unsigned int* step_counter, int world, int advance, int* status,
+                          void* stream);
+/* vib3_launch_peer_wait (advancing) for the `world` token messages, then vib3_launch_select_local_pairs over them, as
+ * one launch; and the wait for the partial rows of the current step (flags reach *step_counter, which the message
+ * wait advanced) followed by vib3_launch_sum_rows_f32, as one launch. */
+int vib3_launch_peer_select_pairs(const unsigned int* flags, unsigned int* step_counter, int world, int* status,
+                                  const unsigned short* ids, int ids_stride_bytes, const float* weights,
+                                  int weights_stride_bytes, int top_k, int expert_lo, int expert_hi,
+                                  unsigned short* pair_experts, float* pair_weights, unsigned short* pair_tokens,
+                                  int capacity, int* count_out, void* stream);
+int vib3_launch_peer_sum_rows(const unsigned int* flags, const unsigned int* step_counter, int world, int* status,
+                              const float* in, int rows, int cols, int row_stride, float* out, void* stream);
 /* Keep, in order, the (expert, weight) pairs with expert_lo <= expert < expert_hi; *count_out = how
  * many.  ids_out / weights_out have top_k entries (unused ones are filled with expert_lo / 0). */
 int vib3_launch_select_local_experts(const unsigned short* ids, const float* weights, int top_k, int expert_lo,

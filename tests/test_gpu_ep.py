@@ -50,7 +50,7 @@ def _run(world, what, collectives=None):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("collectives", ["ring", "a2a"])
+@pytest.mark.parametrize("collectives", ["ring", "a2a", "peer"])
 def test_expert_parallel_layer_equals_single_gpu(world, collectives):
     for res in _run(world, "layer", collectives):
         assert res["collectives"] == collectives
@@ -64,3 +64,26 @@ def test_expert_parallel_layer_equals_single_gpu(world, collectives):
 def test_expert_parallel_stack_equals_single_gpu(world, batch):
     for res in _run(world, batch):
         assert res["status"] == 0 and res["rel_l2"] <= 2e-3, res
+
+
+def test_peer_wait_gives_up_on_an_absent_peer():
+    """A flag that nobody sets: the bounded wait runs out, sets VIB3_STATUS_TIMEOUT and returns; the step counter
+    still advances and the context stays usable.  (The absent peer is simulated on the host: nothing stores the flag.)"""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from vic_b200 import kernels
+    dev = torch.device("cuda:0")
+    flags = torch.zeros(2, dtype=torch.int32, device=dev)
+    flags[0] = 1                                   # rank 0 "arrived", rank 1 never does
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    kernels.peer_wait(flags, counter, 2, True, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 4
+    assert int(counter.item()) == 1
+    # both present: no time-out, and the same context still runs kernels
+    status.zero_()
+    flags.fill_(2)
+    kernels.peer_wait(flags, counter, 2, True, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(counter.item()) == 2

@@ -17,6 +17,7 @@ SOURCES = [
     "moe_pipe.cu",
     "moe_noalloc.cu",
     "moe_grouped.cu",
+    "ep_peer.cu",
     "router.cu",
     "host/page_pool.cpp",
     "host/vib3_file.cpp",

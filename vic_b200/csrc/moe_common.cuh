@@ -49,6 +49,38 @@ __device__ __forceinline__ void flag(int* status, int bit) {
     if (status) atomicOr(status, bit);
 }
 
+// One warp lists the (token, expert, weight) triples, token-major, whose expert lies in [lo, hi): the pairs of a step
+// that an expert-parallel rank owns.  ids / w: n_tokens rows of top_k entries, row strides in bytes.  The lists have
+// room for `capacity` entries; *count_out receives the number of pairs found, even if it exceeds the capacity.
+__device__ __forceinline__ void select_local_pairs_warp(const unsigned char* ids, int ids_stride, const unsigned char* w, int w_stride,
+                                                        int n_tokens, int top_k, int lo, int hi, unsigned short* pe, float* pw,
+                                                        unsigned short* pt, int capacity, int* count_out) {
+    const int lane = threadIdx.x & 31;
+    const int total = n_tokens * top_k;
+    int n = 0;
+    for (int base = 0; base < total; base += 32) {
+        const int i = base + lane;
+        int e = -1, tk = 0;
+        float wv = 0.f;
+        if (i < total) {
+            tk = i / top_k;
+            const int j = i - tk * top_k;
+            e = reinterpret_cast<const unsigned short*>(ids + (size_t)tk * ids_stride)[j];
+            wv = reinterpret_cast<const float*>(w + (size_t)tk * w_stride)[j];
+        }
+        const bool keep = e >= lo && e < hi;
+        const unsigned m = __ballot_sync(0xffffffffu, keep);
+        const int pos = n + __popc(m & ((1u << lane) - 1u));
+        if (keep && pos < capacity) {
+            pe[pos] = (unsigned short)e;
+            pw[pos] = wv;
+            pt[pos] = (unsigned short)tk;
+        }
+        n += __popc(m);
+    }
+    if (lane == 0) *count_out = n;
+}
+
 // Position of slot s's activations in the scratch buffer: the shared expert (slot top_k in plan
 // order) is stored FIRST, so that where it lives does not depend on the routing — the gate/up kernel
 // can then work on the shared expert before the router has finished.  `a.top_k` is the active count.

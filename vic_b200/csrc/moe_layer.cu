@@ -546,30 +546,7 @@ extern "C" int vib3_launch_moe_layer_int4_paged_grouped(
 __global__ void select_local_pairs_kernel(const unsigned char* ids, int ids_stride, const unsigned char* w, int w_stride,
                                           int n_tokens, int top_k, int lo, int hi, unsigned short* pe, float* pw,
                                           unsigned short* pt, int capacity, int* count_out) {
-    const int lane = threadIdx.x;
-    const int total = n_tokens * top_k;
-    int n = 0;
-    for (int base = 0; base < total; base += 32) {
-        const int i = base + lane;
-        int e = -1, tk = 0;
-        float wv = 0.f;
-        if (i < total) {
-            tk = i / top_k;
-            const int j = i - tk * top_k;
-            e = reinterpret_cast<const unsigned short*>(ids + (size_t)tk * ids_stride)[j];
-            wv = reinterpret_cast<const float*>(w + (size_t)tk * w_stride)[j];
-        }
-        const bool keep = e >= lo && e < hi;
-        const unsigned m = __ballot_sync(0xffffffffu, keep);
-        const int pos = n + __popc(m & ((1u << lane) - 1u));
-        if (keep && pos < capacity) {
-            pe[pos] = (unsigned short)e;
-            pw[pos] = wv;
-            pt[pos] = (unsigned short)tk;
-        }
-        n += __popc(m);
-    }
-    if (lane == 0) *count_out = n;
+    select_local_pairs_warp(ids, ids_stride, w, w_stride, n_tokens, top_k, lo, hi, pe, pw, pt, capacity, count_out);
 }
 
 extern "C" int vib3_launch_select_local_pairs(const unsigned short* ids, int ids_stride_bytes, const float* weights,

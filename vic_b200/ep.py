@@ -17,8 +17,11 @@ scaling), which is how a data-parallel attention stage feeds an expert-parallel 
   4. reduce_scatter of the per-token partial sums [G, H] fp32: each rank receives the full layer
      output of its own token.
 
-Peer data always lands in local HBM (NCCL receive buffers) before a kernel reads it.  The only
-difference from the single-GPU result is the fp32 association of the cross-rank sum.
+The two exchanges come in three forms (ExpertParallelDecoder(collectives=...)): "peer" — the default on GPUs — stores
+the message / the partial rows straight into the peers' buffers over NVLink and follows them with a flag
+(csrc/ep_peer.cu); "ring" and "a2a" use NCCL.
+Peer data always lands in local HBM before a kernel reads it.  The only difference from the single-GPU result is
+the fp32 association of the cross-rank sum.
 """
 from __future__ import annotations
 
@@ -109,6 +112,95 @@ def combine_partials(out: torch.Tensor, partial: torch.Tensor, rank: int, world:
         dist.reduce_scatter_tensor(out, partial.view(-1), op=dist.ReduceOp.SUM, group=group)
 
 
+class _DevMem:
+    """A device allocation owned by somebody else, as an object torch can wrap (no copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class PeerExchange:
+    """The two exchanges of a decode step over peer memory instead of NCCL (csrc/ep_peer.cu): every rank maps every
+    other rank's exchange buffer; a message or a partial row is stored straight into the peers' buffers and followed
+    by a flag.  Layout of a rank's buffer: [G messages][G rows of H fp32: row r = rank r's partial sum of this
+    rank's token][G flags of the messages][G flags of the rows]."""
+
+    def __init__(self, hidden: int, msg_bytes: int, rank: int, world: int, device, group=None):
+        import ctypes as C
+        from .lib import check, lib
+        self.rank, self.world, self.group = rank, world, group
+        self.msg_bytes, self.hidden = msg_bytes, hidden
+        self.recv_off = 0
+        self.rows_off = (world * msg_bytes + 255) // 256 * 256
+        self.flags1_off = self.rows_off + (world * hidden * 4 + 255) // 256 * 256
+        self.flags2_off = self.flags1_off + 256 * ((world * 4 + 255) // 256)
+        self.nbytes = self.flags2_off + 256 * ((world * 4 + 255) // 256)
+        handle = (C.c_ubyte * 64)()
+        ptr = C.c_void_p()
+        check("peer_alloc", lib().vib3_peer_alloc(self.nbytes, C.byref(ptr), handle))
+        self._own = ptr.value
+        handles: List[Optional[bytes]] = [None] * world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.bases: List[int] = []
+        self._opened: List[int] = []
+        for r in range(world):
+            if r == rank:
+                self.bases.append(self._own)
+                continue
+            q = C.c_void_p()
+            check("peer_open", lib().vib3_peer_open((C.c_ubyte * 64).from_buffer_copy(handles[r]), C.byref(q)))
+            self.bases.append(q.value)
+            self._opened.append(q.value)
+        mem = torch.as_tensor(_DevMem(self._own, self.nbytes), device=device)
+        self.recv = mem[self.recv_off:self.recv_off + world * msg_bytes].view(world, msg_bytes)
+        self.rows = mem[self.rows_off:self.rows_off + world * hidden * 4].view(torch.float32).view(world, hidden)
+        self.flags1 = mem[self.flags1_off:self.flags1_off + world * 4].view(torch.int32)
+        self.flags2 = mem[self.flags2_off:self.flags2_off + world * 4].view(torch.int32)
+
+        def table(off):
+            return torch.tensor([b + off for b in self.bases], dtype=torch.int64, device=device)
+        self.recv_table, self.rows_table = table(self.recv_off), table(self.rows_off)
+        self.flags1_table, self.flags2_table = table(self.flags1_off), table(self.flags2_off)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)   # the step both exchanges are at
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)   # every rank has mapped every buffer before anybody stores into one
+
+    def publish_message(self, send: torch.Tensor) -> None:
+        """This rank's message into slot `rank` of every rank's buffer, flagged with the NEXT step."""
+        from . import kernels
+        kernels.peer_publish(send, 0, self.msg_bytes, self.recv_table, self.msg_bytes, self.flags1_table, self.counter, 1,
+                             self.rank, self.world)
+
+    def wait_select_pairs(self, status, ids, weights, top_k, lo, hi, pair_e, pair_w, pair_t, n_pairs) -> None:
+        """Wait for every rank's message of the next step (the step counter advances), then list this rank's pairs."""
+        from . import kernels
+        kernels.peer_select_pairs(self.flags1, self.counter, self.world, status, ids, self.msg_bytes, weights, self.msg_bytes, top_k,
+                                  lo, hi, pair_e, pair_w, pair_t, pair_e.numel(), n_pairs)
+
+    def publish_rows(self, partial: torch.Tensor) -> None:
+        """Row t of `partial` ([G, H] fp32) goes to rank t's row `rank`, flagged with the current step."""
+        from . import kernels
+        kernels.peer_publish(partial, self.hidden * 4, self.hidden * 4, self.rows_table, self.hidden * 4, self.flags2_table,
+                             self.counter, 0, self.rank, self.world)
+
+    def wait_sum_rows(self, status, out: torch.Tensor) -> None:
+        """Wait for every rank's partial row of the current step, then add the rows in rank order."""
+        from . import kernels
+        kernels.peer_sum_rows(self.flags2, self.counter, self.world, status, self.rows, out)
+
+    def close(self) -> None:
+        from .lib import lib
+        if self._own is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)   # nobody unmaps or frees while a peer may still store
+        for q in self._opened:
+            lib().vib3_peer_close(q)
+        dist.barrier(group=self.group)
+        lib().vib3_peer_free(self._own)
+        self._own, self._opened = None, []
+
+
 class ExpertParallelDecoder:
     """One rank's share of an expert-parallel MoE layer stack."""
 
@@ -125,9 +217,16 @@ class ExpertParallelDecoder:
         self.recv_x, self.recv_ids, self.recv_w = message_views(self.recv, sh.hidden)
         self.partial = torch.zeros(world, sh.hidden, dtype=torch.float32, device=dev)
         self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
-        # "a2a": both exchanges as one-hop all-to-alls (plus a row sum); "ring": NCCL all-gather / reduce-scatter
+        # "peer": stores into the peers' buffers over NVLink, followed by flags (PeerExchange); "a2a": both exchanges
+        # as NCCL one-hop all-to-alls (plus a row sum); "ring": NCCL all-gather / reduce-scatter
         # measured: two ranks ring 11 + 11 us, a2a 14 + 14 us; eight ranks ring 21 + 19 us, a2a 16 + 17 us
-        self.collectives = collectives or ("a2a" if world >= 8 else "ring")
+        on_gpus = world > 1 and dev.type == "cuda" and dist.is_initialized() and dist.get_backend(group) == "nccl"
+        self.collectives = collectives or ("peer" if on_gpus else "ring")
+        self.peer = None
+        if self.collectives == "peer":
+            self.peer = PeerExchange(sh.hidden, self.msg_bytes, rank, world, dev, group)
+            self.recv = self.peer.recv
+            self.recv_x, self.recv_ids, self.recv_w = message_views(self.recv, sh.hidden)
         self.send_rep = torch.zeros(world, self.msg_bytes, dtype=torch.uint8, device=dev) if self.collectives == "a2a" else None
         self.partial_in = torch.zeros(world, sh.hidden, dtype=torch.float32, device=dev) if self.collectives == "a2a" else None
         cap = world * sh.top_k
@@ -141,6 +240,8 @@ class ExpertParallelDecoder:
         self.grouped_launches = (cap + PAIRS_PER_LAUNCH - 1) // PAIRS_PER_LAUNCH
         # router, pair selection, (gate/up, down) per grouped launch, the row sum of the all-to-all form
         self.launches_per_step = 2 + 2 * self.grouped_launches + (1 if self.collectives == "a2a" else 0)
+        if self.peer is not None:   # router (2), publish, wait + pair selection, grouped pairs, publish, wait + row sum
+            self.launches_per_step = 2 + 1 + 1 + 2 * self.grouped_launches + 1 + 1
 
     def step(self, layer: int, x: torch.Tensor, logit_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
@@ -159,6 +260,9 @@ class ExpertParallelDecoder:
                                logit_offset=logit_offset)
 
     def gather(self) -> None:
+        if self.peer is not None:
+            self.peer.publish_message(self.send)   # stores only: the wait is the first thing experts() does
+            return
         gather_messages(self.send, self.recv, self.world, self.group, self.send_rep)
 
     def experts(self, layer: int) -> None:
@@ -166,9 +270,13 @@ class ExpertParallelDecoder:
         from .core_types import X_BF16
         sh, dec = self.model.shape, self.dec
         H = sh.hidden
-        kernels.select_local_pairs(self.recv_ids, self.msg_bytes, self.recv_w, self.msg_bytes, self.world, sh.top_k,
-                                   self.expert_lo, self.expert_hi, self.pair_e, self.pair_w, self.pair_t,
-                                   self.pair_e.numel(), self.n_pairs)
+        if self.peer is not None:
+            self.peer.wait_select_pairs(dec.status, self.recv_ids, self.recv_w, sh.top_k, self.expert_lo, self.expert_hi,
+                                        self.pair_e, self.pair_w, self.pair_t, self.n_pairs)
+        else:
+            kernels.select_local_pairs(self.recv_ids, self.msg_bytes, self.recv_w, self.msg_bytes, self.world, sh.top_k,
+                                       self.expert_lo, self.expert_hi, self.pair_e, self.pair_w, self.pair_t,
+                                       self.pair_e.numel(), self.n_pairs)
         for j in range(self.grouped_launches):
             kernels.moe_layer_int4_paged_grouped(
                 self.recv_x, X_BF16, self.msg_bytes, self.world, dec.tables[layer], sh.num_experts,
@@ -177,8 +285,17 @@ class ExpertParallelDecoder:
                 sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status)
 
     def combine(self) -> torch.Tensor:
+        if self.peer is not None:
+            self.peer.publish_rows(self.partial)
+            self.peer.wait_sum_rows(self.dec.status, self.out)
+            return self.out
         combine_partials(self.out, self.partial, self.rank, self.world, self.group, self.partial_in)
         return self.out
+
+    def close(self) -> None:
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
 
     def routing(self):
         """This rank's token's routing of the last step (host copies)."""
@@ -325,6 +442,7 @@ def parity_check(rank: int, world: int, dev, steps: int = 6, group=None) -> dict
     res = {"max_abs": float(t[0]), "rel_l2": float(t[1]), "topk_equal": bool(t[2] == 0), "status": int(t[3]),
            "max_local_pairs": int(t[4]), "steps": steps, "collectives": epd.collectives,
            "ok": bool(t[0] <= 2e-2 and t[1] <= 1e-3 and t[2] == 0 and t[3] == 0)}
+    epd.close()
     del epd, ref, mine, full
     torch.cuda.empty_cache()
     return res
@@ -444,11 +562,25 @@ def bench_main(args) -> None:
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0]) / e2e_steps
 
-    # where the step's time goes: each phase alone in a CUDA graph of its own
-    phases = {}
-    for name, fn in (("route", lambda i: ep.route(i % layers, xs[i % B.N_TOKENS])), ("exchange_tokens", lambda i: ep.gather()),
-                     ("experts", lambda i: ep.experts(i % layers)), ("combine", lambda i: ep.combine())):
-        phases[name] = round(timed_graph(fn, 16, 64, 5.0)[0] * 1e3, 1)
+    # where the step's time goes: the step cut short after each phase (every rank runs the same prefix, so an
+    # exchange always finds its partners), each prefix in a CUDA graph of its own; a phase is the difference
+    def prefix(n):
+        def run(i):
+            ep.route(i % layers, xs[i % B.N_TOKENS])
+            if n >= 2:
+                ep.gather()
+            if n >= 3:
+                ep.experts(i % layers)
+            if n >= 4:
+                ep.combine()
+        return run
+    cum = [timed_graph(prefix(n), 16, 64, 5.0)[0] * 1e3 for n in (1, 2, 3, 4)]
+    phases = {"route": round(cum[0], 1), "exchange_tokens": round(cum[1] - cum[0], 1), "experts": round(cum[2] - cum[1], 1),
+              "combine": round(cum[3] - cum[2], 1)}
+    if ep.peer is not None:
+        phases["note"] = ("the wait for the messages is the first warp of the pair selection, so it counts under experts; the shortened "
+                          "steps lack the second exchange that normally keeps a rank from overwriting a message still being read, so "
+                          "they are timings only")
     assert int(ep.dec.status.item()) == 0
 
     # correctness at this world size, outside every timed region
@@ -480,7 +612,8 @@ def bench_main(args) -> None:
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": B.DTYPE,
             "data": "synthetic", "config": B.workload_config(world),
             "timed": {"steps": timed_steps, "graph_steps": chunk, "physical_layers": layers, "launch_mode": "cuda-graph",
-                      "collectives": f"NCCL ({ep.collectives})", "experts_per_gpu": sh.num_experts // world},
+                      "collectives": "peer memory: stores and flags over NVLink (csrc/ep_peer.cu)" if ep.peer is not None else f"NCCL ({ep.collectives})",
+                      "experts_per_gpu": sh.num_experts // world},
             "e2e": {"value": world / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": world * sh.hidden * 2,
                     "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
             "gpu_launches": timed_steps * ep.launches_per_step * world,
@@ -494,6 +627,7 @@ def bench_main(args) -> None:
         print(json.dumps(line))
     # leave without tearing the communicator down under live CUDA graphs that hold its kernels
     torch.cuda.synchronize()
+    ep.close()
     import sys
     sys.stdout.flush()
     os._exit(0)

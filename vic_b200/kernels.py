@@ -255,6 +255,35 @@ def sum_rows_f32(rows_in: torch.Tensor, out: torch.Tensor, stream: Optional[int]
                                                          _ptr(out), _stream(stream)))
 
 
+def peer_publish(src: torch.Tensor, src_stride_bytes: int, nbytes: int, dst_table: torch.Tensor, dst_stride_bytes: int,
+                 flag_table: torch.Tensor, step_counter: torch.Tensor, step_offset: int, rank: int, world: int,
+                 stream: Optional[int] = None) -> None:
+    """Store nbytes from src (+ d * src_stride_bytes) into every rank d's buffer at slot `rank`, then the flag
+    (*step_counter + step_offset)."""
+    check("peer_publish", lib().vib3_launch_peer_publish(_ptr(src), src_stride_bytes, nbytes, _ptr(dst_table), dst_stride_bytes,
+                                                         _ptr(flag_table), _ptr(step_counter), step_offset, rank, world, _stream(stream)))
+
+
+def peer_wait(flags: torch.Tensor, step_counter: torch.Tensor, world: int, advance: bool, status, stream: Optional[int] = None) -> None:
+    """Wait (bounded) until every peer's flag has reached the next step; advance the step counter."""
+    check("peer_wait", lib().vib3_launch_peer_wait(_ptr(flags), _ptr(step_counter), world, int(advance), _ptr(status), _stream(stream)))
+
+
+def peer_select_pairs(flags, step_counter, world: int, status, ids, ids_stride_bytes: int, weights, weights_stride_bytes: int,
+                      top_k: int, expert_lo: int, expert_hi: int, pair_experts, pair_weights, pair_tokens, capacity: int, count_out,
+                      stream: Optional[int] = None) -> None:
+    """peer_wait for the messages (advancing the step) and select_local_pairs over them in one launch."""
+    check("peer_select_pairs", lib().vib3_launch_peer_select_pairs(
+        _ptr(flags), _ptr(step_counter), world, _ptr(status), _ptr(ids), ids_stride_bytes, _ptr(weights), weights_stride_bytes, top_k,
+        expert_lo, expert_hi, _ptr(pair_experts), _ptr(pair_weights), _ptr(pair_tokens), capacity, _ptr(count_out), _stream(stream)))
+
+
+def peer_sum_rows(flags, step_counter, world: int, status, rows_in: torch.Tensor, out: torch.Tensor, stream: Optional[int] = None) -> None:
+    """Wait for the partial rows of the current step, then out[c] = sum_r rows_in[r, c] in row order: one launch."""
+    check("peer_sum_rows", lib().vib3_launch_peer_sum_rows(_ptr(flags), _ptr(step_counter), world, _ptr(status), _ptr(rows_in),
+                                                           rows_in.shape[0], rows_in.shape[1], rows_in.stride(0), _ptr(out), _stream(stream)))
+
+
 def select_local_experts(ids, weights, top_k: int, expert_lo: int, expert_hi: int, ids_out, weights_out, count_out,
                          stream: Optional[int] = None) -> None:
     check("select_local_experts", lib().vib3_launch_select_local_experts(

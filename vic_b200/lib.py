@@ -72,6 +72,14 @@ SIGNATURES = {
     "vib3_moe_step_run": (_i, [_vp, _vp, _vp]),
     "vib3_moe_step_destroy": (None, [_vp]),
     "vib3_launch_sum_rows_f32": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "vib3_peer_alloc": (_i, [C.c_size_t, C.POINTER(_vp), _vp]),
+    "vib3_peer_open": (_i, [_vp, C.POINTER(_vp)]),
+    "vib3_peer_close": (_i, [_vp]),
+    "vib3_peer_free": (_i, [_vp]),
+    "vib3_launch_peer_publish": (_i, [_vp, C.c_size_t, _i, _vp, C.c_size_t, _vp, _vp, _i, _i, _i, _vp]),
+    "vib3_launch_peer_select_pairs": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
+    "vib3_launch_peer_sum_rows": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp]),
+    "vib3_launch_peer_wait": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "vib3_launch_select_local_experts": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "vib3_moe_grouped_workspace_bytes": (C.c_size_t, [_i, _i, _i, _i, _i, _i, _i]),
     "vib3_moe_grouped_prewarm": (_i, [_vp, C.c_size_t, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, C.c_size_t, C.POINTER(_vp)]),
