@@ -95,16 +95,19 @@ struct GroupedArgs {
     int* status;
 };
 
-// mbar_wait for the roles that wait long: a failed poll sleeps, so that the polling loop does not take issue slots from
-// the converting warps that share its scheduler.
-__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, unsigned parity, unsigned ns) {
+// The waits of this kernel: mbarrier.try_wait with a suspend-time hint, so that a waiting warp sleeps in hardware
+// until the barrier's phase completes (or the hint runs out) instead of polling — the polling loops of 26 warps took a
+// quarter of the SM's issue slots from the converting warps.  Bounded: kGrpWaitTries tries of kGrpWaitHintNs each
+// (about four seconds), then false.
+constexpr unsigned kGrpWaitHintNs = 4000000u;
+constexpr unsigned kGrpWaitTries = 1024u;
+__device__ __forceinline__ bool mbar_wait_hint(uint64_t* bar, unsigned parity) {
     const uint32_t addr = smem_u32(bar);
-    for (unsigned it = 0; it < kSpinLimit; ++it) {
+    for (unsigned it = 0; it < kGrpWaitTries; ++it) {
         uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity), "r"(kGrpWaitHintNs) : "memory");
         if (ok) return true;
-        __nanosleep(ns);
     }
     return false;
 }
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             for (int i = 0; i < total; ++i, ++it) {
                 const int s = i % nslab;
                 const int st = it % kGrpStages;
-                if (it >= kGrpStages) ok = mbar_wait_sleep(empty + st, ((it / kGrpStages) - 1) & 1, 100);
+                if (it >= kGrpStages) ok = mbar_wait_hint(empty + st, ((it / kGrpStages) - 1) & 1);
                 if (!ok) break;
                 if (lane == 0) mbar_expect_tx(full + st, kGrpRawBytes);
                 __syncwarp();
@@ -300,7 +303,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
         // drain: every issued copy must have landed before the CTA's shared memory goes away
         if (lane == 0)
             for (int k = max(0, it - kGrpStages); k < it; ++k)
-                if (!mbar_wait(full + (k % kGrpStages), (k / kGrpStages) & 1)) flag(a.status, kStatusTimeout);
+                if (!mbar_wait_hint(full + (k % kGrpStages), (k / kGrpStages) & 1)) flag(a.status, kStatusTimeout);
     } else if (warp == kGrpXWarp) {
         // ── TMA producer of the token ring: one copy per slab (four K-major tiles of 64 columns) ──
         int it = 0;
@@ -310,7 +313,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN) {
                 for (int s = 0; s < nslab; ++s, ++it) {
                     const int xs = it % kGrpXStages;
-                    if (it >= kGrpXStages) ok = mbar_wait_sleep(a_empty + xs, ((it / kGrpXStages) - 1) & 1, 100);
+                    if (it >= kGrpXStages) ok = mbar_wait_hint(a_empty + xs, ((it / kGrpXStages) - 1) & 1);
                     if (!ok) break;
                     if (lane == 0) {
                         mbar_expect_tx(xfull + xs, kGrpXBytes);
@@ -323,7 +326,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
         if (lane == 0)
             for (int k = max(0, it - kGrpXStages); k < it; ++k)
-                if (!mbar_wait(xfull + (k % kGrpXStages), (k / kGrpXStages) & 1)) flag(a.status, kStatusTimeout);
+                if (!mbar_wait_hint(xfull + (k % kGrpXStages), (k / kGrpXStages) & 1)) flag(a.status, kStatusTimeout);
     } else if (warp <= kGrpMmaWarps) {
         // ── MMA issuers: warp w takes the K steps 4 (w - 1) .. 4 (w - 1) + 3 of every slab and accumulates them into
         // its own partial accumulator; the epilogue adds the four ──
@@ -334,10 +337,10 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
                 const uint32_t idesc = (1u << 4) | ((uint32_t)(kGrpMaxN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
                 const int db = pc & 1;
-                if (pc >= 2) ok = mbar_wait_sleep(d_empty + db, ((pc >> 1) - 1) & 1, 100);
+                if (pc >= 2) ok = mbar_wait_hint(d_empty + db, ((pc >> 1) - 1) & 1);
                 for (int s = 0; ok && s < nslab; ++s, ++it) {
                     const int xs = it % kGrpXStages, ab = it % kGrpABufs;
-                    ok = mbar_wait_sleep(xfull + xs, (it / kGrpXStages) & 1, 20) && mbar_wait_sleep(a_full + ab, (it / kGrpABufs) & 1, 20);
+                    ok = mbar_wait_hint(xfull + xs, (it / kGrpXStages) & 1) && mbar_wait_hint(a_full + ab, (it / kGrpABufs) & 1);
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
@@ -385,7 +388,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             for (int i = 0; ok && i < total; ++i, ++it) {
                 if ((it & 1) != team) continue;
                 const int st = it % kGrpStages, ab = it % kGrpABufs;
-                ok = mbar_wait(full + st, (it / kGrpStages) & 1);
+                ok = mbar_wait_hint(full + st, (it / kGrpStages) & 1);
                 if (!ok) break;
                 const uint32_t sb = smem_u32(wring + (size_t)st * kGrpRawBytes);
                 const uint32_t cb = sb + code_off;
@@ -399,7 +402,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
                     dequant_chunk(c0, __byte_perm(sc0, 0, 0x1010), h0);
                     dequant_chunk(c1, __byte_perm(sc0, 0, 0x3232), h1);
                 }
-                if (it >= kGrpABufs) ok = mbar_wait(a_empty + ab, ((it / kGrpABufs) - 1) & 1);
+                if (it >= kGrpABufs) ok = mbar_wait_hint(a_empty + ab, ((it / kGrpABufs) - 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 uint4 c2 = make_uint4(0, 0, 0, 0), c3 = c2;
@@ -434,7 +437,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
                 const int ntok = min(kGrpMaxN, t.n_tok - p0);
                 const int db = pc & 1;
-                ok = mbar_wait_sleep(d_full + db, (pc >> 1) & 1, 500);
+                ok = mbar_wait_hint(d_full + db, (pc >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + kGrpDCol0 + db * kGrpMmaWarps * kGrpMaxN;
