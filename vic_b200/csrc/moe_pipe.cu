@@ -158,7 +158,26 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
                     ok = mbar_wait(reinterpret_cast<uint64_t*>(&rs.routing_ready), 0);
                     if (!ok) break;
                 } else {
-                    pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
+                    // Expert ids, weights and the optional slot count are outputs of earlier kernels.  A router that
+                    // announces its routing lets this warp go as soon as ids and weights are in memory, about a
+                    // microsecond before the router's launch has ended and been flushed; otherwise (or if the
+                    // announcement does not come within the bound) the dependency wait does it.
+                    bool announced = false;
+                    if (a.route_announce) {
+                        unsigned want, have = 0;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(want) : "l"(a.route_announce) : "memory");
+                        if (lane == 0) {
+                            for (unsigned it = 0; it < (1u << 20); ++it) {
+                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(have) : "l"(a.route_announce + 1) : "memory");
+                                if (have == want) break;
+                                __nanosleep(200);
+                            }
+                        }
+                        have = __shfl_sync(0xffffffffu, have, 0);
+                        __threadfence();
+                        announced = have == want;
+                    }
+                    if (!announced) pdl_wait();
                     // Only now may the next kernel in the stream start: it reads the routing without waiting,
                     // and may overwrite nothing this kernel still reads.
                     pdl_trigger();
@@ -384,6 +403,29 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + st);
             ++n;
+        }
+    }
+    // This warp's share of the CTA's tiles is done.  The down kernel that follows gives CTA b the output rows
+    // cta_share(H): ask for those rows of every slot's down matrix to be brought into L2 now, so that the memory system
+    // keeps working across the boundary between the two kernels (its CTAs cannot be resident beside this one, and
+    // their rings start empty).  A hint only: nothing waits for it and nothing depends on it.
+    if (warp == 0 && a.prefetch_down && !grouped && !ROUTED) {
+        int h0, h1;
+        cta_share(a.H, h0, h1);
+        const unsigned dcode = (unsigned)a.I / 2, dscale = (unsigned)a.I / 16;
+        const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+        if (lane < slots && h1 > h0) {
+            const PageEntry* pg = slot_pages(a, lane);
+            for (int p = h0 / a.rpp_dn; pg && p <= (h1 - 1) / a.rpp_dn && p < a.P; ++p) {
+                const PageEntry e = pg[kSegDown * a.P + p];
+                const int r0 = max(h0, p * a.rpp_dn) - p * a.rpp_dn;
+                const int nr = min(h1, (p + 1) * a.rpp_dn) - max(h0, p * a.rpp_dn);
+                if (e.ptr == 0 || nr <= 0 || r0 + nr > e.row_count) continue;
+                const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + (size_t)r0 * dcode), "r"(nr * dcode) : "memory");
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;"
+                             ::"l"(base + (size_t)e.row_count * dcode + (size_t)r0 * dscale), "r"(nr * dscale) : "memory");
+            }
         }
     }
 }
