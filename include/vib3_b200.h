@@ -141,13 +141,13 @@ int vib3_launch_moe_layer_int4_paged(const void* x, int x_dtype, const void* pag
 /* Router and experts of one token in one call; the routing (ids_out u16[top_k], weights_out f32[top_k],
  * device) is an OUTPUT, written for the caller and for the kernels that follow.  Replaces
  * run_router_gpu_topk_nosync (src/compute/kernels.rs:1890-1953) followed by the per-page expert sequence
- * (src/runtime/engine.rs:6094-6107, :6215-6223, :6290-6296).  The router is launched first and tells the gate/up
- * kernel through two workspace words when ids and weights are in memory, so that the expert kernels go on about a
- * microsecond before the router's launch has ended (vib3_config_set key 2 instead lets the gate/up kernel route the
- * token in its own prologue; measured slower).  Router arguments as for vib3_launch_router_topk_ex except the
- * workspace: EIGHT uint32, zero before the first call ([0..3] as there, [4..5] the announcement, [6..7] spare);
- * layer arguments as for vib3_launch_moe_layer_int4_paged.  The launch may follow the kernel that produces x with
- * programmatic dependent launch. */
+ * (src/runtime/engine.rs:6094-6107, :6215-6223, :6290-6296).  Where the shapes allow (hidden and expert
+ * dimensions multiples of 256, a router row no larger than a ring stage) the gate/up kernel streams the
+ * router's rows through its own ring and selects in its prologue — two launches for the layer and no idle
+ * memory pipe while the router's serial tail runs; otherwise the router is launched first.  Router
+ * arguments as for vib3_launch_router_topk_ex (workspace: four uint32, zero before the first call; [0]
+ * and [2] are left zero), layer arguments as for vib3_launch_moe_layer_int4_paged.  The launch may
+ * follow the kernel that produces x with programmatic dependent launch. */
 int vib3_launch_moe_layer_routed_int4_paged(const void* x, int x_dtype, const void* router_w, int w_dtype,
                                             float* scores_buf, const float* bias_or_null,
                                             const float* logit_offset_or_null, unsigned short* ids_out,
@@ -191,7 +191,7 @@ int vib3_launch_moe_layer_int4_paged_var(const void* x, int x_dtype, const void*
  * 5052-5360).  x_host: ordinary or pinned host memory.  If out_dev is null, out_host must be
  * device-addressable (pinned) memory and the last kernel stores the result into it directly;
  * otherwise the kernels write out_dev and a device-to-host copy follows.  x_dev: device scratch for
- * the token.  Other arguments as for vib3_launch_moe_layer_routed_int4_paged (workspace: eight uint32). */
+ * the token.  Other arguments as for vib3_launch_router_topk_ex / vib3_launch_moe_layer_int4_paged. */
 int vib3_moe_layer_step_host(const void* x_host, int x_dtype, void* x_dev, const void* router_w, int w_dtype,
                              float* scores_buf, const float* bias_or_null, unsigned short* ids_dev, float* weights_dev,
                              int num_experts, int top_k, int scoring_mode, float scaling_factor, int normalize,
@@ -349,8 +349,7 @@ int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_dtype, int x
  * 0 forces the direct-load kernels.  key 1: launch the staged kernels with programmatic dependent
  * launch so that their prologue overlaps the previous kernel's tail (default 1).  key 2:
  * vib3_launch_moe_layer_routed_int4_paged routes inside the gate/up kernel (default 0: the router is a
- * launch of its own, which measures faster on the Kimi shape).  key 3: the gate/up kernel of a whole-layer call
- * asks, once its own copies are issued, for the down matrices' rows to be brought into L2 (default 1).  The switches are
+ * launch of its own, which measures faster on the Kimi shape).  The switches are
  * atomics: a launch running concurrently on another thread sees the old or the new value.  Returns
  * the previous value, or VIB3_ERR_UNSUPPORTED for an unknown key. */
 int vib3_config_set(int key, int value);

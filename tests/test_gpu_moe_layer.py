@@ -63,7 +63,8 @@ def test_fused_layer_vs_oracle(cuda_dev, oracle, name, xdt, ntok):
 
 @pytest.mark.parametrize("name,xdt", [("kimi", torch.bfloat16), ("kimi", torch.float32), ("mixtral", torch.float16)])
 def test_staged_kernels_equal_direct_kernels_bit_for_bit(cuda_dev, name, xdt):
-    """The bulk-copy staged kernels and the direct-load kernels share their arithmetic: same bits."""
+    """The bulk-copy staged kernels and the direct-load kernels share their arithmetic: same bits (experts wider
+    than 2048: same bits for gate/up, agreement to rounding for down, whose staged form splits K across warps)."""
     from vic_b200.lib import lib
     from vic_b200.moe import MoeDecoder
     from vic_b200.synth import synth_activation
@@ -81,7 +82,11 @@ def test_staged_kernels_equal_direct_kernels_bit_for_bit(cuda_dev, name, xdt):
             torch.cuda.synchronize()
             assert int(dec.status.item()) == 0
             assert torch.equal(act_a, dec.act)
-            assert torch.equal(a, b)
+            if model.shape.intermediate <= 2048:
+                assert torch.equal(a, b)
+            else:
+                # wide experts: the staged down kernel splits K across warps (another fp32 association)
+                assert float((a - b).abs().max()) <= 2e-3 * max(1.0, float(b.abs().max()))
     finally:
         lib().vib3_config_set(0, 1)
 

@@ -35,8 +35,6 @@ struct MoeLayerArgs {
     int x_stride;                  // bytes between the tokens' activation vectors
     int out_stride;                // floats between the tokens' output rows
     int slot_begin;                // pairs of the device-side count that earlier launches have taken
-    const unsigned int* route_announce;  // optional: the router's two announcement words (RouterArgs::announce)
-    int prefetch_down;             // gate/up launch: warm L2 with the down matrices' rows at the end (the down launch follows)
 };
 
 enum StatusBits : int { kStatusMissingPage = 1, kStatusBadExpert = 2, kStatusTimeout = 4 };

@@ -220,7 +220,6 @@ std::atomic<int> g_use_pdl{1};
 // 1 = vib3_launch_moe_layer_routed_int4_paged lets the gate/up kernel route the token in its prologue where the
 // shapes allow; 0 (default: measured 2 us per layer-token faster on the Kimi shape) = the router is a launch of its own.
 std::atomic<int> g_route_in_kernel{0};
-std::atomic<int> g_prefetch_down{0};     // vib3_config_set key 3
 
 template <class K>
 static int ensure_smem(K kernel, size_t bytes) {
@@ -259,7 +258,7 @@ int make_router_args(const void* x, int x_dtype, const void* W, int w_dtype, flo
                      const float* logit_offset, unsigned short* out_ids, float* out_weights, int hidden_dim, int num_experts,
                      int top_k, int scoring_mode, float scaling_factor, int normalize, int exact_order,
                      unsigned int* workspace, RouterArgs& a);  // router.cu
-int launch_router_args(const RouterArgs& a, cudaStream_t st, bool* announces);  // router.cu
+int launch_router_args(const RouterArgs& a, cudaStream_t st);  // router.cu
 }  // namespace vib3
 
 using namespace vib3;
@@ -291,8 +290,6 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, const Route
     a.H = hidden_dim; a.I = expert_hidden_dim; a.P = pages_per_segment;
     a.rpp_gu = rows_per_page_gate_up; a.rpp_dn = rows_per_page_down; a.status = status;
     a.slot_token = nullptr; a.n_tokens = 1; a.shared_token = 0; a.x_stride = 0; a.out_stride = 0; a.slot_begin = 0;
-    a.prefetch_down = ((phases & 3) == 3 && g_prefetch_down.load(std::memory_order_relaxed)) ? 1 : 0;
-    a.route_announce = nullptr;
     cudaStream_t st = (cudaStream_t)stream;
 
     const bool use_pipe = g_use_pipeline.load(std::memory_order_relaxed) != 0;
@@ -303,11 +300,7 @@ static int moe_layer_dispatch(int phases, const int* num_active_dev, const Route
                                                                                                : VIB3_ERR_UNSUPPORTED;
         if (err == 0) phases &= ~1;
         else if (err != VIB3_ERR_UNSUPPORTED) return err;
-        else {
-            bool announces = false;
-            if ((err = launch_router_args(*router, st, &announces)) != 0) return err;
-            if (announces) a.route_announce = router->announce;
-        }
+        else if ((err = launch_router_args(*router, st)) != 0) return err;
     }
     if ((phases & 1) && use_pipe) {
         err = launch_gateup_pipelined(a, st);
@@ -354,7 +347,6 @@ extern "C" int vib3_config_set(int key, int value) {
     if (key == 0) return g_use_pipeline.exchange(value ? 1 : 0);
     if (key == 1) return g_use_pdl.exchange(value ? 1 : 0);
     if (key == 2) return g_route_in_kernel.exchange(value ? 1 : 0);
-    if (key == 3) return g_prefetch_down.exchange(value ? 1 : 0);
     return VIB3_ERR_UNSUPPORTED;
 }
 
@@ -370,10 +362,8 @@ extern "C" int vib3_launch_moe_layer_int4_paged_var(VIB3_MOE_ARGS, const int* nu
 
 // Router and experts of one token: the routing (ids, weights; device) is an OUTPUT.  Where the shapes allow,
 // the gate/up kernel routes the token in its own prologue (two launches for the layer); otherwise the router
-// is launched first (three).  workspace: EIGHT 32-bit words, zero before the first call: [0..3] as for
-// vib3_launch_router_topk_ex, [4] and [5] carry the router's announcement to the gate/up kernel (a generation and
-// the generation whose routing is in memory), [6] and [7] are spare; calls that share one must not overlap on the
-// GPU.  scores_buf: 3 * num_experts floats.
+// is launched first (three).  workspace: four 32-bit words, zero before the first call and left zero at
+// [0] and [2]; calls that share one must not overlap on the GPU.  scores_buf: 3 * num_experts floats.
 extern "C" int vib3_launch_moe_layer_routed_int4_paged(
     const void* x, int x_dtype, const void* router_w, int w_dtype, float* scores_buf, const float* bias,
     const float* logit_offset, unsigned short* ids_out, float* weights_out, int num_experts, int top_k, int scoring_mode,
@@ -384,7 +374,6 @@ extern "C" int vib3_launch_moe_layer_routed_int4_paged(
     RouterArgs r;
     if (int e = make_router_args(x, x_dtype, router_w, w_dtype, scores_buf, bias, logit_offset, ids_out, weights_out, hidden_dim,
                                  num_experts, top_k, scoring_mode, scaling_factor, normalize, exact_order, workspace, r)) return e;
-    r.announce = workspace + 4;
     return moe_layer_dispatch(3, nullptr, &r, x, x_dtype, page_table, num_experts, shared_pages, ids_out, weights_out, top_k,
                               shared_weight, act_scratch, out, out_accumulate, hidden_dim, expert_hidden_dim, pages_per_segment,
                               rows_per_page_gate_up, rows_per_page_down, group_size, status, stream);
@@ -543,7 +532,7 @@ extern "C" int vib3_launch_moe_layer_int4_paged_grouped(
     a.H = hidden_dim; a.I = expert_hidden_dim; a.P = pages_per_segment;
     a.rpp_gu = rows_per_page_gate_up; a.rpp_dn = rows_per_page_down; a.status = status;
     a.slot_token = pair_tokens + pair_begin; a.n_tokens = n_tokens; a.shared_token = shared_token;
-    a.x_stride = x_stride_bytes; a.out_stride = out_stride; a.slot_begin = pair_begin; a.prefetch_down = 0; a.route_announce = nullptr;
+    a.x_stride = x_stride_bytes; a.out_stride = out_stride; a.slot_begin = pair_begin;
     cudaStream_t st = (cudaStream_t)stream;
     int err = launch_gateup_pipelined(a, st);
     if (err) return err;

@@ -158,26 +158,7 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
                     ok = mbar_wait(reinterpret_cast<uint64_t*>(&rs.routing_ready), 0);
                     if (!ok) break;
                 } else {
-                    // Expert ids, weights and the optional slot count are outputs of earlier kernels.  A router that
-                    // announces its routing lets this warp go as soon as ids and weights are in memory, about a
-                    // microsecond before the router's launch has ended and been flushed; otherwise (or if the
-                    // announcement does not come within the bound) the dependency wait does it.
-                    bool announced = false;
-                    if (a.route_announce) {
-                        unsigned want, have = 0;
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(want) : "l"(a.route_announce) : "memory");
-                        if (lane == 0) {
-                            for (unsigned it = 0; it < (1u << 20); ++it) {
-                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(have) : "l"(a.route_announce + 1) : "memory");
-                                if (have == want) break;
-                                __nanosleep(200);
-                            }
-                        }
-                        have = __shfl_sync(0xffffffffu, have, 0);
-                        __threadfence();
-                        announced = have == want;
-                    }
-                    if (!announced) pdl_wait();
+                    pdl_wait();  // expert ids, weights and the optional slot count are outputs of earlier kernels
                     // Only now may the next kernel in the stream start: it reads the routing without waiting,
                     // and may overwrite nothing this kernel still reads.
                     pdl_trigger();
@@ -403,29 +384,6 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + st);
             ++n;
-        }
-    }
-    // This warp's share of the CTA's tiles is done.  The down kernel that follows gives CTA b the output rows
-    // cta_share(H): ask for those rows of every slot's down matrix to be brought into L2 now, so that the memory system
-    // keeps working across the boundary between the two kernels (its CTAs cannot be resident beside this one, and
-    // their rings start empty).  A hint only: nothing waits for it and nothing depends on it.
-    if (warp == 0 && a.prefetch_down && !grouped && !ROUTED) {
-        int h0, h1;
-        cta_share(a.H, h0, h1);
-        const unsigned dcode = (unsigned)a.I / 2, dscale = (unsigned)a.I / 16;
-        const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-        if (lane < slots && h1 > h0) {
-            const PageEntry* pg = slot_pages(a, lane);
-            for (int p = h0 / a.rpp_dn; pg && p <= (h1 - 1) / a.rpp_dn && p < a.P; ++p) {
-                const PageEntry e = pg[kSegDown * a.P + p];
-                const int r0 = max(h0, p * a.rpp_dn) - p * a.rpp_dn;
-                const int nr = min(h1, (p + 1) * a.rpp_dn) - max(h0, p * a.rpp_dn);
-                if (e.ptr == 0 || nr <= 0 || r0 + nr > e.row_count) continue;
-                const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + (size_t)r0 * dcode), "r"(nr * dcode) : "memory");
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;"
-                             ::"l"(base + (size_t)e.row_count * dcode + (size_t)r0 * dscale), "r"(nr * dscale) : "memory");
-            }
         }
     }
 }
@@ -721,6 +679,212 @@ __global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_pipe_kernel(MoeLa
     }
 }
 
+// ── down for wide experts: K split across warps ───────────────────────────────────────────────
+// When an expert's activations do not fit in two chunks per lane (I > 2048; the Mixtral shape has I = 14336) the
+// K range of a slot is split: warp (slot, ks) keeps chunks 64 ks + lane and 64 ks + 32 + lane of the slot's
+// activations in registers and forms, for every row of a tile, the partial sum over its 2048 columns; the combiner
+// adds a row's partials in ks order (fp32), rounds the row to fp16 as the reference's down projection does, and
+// accumulates the slots in plan order.  (The partial sums change the fp32 association against the direct-load
+// kernel, which runs one chain per lane over the whole row: results agree to rounding, not bit for bit.)
+// slots * KS consumer warps (at most 16), one combiner, one producer.  Tiles of 4 rows x all slots.
+// Not for grouped launches.
+constexpr int kDownKsRows = 4;
+
+__global__ void __launch_bounds__(kDownMaxThreads, 1) moe_down_ksplit_kernel(MoeLayerArgs a, int nstages, int KS) {
+    using MATH = MathQ16;
+    constexpr int NCH = 2;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int max_slots = a.top_k + (a.shared_pages ? 1 : 0);
+    a.top_k = active_top_k(a);
+    const int slots = a.top_k + (a.shared_pages ? 1 : 0);
+    const unsigned code_row = (unsigned)a.I / 2, scale_row = (unsigned)a.I / 16;
+    const int cwarps = slots * KS;
+    const int producer_warp = (int)(blockDim.x >> 5) - 1;
+    const int combiner_warp = producer_warp - 1;
+    const unsigned slot_bytes = kDownKsRows * (code_row + scale_row);
+    const unsigned stage_bytes = max_slots * slot_bytes;
+
+    PageEntry* tab = reinterpret_cast<PageEntry*>(smem_raw);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tab + max_slots * a.P);
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* yfull = empty + kMaxStages;
+    uint64_t* yempty = yfull + kDownYStages;
+    uint64_t* act_read = yempty + kDownYStages;
+    float* wts = reinterpret_cast<float*>(act_read + 1);
+    float* ybuf = wts + kMaxSlots;   // [y stage][row][kMaxSlots]: partial (slot, ks) at slot * KS + ks
+    unsigned char* stages = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(ybuf + kDownYStages * kDownKsRows * kMaxSlots) + 127) & ~(uintptr_t)127);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < nstages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, max(cwarps, 1));
+        }
+        for (int s = 0; s < kDownYStages; ++s) {
+            mbar_init(yfull + s, max(cwarps, 1));
+            mbar_init(yempty + s, 1);
+        }
+        mbar_init(act_read, max(cwarps, 1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // (the routing is complete and visible: this kernel is launched only after every thread of the gate/up kernel has
+    // passed its own wait for the router)
+    for (int i = tid; i < slots * a.P; i += blockDim.x) {
+        const int s = i / a.P, p = i - s * a.P;
+        const PageEntry* pg = slot_pages(a, s);
+        PageEntry e{0, 0, 0, 0};
+        if (pg) e = pg[kSegDown * a.P + p];
+        tab[i] = e;
+    }
+    for (int s = tid; s < slots; s += blockDim.x) wts[s] = s < a.top_k ? __ldcg(a.expert_weights + s) : a.shared_weight;
+    __syncthreads();
+
+    int g0, g1;
+    cta_share(a.H, g0, g1);
+    if (slots == 0) {
+        pdl_wait();
+        if (!a.out_accumulate)
+            for (int r = g0 + tid; r < g1; r += blockDim.x) a.out[r] = 0.f;
+        return;
+    }
+    if (warp < combiner_warp && warp >= cwarps) return;
+
+    if (warp == producer_warp) {
+        TileWalk walk(g0, g1, a.H, a.rpp_dn, kDownKsRows);
+        Tile t;
+        int n = 0;
+        bool ok = true;
+        while (walk.next(t)) {
+            const int st = n % nstages;
+            if (n >= nstages) ok = mbar_wait(empty + st, ((n / nstages) - 1) & 1);
+            if (!ok) break;
+            unsigned char* sb = stages + (size_t)st * stage_bytes;
+            // lane k < 2 * slots issues copy k of the tile (slot k / 2: codes for even k, scales for odd k)
+            const int s = lane >> 1;
+            PageEntry e{0, 0, 0, 0};
+            if (s < slots) e = tab[s * a.P + t.page];
+            const bool mine = s < slots && e.ptr != 0 && t.rin + t.nrows <= e.row_count;
+            const unsigned bytes = mine ? ((lane & 1) ? t.nrows * scale_row : t.nrows * code_row) : 0u;
+            unsigned tx = bytes;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) tx += __shfl_xor_sync(0xffffffffu, tx, o);
+            if (lane == 0) {
+                if (tx) mbar_expect_tx(full + st, tx);
+                else mbar_arrive(full + st);
+            }
+            __syncwarp();
+            if (bytes) {
+                const unsigned char* base = reinterpret_cast<const unsigned char*>(e.ptr);
+                if (lane & 1) bulk_load(sb + s * slot_bytes + kDownKsRows * code_row, base + (size_t)e.row_count * code_row + (size_t)t.rin * scale_row, bytes, full + st);
+                else bulk_load(sb + s * slot_bytes, base + (size_t)t.rin * code_row, bytes, full + st);
+            }
+            ++n;
+        }
+        if (!ok && lane == 0) flag(a.status, kStatusTimeout);
+        if (lane == 0)
+            for (int k = max(0, n - nstages); k < n; ++k)
+                if (!mbar_wait(full + (k % nstages), (k / nstages) & 1)) flag(a.status, kStatusTimeout);
+        return;
+    }
+
+    if (warp == combiner_warp) {
+        if (lane == 0) {
+            if (!mbar_wait(act_read, 0)) flag(a.status, kStatusTimeout);
+            pdl_trigger();
+        }
+        __syncwarp();
+        TileWalk walk(g0, g1, a.H, a.rpp_dn, kDownKsRows);
+        Tile t;
+        int n = 0;
+        while (walk.next(t)) {
+            const int ys = n % kDownYStages;
+            if (!mbar_wait(yfull + ys, (n / kDownYStages) & 1)) {
+                if (lane == 0) flag(a.status, kStatusTimeout);
+                return;
+            }
+            if (lane < t.nrows) {
+                const float* yb = ybuf + ys * (kDownKsRows * kMaxSlots) + lane * kMaxSlots;
+                float out = 0.f;
+                for (int s = 0; s < slots; ++s) {
+                    float y = 0.f;
+                    for (int k = 0; k < KS; ++k) y += yb[s * KS + k];
+                    out = fmaf(wts[s], __half2float(__float2half_rn(y)), out);
+                }
+                const int r = t.row + lane;
+                if (a.out_accumulate) a.out[r] += out;
+                else a.out[r] = out;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(yempty + ys);
+            ++n;
+        }
+        return;
+    }
+
+    // ── consumers: warp (s, ks) ──
+    const int s = warp / KS, ks = warp - s * KS;
+    pdl_wait();  // the activations are the gate/up kernel's output
+    uint4 xv[NCH][4];
+    float sx[NCH];
+    int sq8[NCH];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+        MATH::quantize_chunk(a.act + (size_t)act_slot(a, s) * a.I + (size_t)(64 * ks + lane + 32 * i) * 32, xv[i], sx[i], sq8[i]);
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) asm volatile("" ::"r"(sq8[i]));
+    __syncwarp();
+    if (lane == 0) mbar_arrive(act_read);
+
+    const uint32_t stages_addr = smem_u32(stages);
+    const uint32_t code_base = s * slot_bytes + (64 * ks + lane) * 16;
+    const uint32_t scale_base = s * slot_bytes + kDownKsRows * code_row + (64 * ks + lane) * 2;
+    TileWalk walk(g0, g1, a.H, a.rpp_dn, kDownKsRows);
+    Tile t;
+    int n = 0;
+    while (walk.next(t)) {
+        const int st = n % nstages;
+        if (!mbar_wait(full + st, (n / nstages) & 1)) {
+            if (lane == 0) flag(a.status, kStatusTimeout);
+            return;
+        }
+        const PageEntry e = tab[s * a.P + t.page];
+        const bool present = e.ptr != 0 && t.rin + t.nrows <= e.row_count;
+        const uint32_t sb = stages_addr + st * stage_bytes;
+        float y[kDownKsRows];
+#pragma unroll
+        for (int r = 0; r < kDownKsRows; ++r) {
+            float acc = 0.f;
+            if (r < t.nrows && present) {
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const uint4 q = lds128(sb + code_base + r * code_row + i * 512);
+                    const float sc = scale_to_f32(lds16(sb + scale_base + r * scale_row + i * 64));
+                    acc = MATH::chunk_r(q, sc, xv[i], sx[i], sq8[i], acc);
+                }
+            }
+            y[r] = acc;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + st);
+#pragma unroll
+        for (int r = 0; r < kDownKsRows; ++r) y[r] = warp_sum(y[r]);
+        if (!present && ks == 0 && lane == 0) flag(a.status, kStatusMissingPage);
+        const int ys = n % kDownYStages;
+        if (n >= kDownYStages && !mbar_wait(yempty + ys, ((n / kDownYStages) - 1) & 1)) {
+            if (lane == 0) flag(a.status, kStatusTimeout);
+            return;
+        }
+        if (lane == 0) {
+            float* yb = ybuf + ys * (kDownKsRows * kMaxSlots);
+#pragma unroll
+            for (int r = 0; r < kDownKsRows; ++r) yb[r * kMaxSlots + warp] = y[r];
+            mbar_arrive(yfull + ys);
+        }
+        ++n;
+    }
+}
+
 // ── host side ──────────────────────────────────────────────────────────────────────────────
 
 static bool pipe_shape_ok(const MoeLayerArgs& a) {
@@ -821,9 +985,22 @@ int launch_down_pipelined(const MoeLayerArgs& a, cudaStream_t st) {
     if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
     const int nchunks = a.I / kGroupSize;
-    // register-resident activations: at most two chunks per lane
-    if (nchunks != 32 && nchunks != 64) return VIB3_ERR_UNSUPPORTED;
     const size_t row_bytes = (size_t)a.I / 2 + (size_t)a.I / 16;
+    // register-resident activations: at most two chunks per lane; wider experts split K across warps
+    if (nchunks > 64) {
+        const int KS = nchunks / 64;
+        if (nchunks % 64 || a.slot_token || slots * KS > 16 || slots * KS > kMaxSlots) return VIB3_ERR_UNSUPPORTED;
+        const size_t fixed_ks = (size_t)slots * a.P * sizeof(PageEntry) + (2 * (kMaxStages + kDownYStages) + 1) * sizeof(uint64_t) +
+                                kMaxSlots * sizeof(float) + kDownYStages * kDownKsRows * kMaxSlots * sizeof(float) + 256;
+        const size_t stage_ks = (size_t)slots * kDownKsRows * row_bytes;
+        const int nst = pick_stages(fixed_ks, stage_ks, 2);
+        if (nst == 0) return VIB3_ERR_UNSUPPORTED;
+        static const int attr = set_max_smem(moe_down_ksplit_kernel);
+        if (attr) return attr;
+        const int grid_ks = min(sm_count(), (a.H + kDownKsRows - 1) / kDownKsRows);
+        return launch_pipe(moe_down_ksplit_kernel, grid_ks, (slots * KS + 2) * 32, fixed_ks + (size_t)nst * stage_ks, st, a, nst, KS);
+    }
+    if (nchunks != 32 && nchunks != 64) return VIB3_ERR_UNSUPPORTED;
     const size_t fixed = (size_t)slots * a.P * sizeof(PageEntry) + (2 * (kMaxStages + kDownYStages) + 1) * sizeof(uint64_t) +
                          2 * kMaxSlots * sizeof(float) + kDownYStages * kDownTileRows * kMaxSlots * sizeof(float) + 256;
     if (slots > 9) {

@@ -203,11 +203,6 @@ __global__ void __launch_bounds__(kRowsThreads) router_rows_kernel(RouterArgs a,
     const int e0 = blockIdx.x * kRowsPerCta;
     const int nrows = min(kRowsPerCta, a.E - e0);
     if (tid == 0) {
-        if (a.announce && blockIdx.x == 0) {
-            // before any dependent can be launched (they need every CTA's trigger, this one's included)
-            atomicAdd(a.announce, 1u);
-            __threadfence();
-        }
         pdl_trigger();
         for (int r = 0; r < nrows; ++r) mbar_init(full + r, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -273,20 +268,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_select_kernel(RouterArg
     pdl_wait();   // the logits are the rows kernel's output
     __syncthreads();
     router_finish(a, sm, ring, threadIdx.x, kRouterThreads, a.mode != 0, true, nullptr, nullptr);
-    if (a.announce) {
-        // ids and weights are stored (by lanes of the first warp): make them visible, then say so
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned gen;
-            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(a.announce) : "memory");
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.announce + 1), "r"(gen) : "memory");
-        }
-    }
 }
-
-// Whether the last router launch of this host thread announces its routing through RouterArgs::announce.
-static thread_local bool t_router_announces = false;
 
 template <class K, class... Args>
 static int launch_router_pdl(K kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, Args... args) {
@@ -316,14 +298,11 @@ static int launch_rows_t(const RouterArgs& a, cudaStream_t st, int n_tokens) {
     const dim3 grid((a.E + kRowsPerCta - 1) / kRowsPerCta);
     if (int e = launch_router_pdl(router_rows_kernel<XD, WD>, grid, kRowsThreads, smem, st, a, n_tokens, tok_chunk)) return e;
     if (a.counter == nullptr) return VIB3_OK;   // logits only
-    const int e = launch_router_pdl(router_select_kernel, dim3(n_tokens), kRouterThreads, 0, st, a);
-    t_router_announces = e == 0 && a.announce != nullptr && n_tokens == 1;
-    return e;
+    return launch_router_pdl(router_select_kernel, dim3(n_tokens), kRouterThreads, 0, st, a);
 }
 
 template <int XD, int WD>
 static int launch_router_t(const RouterArgs& a, cudaStream_t st, int n_tokens) {
-    t_router_announces = false;
     if (XD >= 0) {
         const int e = launch_rows_t<XD < 0 ? 0 : XD, WD>(a, st, n_tokens);
         if (e != VIB3_ERR_UNSUPPORTED) return e;
@@ -408,11 +387,7 @@ extern "C" int vib3_launch_router_topk(const void* x_f32, const void* W_f16, flo
 }
 
 namespace vib3 {
-int launch_router_args(const RouterArgs& a, cudaStream_t st, bool* announces) {
-    const int e = launch_router(a, st);
-    if (announces) *announces = t_router_announces;
-    return e;
-}
+int launch_router_args(const RouterArgs& a, cudaStream_t st) { return launch_router(a, st); }
 }  // namespace vib3
 
 // Fill and validate the arguments of the single-launch router (shared with the expert kernel that routes

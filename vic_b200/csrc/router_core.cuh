@@ -37,10 +37,6 @@ struct RouterArgs {
     int ids_stride;      // entries
     int weights_stride;  // entries
     int counter_stride;  // words
-    // Optional (one token, rows-resident form): two words that tell a dependent kernel when the routing is in memory
-    // without waiting for this launch to end.  [0]: generation, advanced when the router starts; [1]: set to the
-    // generation once ids and weights are stored.
-    unsigned int* announce;
 };
 
 // The arguments of token blockIdx.y of a batched launch.

@@ -29,7 +29,7 @@ class MoeDecoder:
         self.scores = torch.zeros(3 * sh.num_experts, dtype=torch.float32, device=dev)
         self.ids = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.int16, device=dev)
         self.weights = torch.zeros(MAX_ACTIVE_EXPERTS, dtype=torch.float32, device=dev)
-        self.workspace = torch.zeros(8, dtype=torch.int32, device=dev)   # (the routed layer call wants eight words)
+        self.workspace = torch.zeros(4, dtype=torch.int32, device=dev)
         self.act = torch.zeros((sh.top_k + 1) * sh.intermediate, dtype=torch.float16, device=dev)
         self.out = torch.zeros(sh.hidden, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
