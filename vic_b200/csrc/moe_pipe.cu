@@ -344,7 +344,7 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
                     const uint32_t gs_addr = sb + 2 * kTileRows * code_row + p0 * scale_row + lane * 2;
                     const uint32_t us_addr = gs_addr + kTileRows * scale_row;
                     if (NCH > 0) {
-#pragma unroll
+#pragma unroll 1
                         for (int i = 0; i < NCH; ++i) {
                             const uint4 q[4] = {lds128(g_addr + i * 512), lds128(u_addr + i * 512),
                                                 lds128(g_addr + code_row + i * 512), lds128(u_addr + code_row + i * 512)};

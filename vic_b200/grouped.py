@@ -127,7 +127,7 @@ def bench_c3(model: SyntheticMoe, stream, peak_gbs: float, token_counts=(1, 8, 3
     off = torch.from_numpy(zipf_logit_offset(sh.num_experts, 7)).to(dev)
     g = torch.Generator(device=dev).manual_seed(1234 + 3)
     out = {"workload": "C3 kimi-k2.5-shape MoE layer, grouped multi-token decode, router logits skewed by a Zipf(1.1) offset",
-           "note": "HBM-bound by construction (SURVEY: 90 GFLOP of tensor work against up to 7 GB of distinct expert weights at 128 tokens); "
+           "note": "HBM-bound by construction (90 GFLOP of tensor work against up to 7 GB of distinct expert weights at 128 tokens); "
                    "figure of merit = bytes over the distinct experts per second", "cases": []}
     from .synth import synth_activation
     for T in token_counts:
