@@ -494,7 +494,7 @@ __device__ __forceinline__ void stage_activation(typename MATH::XS* dst, const v
 }
 template <>
 __device__ __forceinline__ void stage_activation<MathQ16>(unsigned char* dst, const void* x, int dtype, int n, int tid, int nthreads) {
-    stage_x_q16<4>(dst, x, dtype, n, tid, nthreads);
+    stage_x_q16<2>(dst, x, dtype, n, tid, nthreads);   // (two items per thread and trip: less code for a freshly launched kernel to fetch)
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
