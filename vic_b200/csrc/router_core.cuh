@@ -148,9 +148,11 @@ __device__ __forceinline__ float warp_total(float v) {
 // found by ONE warp: lane l keeps the keys of experts l, l + 32, ... in registers; a round is two
 // warp-wide integer reductions (largest key, then lowest index holding it).  Lane i returns the
 // i-th selected expert (-1 when fewer exist).
-__device__ inline int warp_select(const RouterArgs& a, const TopKSmem& sm, int nsel) {
+// kPerLane: keys per lane, at least E / 32 (the loops over them are unrolled: the narrower form is less code for a
+// freshly launched kernel to fetch).
+template <int kPerLane>
+__device__ __forceinline__ int warp_select_n(const RouterArgs& a, const TopKSmem& sm, int nsel) {
     const int lane = threadIdx.x & 31;
-    constexpr int kPerLane = kRouterMaxExperts / 32;
     unsigned key[kPerLane];
 #pragma unroll
     for (int j = 0; j < kPerLane; ++j) {
@@ -174,6 +176,9 @@ __device__ inline int warp_select(const RouterArgs& a, const TopKSmem& sm, int n
         if (lane == round) mine = best ? (int)who : -1;
     }
     return mine;
+}
+__device__ inline int warp_select(const RouterArgs& a, const TopKSmem& sm, int nsel) {
+    return a.E <= 384 ? warp_select_n<12>(a, sm, nsel) : warp_select_n<kRouterMaxExperts / 32>(a, sm, nsel);
 }
 
 
