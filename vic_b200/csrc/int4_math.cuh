@@ -217,6 +217,15 @@ __device__ __forceinline__ unsigned short lds16(uint32_t addr) {
 // Shared-memory layout of a staged chunk (80 bytes): for word j = 0..3 of the code load (columns
 // 8j..8j+7) one uint4 {hi of even columns, hi of odd columns, lo of even columns, lo of odd
 // columns}, then the float sx and the int 8 * sum q.
+// Byte B (0: low, 1: second) of each of four integers as the four bytes of a word, a in the lowest: three byte permutes
+// (the shift-mask-or form is eleven instructions, and the quantisation code runs once, cold, at the start of a kernel).
+template <int B>
+__device__ __forceinline__ uint32_t pack_bytes(int a, int b, int c, int d) {
+    const uint32_t lo = __byte_perm((uint32_t)a, (uint32_t)b, B == 0 ? 0x0040u : 0x0051u);
+    const uint32_t hi = __byte_perm((uint32_t)c, (uint32_t)d, B == 0 ? 0x0040u : 0x0051u);
+    return __byte_perm(lo, hi, 0x5410u);
+}
+
 struct MathQ16 {
     using XS = unsigned char;
     static constexpr int kStride = 80;  // bytes per staged chunk
@@ -309,10 +318,10 @@ struct MathQ16 {
                 q[k] = max(-32512, min(32512, __float2int_rn(v[8 * j + k] * inv)));
                 sq += q[k];
             }
-            xv[j].x = (uint32_t)((q[0] >> 8) & 0xFF) | ((uint32_t)((q[2] >> 8) & 0xFF) << 8) | ((uint32_t)((q[4] >> 8) & 0xFF) << 16) | ((uint32_t)((q[6] >> 8) & 0xFF) << 24);
-            xv[j].y = (uint32_t)((q[1] >> 8) & 0xFF) | ((uint32_t)((q[3] >> 8) & 0xFF) << 8) | ((uint32_t)((q[5] >> 8) & 0xFF) << 16) | ((uint32_t)((q[7] >> 8) & 0xFF) << 24);
-            xv[j].z = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[2] & 0xFF) << 8) | ((uint32_t)(q[4] & 0xFF) << 16) | ((uint32_t)(q[6] & 0xFF) << 24);
-            xv[j].w = (uint32_t)(q[1] & 0xFF) | ((uint32_t)(q[3] & 0xFF) << 8) | ((uint32_t)(q[5] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+            xv[j].x = pack_bytes<1>(q[0], q[2], q[4], q[6]);
+            xv[j].y = pack_bytes<1>(q[1], q[3], q[5], q[7]);
+            xv[j].z = pack_bytes<0>(q[0], q[2], q[4], q[6]);
+            xv[j].w = pack_bytes<0>(q[1], q[3], q[5], q[7]);
         }
         sx = m * (1.0f / 32512.f);
         sq8 = 8 * sq;
@@ -471,10 +480,10 @@ __device__ __forceinline__ void stage_x_q16(unsigned char* dst, const void* x, i
             sq += __shfl_xor_sync(0xffffffffu, sq, 1);
             sq += __shfl_xor_sync(0xffffffffu, sq, 2);
             uint4 o;
-            o.x = (uint32_t)((q[0] >> 8) & 0xFF) | ((uint32_t)((q[2] >> 8) & 0xFF) << 8) | ((uint32_t)((q[4] >> 8) & 0xFF) << 16) | ((uint32_t)((q[6] >> 8) & 0xFF) << 24);
-            o.y = (uint32_t)((q[1] >> 8) & 0xFF) | ((uint32_t)((q[3] >> 8) & 0xFF) << 8) | ((uint32_t)((q[5] >> 8) & 0xFF) << 16) | ((uint32_t)((q[7] >> 8) & 0xFF) << 24);
-            o.z = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[2] & 0xFF) << 8) | ((uint32_t)(q[4] & 0xFF) << 16) | ((uint32_t)(q[6] & 0xFF) << 24);
-            o.w = (uint32_t)(q[1] & 0xFF) | ((uint32_t)(q[3] & 0xFF) << 8) | ((uint32_t)(q[5] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+            o.x = pack_bytes<1>(q[0], q[2], q[4], q[6]);
+            o.y = pack_bytes<1>(q[1], q[3], q[5], q[7]);
+            o.z = pack_bytes<0>(q[0], q[2], q[4], q[6]);
+            o.w = pack_bytes<0>(q[1], q[3], q[5], q[7]);
             if (live) {
                 unsigned char* chunk = dst + (size_t)c * MathQ16::kStride;
                 *reinterpret_cast<uint4*>(chunk + 16 * jj) = o;
