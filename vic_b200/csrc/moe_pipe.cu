@@ -96,7 +96,10 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
     int e0 = 0, e1 = 0;  // this CTA's router rows
     if (ROUTED) cta_share(r.E, e0, e1);
     const int nrows = e1 - e0;
-    if (tid == 0) {
+    // A launch that does not route itself: the producer warp initialises the barriers and copies the shared expert's
+    // table itself, and starts the first copies at once — the weights need neither the token nor the other warps;
+    // the consumers meet it (and each other) at a named barrier once the token is staged.
+    if (ROUTED ? tid == 0 : tid == kConsumerWarps * 32) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, kGroupWarps);
@@ -126,9 +129,18 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
         const int n16 = (a.H * (a.x_dtype == X_F32 ? 4 : 2)) >> 4;
         for (int i = tid; i < n16; i += kConsumerWarps * 32) reinterpret_cast<uint4*>(xraw)[i] = __ldg(reinterpret_cast<const uint4*>(a.x) + i);
     }
-    if (a.shared_pages)
-        for (int i = tid; i < 2 * a.P; i += blockDim.x) tab[cap_k * 2 * a.P + i] = a.shared_pages[i];
-    __syncthreads();
+    if (ROUTED) {
+        if (a.shared_pages)
+            for (int i = tid; i < 2 * a.P; i += blockDim.x) tab[cap_k * 2 * a.P + i] = a.shared_pages[i];
+        __syncthreads();
+    } else if (warp == kConsumerWarps) {
+        if (a.shared_pages)
+            for (int i = lane; i < 2 * a.P; i += 32) tab[cap_k * 2 * a.P + i] = a.shared_pages[i];
+        __syncwarp();
+        asm volatile("bar.arrive 3, %0;" ::"r"(kPipeThreads) : "memory");
+    } else {
+        asm volatile("bar.sync 3, %0;" ::"r"(kPipeThreads) : "memory");
+    }
 
     int n = 0;  // tiles of this CTA so far, over both passes (producer and consumers count alike)
     const int first_pass = (a.shared_pages && !grouped) ? 0 : 1;
