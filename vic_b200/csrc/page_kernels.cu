@@ -259,19 +259,21 @@ extern "C" int vib3_launch_residual_add_f32_f32(void* acc_f32, const void* layer
 // Sum of squares: 256 partial sums (fused multiply-add), then a halving tree in shared memory, as the reference
 // kernel (cuda/src/kernels.cu:921-953); square root and reciprocal are IEEE (the reference's CPU path,
 // src/compute/kernels.rs:2591-2603; its CUDA build uses the fast-math approximations).
-__device__ __forceinline__ float block_sum_256(float v, float* red) {
-    const int tid = threadIdx.x;
+// Sum over the CTA (a whole number of warps, at most 32): butterfly inside each warp, then the warps' sums in
+// warp order by every thread — the same value, bit for bit, in all threads.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int tid = threadIdx.x, nwarps = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     __syncthreads();   // (red may still be read from an earlier call)
-    red[tid] = v;
+    if ((tid & 31) == 0) red[tid >> 5] = v;
     __syncthreads();
-    for (int s = 128; s > 0; s >>= 1) {
-        if (tid < s) red[tid] += red[tid + s];
-        __syncthreads();
-    }
-    return red[0];
+    float s = 0.f;
+    for (int w = 0; w < nwarps; ++w) s += red[w];
+    return s;
 }
-__device__ __forceinline__ float block_inv_rms_256(float ss, int H, float eps, float* red) {
-    const float rms = sqrtf(block_sum_256(ss, red) / (float)H + eps);
+__device__ __forceinline__ float block_inv_rms(float ss, int H, float eps, float* red) {
+    const float rms = sqrtf(block_sum(ss, red) / (float)H + eps);
     return 1.0f / rms;
 }
 
@@ -281,11 +283,13 @@ __device__ __forceinline__ void store_x(void* out, int dtype, int d, float v) {
     else reinterpret_cast<__nv_bfloat16*>(out)[d] = __float2bfloat16_rn(v);
 }
 
-// One CTA of 256 threads per token: hidden += delta (optional), x = cast(hidden * inv_rms * weight).
-// VEC: H a multiple of 4 and at most 8192, 16-byte aligned rows: a thread keeps its (at most eight) 4-column
-// items in registers — every load is requested before anything is stored, one pass over the row.
+// One CTA per token: hidden += delta (optional), x = cast(hidden * inv_rms * weight).
+// VEC (1024 threads): H a multiple of 4 and at most 8192, 16-byte aligned rows: a thread keeps its (at most two)
+// 4-column items in registers — every load is requested before anything is stored, one pass over the row.  Two items
+// per thread rather than eight in a quarter of the threads: the kernel runs once per layer on cold instruction caches,
+// and its time is the code it has to fetch.  Otherwise 256 threads and three passes.
 template <bool VEC>
-__global__ void __launch_bounds__(256) residual_rms_norm_kernel(float* __restrict__ hidden, int hidden_stride, const void* __restrict__ delta,
+__global__ void __launch_bounds__(VEC ? 1024 : 256) residual_rms_norm_kernel(float* __restrict__ hidden, int hidden_stride, const void* __restrict__ delta,
                                                                 int delta_dtype, int delta_stride, const float* __restrict__ delta2,
                                                                 int delta2_stride, const __half* __restrict__ weight, float eps,
                                                                 int center, void* __restrict__ x_out, int x_dtype, int x_stride, int H) {
@@ -296,13 +300,13 @@ __global__ void __launch_bounds__(256) residual_rms_norm_kernel(float* __restric
     const float* d2row = delta2 ? delta2 + (size_t)t * delta2_stride : nullptr;
     unsigned char* xrow = reinterpret_cast<unsigned char*>(x_out) + (size_t)t * x_stride;
     if (VEC) {
-        constexpr int kItems = 8;
+        constexpr int kItems = 2, kThreads = 1024;
         const int n4 = H >> 2;
         float4 h[kItems], dl[kItems];
         uint2 wv[kItems];
 #pragma unroll
         for (int i = 0; i < kItems; ++i) {
-            const int it = tid + 256 * i;
+            const int it = tid + kThreads * i;
             h[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             dl[i] = h[i];
             wv[i] = make_uint2(0x3C003C00u, 0x3C003C00u);   // 1.0
@@ -337,22 +341,22 @@ __global__ void __launch_bounds__(256) residual_rms_norm_kernel(float* __restric
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < kItems; ++i) sum += (h[i].x + h[i].y) + (h[i].z + h[i].w);
-            mean = block_sum_256(sum, red) / (float)H;
+            mean = block_sum(sum, red) / (float)H;
         }
         float ss = 0.f;
 #pragma unroll
         for (int i = 0; i < kItems; ++i) {
-            if (tid + 256 * i < n4) {
+            if (tid + kThreads * i < n4) {
                 ss = fmaf(h[i].x - mean, h[i].x - mean, ss);
                 ss = fmaf(h[i].y - mean, h[i].y - mean, ss);
                 ss = fmaf(h[i].z - mean, h[i].z - mean, ss);
                 ss = fmaf(h[i].w - mean, h[i].w - mean, ss);
             }
         }
-        const float inv_rms = block_inv_rms_256(ss, H, eps, red);
+        const float inv_rms = block_inv_rms(ss, H, eps, red);
 #pragma unroll
         for (int i = 0; i < kItems; ++i) {
-            const int it = tid + 256 * i;
+            const int it = tid + kThreads * i;
             if (it < n4) {
                 if (drow || d2row) reinterpret_cast<float4*>(row)[it] = h[i];
                 const __half2 w0 = *reinterpret_cast<const __half2*>(&wv[i].x), w1 = *reinterpret_cast<const __half2*>(&wv[i].y);
@@ -372,11 +376,11 @@ __global__ void __launch_bounds__(256) residual_rms_norm_kernel(float* __restric
         if (center) {
             float sum = 0.f;
             for (int d = tid; d < H; d += 256) sum += row[d];
-            mean = block_sum_256(sum, red) / (float)H;
+            mean = block_sum(sum, red) / (float)H;
         }
         float ss = 0.f;
         for (int d = tid; d < H; d += 256) ss = fmaf(row[d] - mean, row[d] - mean, ss);
-        const float inv_rms = block_inv_rms_256(ss, H, eps, red);
+        const float inv_rms = block_inv_rms(ss, H, eps, red);
         for (int d = tid; d < H; d += 256) {
             float v = (row[d] - mean) * inv_rms;
             if (weight) v *= __half2float(weight[d]);
@@ -392,7 +396,7 @@ static int launch_norm(float* hidden, int hidden_stride, const void* delta, int 
                      (delta_stride & 15) == 0 && ((uintptr_t)delta2 & 15) == 0 && (delta2_stride & 3) == 0 && ((uintptr_t)weight & 7) == 0 &&
                      ((uintptr_t)x_out & 15) == 0 && (x_stride & 15) == 0;
     if (vec)
-        residual_rms_norm_kernel<true><<<n_tokens, 256, 0, st>>>(hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2, delta2_stride,
+        residual_rms_norm_kernel<true><<<n_tokens, 1024, 0, st>>>(hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2, delta2_stride,
                                                                  (const __half*)weight, eps, center, x_out, x_dtype, x_stride, H);
     else
         residual_rms_norm_kernel<false><<<n_tokens, 256, 0, st>>>(hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2, delta2_stride,
