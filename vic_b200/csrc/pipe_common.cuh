@@ -88,11 +88,18 @@ struct TileWalk {
     }
 };
 
+// This CTA's contiguous share of `total` rows.  (32-bit arithmetic where the products fit — they do for every shape
+// the staged kernels accept: a 64-bit division is a subroutine of some hundred instructions, and this runs, cold, on
+// the path between the arrival of the routing and the first copy of the second pass.)
 __device__ __forceinline__ void cta_share(int total, int& begin, int& end) {
-    const long long b = (long long)total * blockIdx.x / gridDim.x;
-    const long long e = (long long)total * (blockIdx.x + 1) / gridDim.x;
-    begin = (int)b;
-    end = (int)e;
+    const unsigned g = gridDim.x, b = blockIdx.x;
+    if ((unsigned)total <= 0xFFFFFFFFu / g) {
+        begin = (int)((unsigned)total * b / g);
+        end = (int)((unsigned)total * (b + 1) / g);
+    } else {
+        begin = (int)((long long)total * b / g);
+        end = (int)((long long)total * (b + 1) / g);
+    }
 }
 
 // Ring bookkeeping.  Tile n of a CTA uses stage n % nstages (use number u = n / nstages of that
