@@ -10,8 +10,8 @@ namespace vib3 {
 constexpr int kRouterMaxExperts = 512;  // MAX_EXPERTS, src/core/types.rs:20
 constexpr int kRouterMaxTopK = 16;      // MAX_ACTIVE_EXPERTS, src/core/types.rs:26
 constexpr int kRouterXMax = 8192;       // widest activation vector staged in shared memory
-constexpr int kSeqCands = 2;            // near-tied experts recomputed side by side (more take further rounds)
-constexpr int kSeqBlock = 1024;         // products per hand-over between the warps of a recomputation
+constexpr int kSeqCands = 4;            // near-tied experts recomputed side by side (more take further rounds)
+constexpr int kSeqBlock = 512;          // products per hand-over between the warps of a recomputation
 constexpr unsigned kRouterSpinLimit = 1u << 22;
 
 enum WDType : int { W_F16 = 0, W_F32 = 1 };
