@@ -108,3 +108,19 @@ def test_stack_placement_rules_and_imbalance_bound():
     assert 2.8 < b1["speedup_bound"] < 3.4 and abs(b1["distinct_experts"] - 8) < 1e-9
     assert 6.2 < b32["speedup_bound"] < 7.0 and 180 < b32["distinct_experts"] < 195
     assert ep.imbalance_bound(384, 8, 1, 4, trials=10)["speedup_bound"] == 1.0
+
+
+def test_peer_exchange_buffer_layout():
+    """The parts of a rank's peer-exchange buffer are aligned for 16-byte stores and do not overlap, at every world size."""
+    from vic_b200 import ep
+    from vic_b200.core_types import KIMI
+    _, _, msg = ep.message_layout(KIMI.hidden)
+    assert msg % 16 == 0
+    for world in (2, 3, 4, 8):
+        recv, rows, f1, f2, total = ep.peer_layout(KIMI.hidden, msg, world)
+        parts = [(recv, world * msg), (rows, world * KIMI.hidden * 4), (f1, world * 4), (f2, world * 4)]
+        for off, size in parts:
+            assert off % 256 == 0
+        for (a, sa), (b, _) in zip(parts, parts[1:]):
+            assert a + sa <= b
+        assert parts[-1][0] + parts[-1][1] <= total

@@ -119,6 +119,18 @@ class _DevMem:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
 
 
+def peer_layout(hidden: int, msg_bytes: int, world: int) -> Tuple[int, int, int, int, int]:
+    """Byte offsets (messages, partial rows, message flags, row flags) and total size of a rank's exchange buffer:
+    [G messages][G rows of H fp32][G flags][G flags], every part 256-byte aligned."""
+    def up(v):
+        return (v + 255) // 256 * 256
+    recv_off = 0
+    rows_off = up(world * msg_bytes)
+    flags1_off = rows_off + up(world * hidden * 4)
+    flags2_off = flags1_off + up(world * 4)
+    return recv_off, rows_off, flags1_off, flags2_off, flags2_off + up(world * 4)
+
+
 class PeerExchange:
     """The two exchanges of a decode step over peer memory instead of NCCL (csrc/ep_peer.cu): every rank maps every
     other rank's exchange buffer; a message or a partial row is stored straight into the peers' buffers and followed
@@ -130,11 +142,7 @@ class PeerExchange:
         from .lib import check, lib
         self.rank, self.world, self.group = rank, world, group
         self.msg_bytes, self.hidden = msg_bytes, hidden
-        self.recv_off = 0
-        self.rows_off = (world * msg_bytes + 255) // 256 * 256
-        self.flags1_off = self.rows_off + (world * hidden * 4 + 255) // 256 * 256
-        self.flags2_off = self.flags1_off + 256 * ((world * 4 + 255) // 256)
-        self.nbytes = self.flags2_off + 256 * ((world * 4 + 255) // 256)
+        self.recv_off, self.rows_off, self.flags1_off, self.flags2_off, self.nbytes = peer_layout(hidden, msg_bytes, world)
         handle = (C.c_ubyte * 64)()
         ptr = C.c_void_p()
         check("peer_alloc", lib().vib3_peer_alloc(self.nbytes, C.byref(ptr), handle))
