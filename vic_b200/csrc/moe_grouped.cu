@@ -78,26 +78,18 @@ struct GroupedWork {
 
 struct Unit;
 struct GroupedArgs {
-    const PageEntry* page_table;    // [E][3][P]
-    const PageEntry* shared_pages;  // [3][P] or null
-    const unsigned char* pool_base;
     const GroupedWork* work;
-    const int* active;       // [n_active] expert ids, E = the shared expert; most tokens first
-    const int* counts;       // [E + 1]
-    const int* offsets;      // [E + 1] first sorted pair of the expert
     __half* act;             // [pairs][I], K order permuted
     __half* y;               // [pairs][H]
     const Unit* units_gu;    // [n_active * tiles_gu]
     const Unit* units_dn;    // [n_active * tiles_dn]
     int tiles_gu, tiles_dn;
-    int E, P, H, I;
-    int rpp_gu, rpp_dn;
+    int H, I;
     int* status;
 };
 
 // The waits of this kernel: mbarrier.try_wait with a suspend-time hint, so that a waiting warp sleeps in hardware
-// until the barrier's phase completes (or the hint runs out) instead of polling — the polling loops of 26 warps took a
-// quarter of the SM's issue slots from the converting warps.  Bounded: kGrpWaitTries tries of kGrpWaitHintNs each
+// until the barrier's phase completes (or the hint runs out) instead of polling.  Bounded: kGrpWaitTries tries of kGrpWaitHintNs each
 // (about four seconds), then false.
 constexpr unsigned kGrpWaitHintNs = 4000000u;
 constexpr unsigned kGrpWaitTries = 1024u;
@@ -970,10 +962,8 @@ extern "C" int vib3_launch_moe_grouped_int4(void* handle, const void* x, int x_d
     if (err) return err;
 
     GroupedArgs a;
-    a.units_gu = h->units_gu; a.units_dn = h->units_dn; a.tiles_gu = h->tiles_gu; a.tiles_dn = h->tiles_dn;
-    a.page_table = (const PageEntry*)page_table; a.shared_pages = (const PageEntry*)shared_pages; a.pool_base = h->pool_base;
-    a.work = h->work; a.active = h->active; a.counts = h->counts; a.offsets = h->offsets; a.act = h->act; a.y = h->y;
-    a.E = h->E; a.P = pages_per_segment; a.H = h->H; a.I = h->I; a.rpp_gu = h->rpp_gu; a.rpp_dn = h->rpp_dn; a.status = status;
+    a.work = h->work; a.act = h->act; a.y = h->y; a.units_gu = h->units_gu; a.units_dn = h->units_dn;
+    a.tiles_gu = h->tiles_gu; a.tiles_dn = h->tiles_dn; a.H = h->H; a.I = h->I; a.status = status;
     err = launch_pdl(moe_grouped_kernel<false>, dim3(sm_count()), kGrpThreads, kGrpSmem, st, h->maps, a);
     if (err) return err;
     err = launch_pdl(moe_grouped_kernel<true>, dim3(sm_count()), kGrpThreads, kGrpSmem, st, h->maps, a);
