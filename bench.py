@@ -464,18 +464,22 @@ def main():
     redo_total = int(dec.workspace[1].item())
 
     # ── e2e: host buffers every step, one call per token through the library's host-to-host entry point
-    # (MoeDecoder.forward_host_bound -> vib3_moe_step_run: the token from host memory in, one graph launch — copy in,
+    # (MoeDecoder.bind_host_step -> vib3_moe_step_run: the token from host memory in, one graph launch — copy in,
     # router, the two expert kernels, the fp32 output stored into pinned host memory — and the wait for it) ──
     x_host = [xs[i].cpu().pin_memory() for i in range(N_TOKENS)]
+    x_ptrs = [t.data_ptr() for t in x_host]
+    bound = [dec.bind_host_step(l, x_host[0].dtype, stream) for l in range(PHYS_LAYERS)]   # what a serving loop keeps per layer
     checksum = 0.0
     e2e_steps = max(K, MIN_TIMED_STEPS)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         for i in range(max(W, PHYS_LAYERS)):
-            dec.forward_host_bound(i % PHYS_LAYERS, x_host[i % N_TOKENS], stream)
+            bound[i % PHYS_LAYERS].run(x_ptrs[i % N_TOKENS])
         e0.record(stream)
         for i in range(e2e_steps):
-            checksum += float(dec.forward_host_bound(i % PHYS_LAYERS, x_host[i % N_TOKENS], stream)[0])  # the host reads the result
+            step = bound[i % PHYS_LAYERS]
+            step.run(x_ptrs[i % N_TOKENS])      # vib3_moe_step_run(handle, host pointer, stream)
+            checksum += float(step.out_np[0])   # the host reads the result
         e1.record(stream)
         stream.synchronize()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps

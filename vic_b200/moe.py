@@ -17,6 +17,26 @@ from .core_types import EXPERT_SHARED, MAX_ACTIVE_EXPERTS, SCORING_SIGMOID
 from .synth import SyntheticMoe
 
 
+class BoundHostStep:
+    """Handle of vib3_moe_step_create with its buffers.  ``run(x_ptr)`` is vib3_moe_step_run on a host pointer: the token is
+    copied in, the layer's graph launched and waited for; the fp32 [H] result is then in ``out`` (pinned host memory,
+    ``out_np`` is the same memory as a numpy array), valid until the next run."""
+
+    __slots__ = ("handle", "x_dev", "out", "out_np", "stream_ptr", "_run")
+
+    def __init__(self, handle, x_dev: torch.Tensor, out: torch.Tensor, stream_ptr: int):
+        from .lib import lib
+        self.handle, self.x_dev, self.out, self.stream_ptr = handle, x_dev, out, stream_ptr
+        self.out_np = out.numpy()
+        self._run = lib().vib3_moe_step_run
+
+    def run(self, x_ptr: int) -> None:
+        err = self._run(self.handle, x_ptr, self.stream_ptr)
+        if err:
+            from .lib import check
+            check("moe_step_run", err)
+
+
 class MoeDecoder:
     """Device buffers and launch sequence for batch-1 decode over a SyntheticMoe (or any pool with
     the same page-table layout)."""
@@ -132,43 +152,49 @@ class MoeDecoder:
                                     sh.down.rows_per_page, self.status, stream.cuda_stream)
         return out_pin
 
-    def forward_host_bound(self, layer: int, x_host: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
-        """forward_host_call with the layer bound once as a CUDA graph inside the library (vib3_moe_step_create /
-        vib3_moe_step_run): per token one C call with three arguments.  The first call for a (layer, dtype) builds the
-        graph and must not happen inside a stream capture; ``stream`` must be a non-default stream.  Returns the
-        pinned fp32 [H] result buffer of that (layer, dtype), valid until the next call."""
+    def bind_host_step(self, layer: int, dtype: torch.dtype, stream: torch.cuda.Stream) -> "BoundHostStep":
+        """One layer bound as a CUDA graph inside the library (vib3_moe_step_create): what a serving loop keeps per
+        layer.  Built once per (layer, dtype), outside any stream capture, on a non-default stream."""
         import ctypes as C
         from .lib import check, lib
         sh = self.model.shape
-        stream = stream or torch.cuda.current_stream()
-        if x_host.is_cuda:
-            raise ValueError("host tensor expected")
         if not hasattr(self, "_bound"):
             self._bound = {}
-        key = (layer, x_host.dtype)
+        key = (layer, dtype)
         ent = self._bound.get(key)
         if ent is None:
-            x_dev = torch.zeros(sh.hidden, dtype=x_host.dtype, device=self.out.device)
+            x_dev = torch.zeros(sh.hidden, dtype=dtype, device=self.out.device)
             out_pin = torch.zeros(sh.hidden, dtype=torch.float32).pin_memory()
             w = self.model.router_w[layer]
             h = C.c_void_p()
             check("moe_step_create", lib().vib3_moe_step_create(
-                kernels.x_dtype_code(x_host), x_dev.data_ptr(), w.data_ptr(), {torch.float16: 0, torch.float32: 1}[w.dtype],
+                {torch.float32: kernels.X_F32, torch.float16: kernels.X_F16, torch.bfloat16: kernels.X_BF16}[dtype], x_dev.data_ptr(), w.data_ptr(),
+                {torch.float16: 0, torch.float32: 1}[w.dtype],
                 self.scores.data_ptr(), None, self.ids.data_ptr(), self.weights.data_ptr(), sh.num_experts, sh.top_k, sh.scoring,
                 sh.scaling_factor, int(sh.normalize), int(self.exact_order), self.workspace.data_ptr(), self.tables[layer],
                 self.shared_tables[layer] or None, 1.0, self.act.data_ptr(), out_pin.data_ptr(), sh.hidden, sh.intermediate,
                 sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, 32, self.status.data_ptr(),
                 stream.cuda_stream, C.byref(h)))
-            ent = (h, x_dev, out_pin, lib().vib3_moe_step_run)
+            ent = BoundHostStep(h, x_dev, out_pin, stream.cuda_stream)
             self._bound[key] = ent
-        h, _, out_pin, run = ent
-        check("moe_step_run", run(h, x_host.data_ptr(), stream.cuda_stream))
-        return out_pin
+        return ent
+
+    def forward_host_bound(self, layer: int, x_host: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """forward_host_call with the layer bound once as a CUDA graph inside the library (vib3_moe_step_create /
+        vib3_moe_step_run): per token one C call with three arguments.  The first call for a (layer, dtype) builds the
+        graph and must not happen inside a stream capture; ``stream`` must be a non-default stream.  Returns the
+        pinned fp32 [H] result buffer of that (layer, dtype), valid until the next call."""
+        if x_host.is_cuda:
+            raise ValueError("host tensor expected")
+        stream = stream or torch.cuda.current_stream()
+        step = self.bind_host_step(layer, x_host.dtype, stream)
+        step.run(x_host.data_ptr())
+        return step.out
 
     def close(self) -> None:
         from .lib import lib
-        for h, *_ in getattr(self, "_bound", {}).values():
-            lib().vib3_moe_step_destroy(h)
+        for step in getattr(self, "_bound", {}).values():
+            lib().vib3_moe_step_destroy(step.handle)
         self._bound = {}
 
     def forward_tokens(self, layer: int, xs: torch.Tensor, outs: Optional[torch.Tensor] = None,
