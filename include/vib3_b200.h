@@ -88,7 +88,10 @@ int vib3_launch_router_topk(const void* x_f32, const void* W_f16, float* scores_
  * logit_offset: added to the logit before scoring.  scores_buf: 3 * num_experts floats; the first
  * num_experts receive the logits, the rest is scratch.
  * exact_order != 0 makes the selected indices equal to those of the reference's CPU router
- * (sequential fp32 summation) even for near-tied experts.  workspace: four uint32, zero before
+ * (sequential fp32 summation) even for near-tied experts; bit 1 of exact_order (value 2) is for a producer of x
+ * that lets its dependents start before it has finished (vib3_launch_residual_rms_norm with bit 1 of `center`): the
+ * router's first kernel then holds back the launches behind it until x is complete — the expert kernels read x
+ * before their own dependency wait.  workspace: four uint32, zero before
  * the first call; [0] is left zero by every call, [1] counts near-tie recomputations, [2] is used by
  * vib3_launch_moe_layer_routed_int4_paged, [3] is set if a bounded wait in the kernels ran out; calls
  * sharing a workspace must not overlap.  The launches carry the programmatic-dependent-launch attribute:
@@ -307,8 +310,12 @@ int vib3_launch_moe_layer_int4_paged_noalloc(const void* x, int x_dtype, const v
  * x_out[t] = cast(hidden[t] * inv_rms(hidden[t]) * weight) (weight_f16 NULL: no weight).  Dtypes VIB3_X_*;
  * strides of delta and x_out in bytes, of hidden in floats.  center != 0 (no counterpart in the reference) removes
  * the row's mean before normalising: for stacks of synthetic layers whose uniformly drawn INT4 codes have mean -0.5
- * (a common term that feeds itself through the residual stream).  With out_accumulate = 1 in the MoE launch that
- * follows, a layer is this launch plus the MoE launches. */
+ * (a common term that feeds itself through the residual stream).  Bit 1 of `center` (value 2): the launch is a
+ * programmatic dependent of its predecessor in any case (the norm weights are requested before the wait); with this
+ * bit it also lets the NEXT launch of the stream start at once.  That launch must wait for its predecessor before it
+ * touches hidden or x_out, and must keep later launches that read them from starting: the router launches do both
+ * when bit 1 of their exact_order argument is set; use the pair together.  With out_accumulate = 1 in the MoE
+ * launch that follows, a layer is this launch plus the MoE launches. */
 int vib3_launch_residual_rms_norm(float* hidden, int hidden_stride, const void* delta_or_null, int delta_dtype,
                                   int delta_stride_bytes, const float* delta2_or_null, int delta2_stride,
                                   const void* weight_f16_or_null, float eps, int center, void* x_out, int x_dtype,

@@ -129,6 +129,53 @@ def test_accumulate_into_residual(cuda_dev):
     assert torch.equal(resid, want)
 
 
+def test_norm_with_early_dependents_and_holding_router_equal_the_plain_chain(cuda_dev):
+    """A stack of norm -> router -> experts launches in a CUDA graph: with the norm letting the router start early and
+    the router holding the expert kernels back until the token is complete, the hidden state after twelve layers
+    equals, bit for bit, that of the chain without either flag (both on the batch-1 and on the grouped path)."""
+    from vic_b200 import kernels as K
+    from vic_b200.grouped import GroupedDecoder
+    from vic_b200.moe import MoeDecoder
+    from vic_b200.synth import synth_activation
+    model = _model("kimi", cuda_dev)
+    sh = model.shape
+    L, depth, T = model.n_layers, 12, 4
+    g = torch.Generator(device=cuda_dev).manual_seed(21)
+    attn = (torch.randn(depth, T, sh.hidden, generator=g, device=cuda_dev) * 0.3).to(torch.bfloat16)
+    norm_w = (1.0 + 0.1 * torch.randn(depth, sh.hidden, generator=g, device=cuda_dev)).to(torch.float16)
+    h0 = synth_activation(sh, g, cuda_dev, torch.float32, T)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        dec, gd = MoeDecoder(model), GroupedDecoder(model, max_tokens=T)
+        for batch in (1, T):
+            h = torch.zeros(batch, sh.hidden, dtype=torch.float32, device=cuda_dev)
+            x = torch.zeros(batch, sh.hidden, dtype=torch.bfloat16, device=cuda_dev)
+
+            def stack(early):   # (nothing between the layers: the norm follows the previous layer's last kernel)
+                h.copy_(h0[:batch])
+                for l in range(depth):
+                    K.residual_rms_norm(h, attn[l, :batch], norm_w[l], 1e-6, x, center=True, early_dependents=early)
+                    if batch == 1:
+                        dec.forward_layer(l % L, x[0], out=h[0], accumulate=True, hold=early)
+                    else:
+                        gd.forward(l % L, x, out=h, accumulate=True, hold=early)
+            got = {}
+            for early in (False, True):
+                stack(early)
+                stream.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=stream):
+                    stack(early)
+                for _ in range(3):
+                    gr.replay()
+                stream.synchronize()
+                got[early] = h.clone()
+            assert torch.isfinite(got[False]).all()
+            assert torch.equal(got[False], got[True])
+        assert int(dec.status.item()) == 0 and int(gd.status.item()) == 0
+        gd.close()
+
+
 def test_paged_equals_contiguous_bit_for_bit(cuda_dev):
     """Same page contents, different slots: scattered pool vs back-to-back pool give identical bits."""
     from vic_b200.buffer_manager import PageBufferManager

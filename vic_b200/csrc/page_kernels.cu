@@ -14,7 +14,10 @@
 #include "int4_math.cuh"
 #include "launch_common.h"
 
+#include <atomic>
+
 namespace vib3 {
+extern std::atomic<int> g_use_pdl;   // 1 = launches may be programmatic dependents (moe_layer.cu)
 
 enum Epilogue : int { EPI_F16 = 0, EPI_SWIGLU_F16 = 1 };
 
@@ -292,9 +295,12 @@ template <bool VEC>
 __global__ void __launch_bounds__(VEC ? 1024 : 256) residual_rms_norm_kernel(float* __restrict__ hidden, int hidden_stride, const void* __restrict__ delta,
                                                                 int delta_dtype, int delta_stride, const float* __restrict__ delta2,
                                                                 int delta2_stride, const __half* __restrict__ weight, float eps,
-                                                                int center, void* __restrict__ x_out, int x_dtype, int x_stride, int H) {
+                                                                int flags, void* __restrict__ x_out, int x_dtype, int x_stride, int H) {
     __shared__ float red[256];
     const int t = blockIdx.x, tid = threadIdx.x;
+    // flags bit 1: the kernels behind this one may start now (they must wait for it before they read x_out or hidden)
+    if ((flags & 2) && tid == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int center = flags & 1;
     float* row = hidden + (size_t)t * hidden_stride;
     const unsigned char* drow = delta ? reinterpret_cast<const unsigned char*>(delta) + (size_t)t * delta_stride : nullptr;
     const float* d2row = delta2 ? delta2 + (size_t)t * delta2_stride : nullptr;
@@ -304,12 +310,20 @@ __global__ void __launch_bounds__(VEC ? 1024 : 256) residual_rms_norm_kernel(flo
         const int n4 = H >> 2;
         float4 h[kItems], dl[kItems];
         uint2 wv[kItems];
+        // The norm weights are nobody's output: they are requested before the wait for the predecessor (the kernel
+        // may be launched as a programmatic dependent, e.g. of the previous sublayer's last kernel).
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) {
+            const int it = tid + kThreads * i;
+            wv[i] = make_uint2(0x3C003C00u, 0x3C003C00u);   // 1.0
+            if (it < n4 && weight) wv[i] = reinterpret_cast<const uint2*>(weight)[it];
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
         for (int i = 0; i < kItems; ++i) {
             const int it = tid + kThreads * i;
             h[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             dl[i] = h[i];
-            wv[i] = make_uint2(0x3C003C00u, 0x3C003C00u);   // 1.0
             if (it < n4) {
                 h[i] = reinterpret_cast<const float4*>(row)[it];
                 if (drow) {
@@ -329,7 +343,6 @@ __global__ void __launch_bounds__(VEC ? 1024 : 256) residual_rms_norm_kernel(flo
                     const float4 e = reinterpret_cast<const float4*>(d2row)[it];
                     dl[i].x += e.x; dl[i].y += e.y; dl[i].z += e.z; dl[i].w += e.w;
                 }
-                if (weight) wv[i] = reinterpret_cast<const uint2*>(weight)[it];
             }
         }
 #pragma unroll
@@ -369,6 +382,7 @@ __global__ void __launch_bounds__(VEC ? 1024 : 256) residual_rms_norm_kernel(flo
             }
         }
     } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (drow || d2row)
             for (int d = tid; d < H; d += 256)   // (a thread re-reads only its own columns)
                 row[d] += (drow ? load_x_as_f32(drow, delta_dtype, d) : 0.f) + (d2row ? d2row[d] : 0.f);
@@ -395,13 +409,18 @@ static int launch_norm(float* hidden, int hidden_stride, const void* delta, int 
     const bool vec = H % 4 == 0 && H <= 8192 && ((uintptr_t)hidden & 15) == 0 && (hidden_stride & 3) == 0 && ((uintptr_t)delta & 15) == 0 &&
                      (delta_stride & 15) == 0 && ((uintptr_t)delta2 & 15) == 0 && (delta2_stride & 3) == 0 && ((uintptr_t)weight & 7) == 0 &&
                      ((uintptr_t)x_out & 15) == 0 && (x_stride & 15) == 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tokens); cfg.blockDim = dim3(vec ? 1024 : 256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    const __half* w16 = (const __half*)weight;
     if (vec)
-        residual_rms_norm_kernel<true><<<n_tokens, 1024, 0, st>>>(hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2, delta2_stride,
-                                                                 (const __half*)weight, eps, center, x_out, x_dtype, x_stride, H);
-    else
-        residual_rms_norm_kernel<false><<<n_tokens, 256, 0, st>>>(hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2, delta2_stride,
-                                                                  (const __half*)weight, eps, center, x_out, x_dtype, x_stride, H);
-    return (int)cudaGetLastError();
+        return (int)cudaLaunchKernelEx(&cfg, residual_rms_norm_kernel<true>, hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2,
+                                       delta2_stride, w16, eps, center, x_out, x_dtype, x_stride, H);
+    return (int)cudaLaunchKernelEx(&cfg, residual_rms_norm_kernel<false>, hidden, hidden_stride, delta, delta_dtype, delta_stride, delta2,
+                                   delta2_stride, w16, eps, center, x_out, x_dtype, x_stride, H);
 }
 
 // Reference signature (cuda/src/kernels.cu:1178): fp32 in, fp32 out, fp16 weight, one vector.

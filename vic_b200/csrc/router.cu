@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kRowsThreads) router_rows_kernel(RouterArgs a,
     const int e0 = blockIdx.x * kRowsPerCta;
     const int nrows = min(kRowsPerCta, a.E - e0);
     if (tid == 0) {
-        pdl_trigger();
+        if (!a.hold_dependents) pdl_trigger();
         for (int r = 0; r < nrows; ++r) mbar_init(full + r, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         for (int r = 0; r < nrows; ++r) {
@@ -213,6 +213,9 @@ __global__ void __launch_bounds__(kRowsThreads) router_rows_kernel(RouterArgs a,
     }
     __syncthreads();
     pdl_wait();   // the tokens are the predecessor's output
+    // A predecessor that let this kernel start early is still writing the tokens until here, and the expert kernel
+    // two launches on reads them before its own wait: then the chain behind this kernel starts only now.
+    if (a.hold_dependents && tid == 0) pdl_trigger();
     const int nchunks = (n_tokens + tok_chunk - 1) / tok_chunk;
     const int n16 = (int)(xbytes >> 4);
     auto stage = [&](int c) {
@@ -401,7 +404,8 @@ int make_router_args(const void* x, int x_dtype, const void* W, int w_dtype, flo
     a.x = x; a.x_dtype = x_dtype; a.W = W; a.w_dtype = w_dtype; a.scores = scores_buf; a.bias = bias;
     a.logit_offset = logit_offset;
     a.out_ids = out_ids; a.out_weights = out_weights; a.counter = workspace; a.H = hidden_dim; a.E = num_experts;
-    a.top_k = top_k; a.mode = scoring_mode; a.scaling = scaling_factor; a.normalize = normalize; a.exact_order = exact_order;
+    a.top_k = top_k; a.mode = scoring_mode; a.scaling = scaling_factor; a.normalize = normalize;
+    a.exact_order = exact_order & 1; a.hold_dependents = (exact_order >> 1) & 1;
     if (w_dtype != W_F16 && w_dtype != W_F32) return VIB3_ERR_UNSUPPORTED;
     if (int e = check_router(a)) return e;
     if (int e = check_topk(a)) return e;

@@ -31,6 +31,7 @@ struct RouterArgs {
     float scaling;
     int normalize;
     int exact_order;
+    int hold_dependents;  // the first kernel lets its dependents start only after its own dependency wait (see make_router_args)
     // batched launch (grid y = token): distances between the tokens' vectors / buffers; zero for one token
     int x_stride;        // bytes
     int scores_stride;   // floats

@@ -360,16 +360,16 @@ class ExpertParallelStack:
         sh, dec = self.model.shape, self.dec
         phys = l % self.model.n_layers
         own_shared = shared_expert_owner(l, self.world) == self.rank
-        K.residual_rms_norm(self.h, self.attn[l], self.norm_w[l], 1e-6, self.x, delta2=prev, center=True)
+        K.residual_rms_norm(self.h, self.attn[l], self.norm_w[l], 1e-6, self.x, delta2=prev, center=True, early_dependents=True)
         if self.T == 1:
-            dec.route(phys, self.x[0])
+            dec.route(phys, self.x[0], hold=True)
             K.select_local_experts(dec.ids, dec.weights, sh.top_k, self.lo, self.hi, self.ids_loc, self.w_loc, self.n_loc)
             K.moe_layer_int4_paged_var(self.x[0], dec.tables[phys], sh.num_experts, dec.shared_tables[phys] if own_shared else 0,
                                        self.ids_loc, self.w_loc, sh.top_k, 1.0, dec.act, self.partial[0], False, sh.hidden,
                                        sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page,
                                        self.n_loc, dec.status)
         else:
-            self.gd.route(phys, self.x)
+            self.gd.route(phys, self.x, hold=True)
             self.gd.experts(phys, self.x, out=self.partial, expert_range=(self.lo, self.hi), shared=own_shared)
         if self.world > 1:
             dist.all_reduce(self.partial, op=dist.ReduceOp.SUM, group=self.group)

@@ -78,10 +78,12 @@ class GroupedDecoder:
         return self._work[0]
 
     def route(self, layer: int, xs: torch.Tensor, logit_offset: Optional[torch.Tensor] = None,
-              bias: Optional[torch.Tensor] = None) -> None:
+              bias: Optional[torch.Tensor] = None, hold: bool = False) -> None:
+        """``hold``: xs comes from a launch that lets its dependents start early (see MoeDecoder.route)."""
         sh = self.model.shape
         kernels.router_topk_batch(xs, self.model.router_w[layer], self.scores, bias, logit_offset, self.ids, self.weights,
-                                  sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize, self.exact_order, self.router_ws)
+                                  sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize,
+                                  int(self.exact_order) | (kernels.EXACT_HOLD if hold else 0), self.router_ws)
 
     def experts(self, layer: int, xs: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
                 expert_range=None, shared: bool = True) -> torch.Tensor:
@@ -102,11 +104,11 @@ class GroupedDecoder:
         return out
 
     def forward(self, layer: int, xs: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
-                logit_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
+                logit_offset: Optional[torch.Tensor] = None, hold: bool = False) -> torch.Tensor:
         """xs [T, H] (bf16 / fp16 / fp32, T <= max_tokens) -> [T, H] fp32; routing left in self.ids / self.weights."""
         if xs.shape[0] > self.max_tokens:
             raise ValueError("more tokens than the decoder was built for")
-        self.route(layer, xs, logit_offset)
+        self.route(layer, xs, logit_offset, hold=hold)
         return self.experts(layer, xs, out, accumulate)
 
 
@@ -179,8 +181,8 @@ def bench_c4_single(model: SyntheticMoe, stream, peak_gbs: float, n_layers: int 
     def token1(i):
         h.copy_(h0[i % 4:i % 4 + 1])
         for l in range(n_layers):
-            K.residual_rms_norm(h, attn[l, :1], norm_w[l], 1e-6, x, center=True)
-            dec.forward_layer(l % L, x[0], out=h[0], accumulate=True)
+            K.residual_rms_norm(h, attn[l, :1], norm_w[l], 1e-6, x, center=True, early_dependents=True)
+            dec.forward_layer(l % L, x[0], out=h[0], accumulate=True, hold=True)
     ms, _, steps = _graph_time(stream, token1, 1, 4, 40.0)
     b_layer = 9 * sh.expert_bytes + sh.num_experts * sh.hidden * 4
     res["batch1"] = {"tokens_per_s": 1e3 / ms, "ms_per_token": ms, "us_per_layer": ms * 1e3 / n_layers,
@@ -197,8 +199,8 @@ def bench_c4_single(model: SyntheticMoe, stream, peak_gbs: float, n_layers: int 
     def token32(i, count=False):
         hT.copy_(hT0)
         for l in range(n_layers):
-            K.residual_rms_norm(hT, attn[l], norm_w[l], 1e-6, xT, center=True)
-            gd.forward(l % L, xT, out=hT, accumulate=True)
+            K.residual_rms_norm(hT, attn[l], norm_w[l], 1e-6, xT, center=True, early_dependents=True)
+            gd.forward(l % L, xT, out=hT, accumulate=True, hold=True)
             if count:
                 dsum.add_(gd.n_distinct.to(torch.int64))
     with torch.cuda.stream(stream):

@@ -93,15 +93,19 @@ def rms_norm_f32(input_f32, output_f32, weight_f16, hidden_dim: int, eps: float,
                                                         _stream(stream)))
 
 
+EXACT_HOLD = 2   # added to a router launch's exact_order: the producer of x lets its dependents start early
+
+
 def residual_rms_norm(hidden: torch.Tensor, delta, weight_f16, eps: float, x_out: torch.Tensor, stream: Optional[int] = None,
-                      delta2=None, center: bool = False) -> None:
+                      delta2=None, center: bool = False, early_dependents: bool = False) -> None:
     """hidden [T, H] fp32 += delta [T, H] + delta2 [T, H] fp32 (either may be None); x_out [T, H] = cast(rms_norm(hidden) *
-    weight): one launch."""
+    weight): one launch.  ``early_dependents``: the next launch of the stream may start while this one runs; it must
+    be a router launch with ``EXACT_HOLD`` added to its exact_order argument (see include/vib3_b200.h)."""
     T, H = hidden.shape
     check("residual_rms_norm", lib().vib3_launch_residual_rms_norm(
         _ptr(hidden), hidden.stride(0), _ptr(delta), x_dtype_code(delta) if delta is not None else 0,
         delta.stride(0) * delta.element_size() if delta is not None else 0, _ptr(delta2),
-        delta2.stride(0) if delta2 is not None else 0, _ptr(weight_f16), eps, int(center), _ptr(x_out),
+        delta2.stride(0) if delta2 is not None else 0, _ptr(weight_f16), eps, int(center) | (2 if early_dependents else 0), _ptr(x_out),
         x_dtype_code(x_out), x_out.stride(0) * x_out.element_size(), H, T, _stream(stream)))
 
 

@@ -57,11 +57,16 @@ class MoeDecoder:
         self.shared_tables = [model.shared_table(l) for l in range(model.n_layers)]
         self.launches_per_layer = 3
 
+    def _order_flags(self, hold: bool) -> int:
+        return int(self.exact_order) | (kernels.EXACT_HOLD if hold else 0)
+
     def route(self, layer: int, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
-              logit_offset: Optional[torch.Tensor] = None) -> None:
+              logit_offset: Optional[torch.Tensor] = None, hold: bool = False) -> None:
+        """``hold``: x comes from a launch that lets its dependents start early (kernels.residual_rms_norm with
+        early_dependents): the router then keeps the expert kernels from starting before x is complete."""
         sh = self.model.shape
         kernels.router_topk_ex(x, self.model.router_w[layer], self.scores, bias, self.ids, self.weights, sh.top_k,
-                               sh.scoring, sh.scaling_factor, sh.normalize, self.exact_order, self.workspace,
+                               sh.scoring, sh.scaling_factor, sh.normalize, self._order_flags(hold), self.workspace,
                                logit_offset=logit_offset)
 
     def experts(self, layer: int, x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
@@ -76,14 +81,14 @@ class MoeDecoder:
 
     def forward_layer(self, layer: int, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                       accumulate: bool = False, bias: Optional[torch.Tensor] = None,
-                      logit_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      logit_offset: Optional[torch.Tensor] = None, hold: bool = False) -> torch.Tensor:
         """x: [H] activations (bf16 / fp16 / fp32).  Returns the fp32 [H] sublayer output.  The routing is left in
-        ``self.ids`` / ``self.weights``."""
+        ``self.ids`` / ``self.weights``.  ``hold`` as in ``route``."""
         sh = self.model.shape
         out = self.out if out is None else out
         kernels.moe_layer_routed_int4_paged(x, self.model.router_w[layer], self.scores, bias, logit_offset, self.ids,
                                             self.weights, sh.top_k, sh.scoring, sh.scaling_factor, sh.normalize,
-                                            self.exact_order, self.workspace, self.tables[layer], sh.num_experts,
+                                            self._order_flags(hold), self.workspace, self.tables[layer], sh.num_experts,
                                             self.shared_tables[layer], 1.0, self.act, out, accumulate, sh.hidden,
                                             sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page,
                                             sh.down.rows_per_page, self.status)
