@@ -58,6 +58,9 @@ struct RoutedSmem {
 template <int NCH, bool ROUTED>
 __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerArgs a, RouterArgs r, int nstages) {
     using MATH = MathQ16;
+    constexpr int kTileRows = gateup_tile_rows(NCH);         // row pairs per stage
+    constexpr int kGroupWarps = kTileRows / kPairsPerWarp;   // warps that consume a stage
+    constexpr int kGroups = kConsumerWarps / kGroupWarps;    // group g takes tiles g, g + kGroups, ...
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nchunks = a.H / kGroupSize;
     const int cap_k = a.top_k;                                  // routed slots the launch was sized for
@@ -188,7 +191,7 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
                 if (lane == 0) mbar_arrive(tab_ready);  // release: the consumers acquire the table through this barrier
                 cta_share((a.top_k + shared_in_pass1) * a.I, g0, g1);
             }
-            TileWalk walk(g0, g1, a.I, a.rpp_gu);
+            TileWalk walk(g0, g1, a.I, a.rpp_gu, kTileRows);
             Tile t;
             while (walk.next(t)) {
                 const int st = n % nstages;
@@ -332,7 +335,7 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
                 return;
             }
         }
-        TileWalk walk(g0, g1, a.I, a.rpp_gu);
+        TileWalk walk(g0, g1, a.I, a.rpp_gu, kTileRows);
         Tile t;
         while (walk.next(t)) {
             if (n % kGroups != group) { ++n; continue; }
@@ -942,8 +945,7 @@ static int launch_gateup_pipe_t(const MoeLayerArgs& a, const RouterArgs& r, cuda
 
 template <bool ROUTED>
 static int launch_gateup_nch(const MoeLayerArgs& a, const RouterArgs& r, cudaStream_t st, int nstages, size_t smem, int grid) {
-    const int nchunks = a.H / kGroupSize;
-    const int nch = nchunks % 32 == 0 ? nchunks / 32 : 0;
+    const int nch = gateup_nch(a.H);
     switch (nch) {
         case 1: return launch_gateup_pipe_t<1, ROUTED>(a, r, st, nstages, smem, grid);
         case 2: return launch_gateup_pipe_t<2, ROUTED>(a, r, st, nstages, smem, grid);
@@ -960,12 +962,15 @@ static int launch_gateup_nch(const MoeLayerArgs& a, const RouterArgs& r, cudaStr
 int launch_gateup_pipelined(const MoeLayerArgs& a, cudaStream_t st, const RouterArgs* router) {
     if (!pipe_shape_ok(a)) return VIB3_ERR_UNSUPPORTED;
     const int slots = a.top_k + (a.shared_pages ? 1 : 0);
-    const size_t stage_bytes = 2 * kTileRows * ((size_t)a.H / 2 + (size_t)a.H / 16);
+    int nch = gateup_nch(a.H);
+    if (nch != 1 && nch != 2 && nch != 4 && nch != 7 && nch != 8) nch = 0;   // the widths launch_gateup_nch instantiates
+    const int tile_rows = gateup_tile_rows(nch);
+    const size_t stage_bytes = 2 * tile_rows * ((size_t)a.H / 2 + (size_t)a.H / 16);
     size_t fixed = (size_t)(a.slot_token ? 2 : 1) * (a.H / kGroupSize) * MathQ16::kStride +
                    (size_t)slots * 2 * a.P * sizeof(PageEntry) +
                    (2 * kMaxStages + 1) * sizeof(uint64_t) + kMaxStages * sizeof(unsigned) + 128;
     const int total = slots * a.I;
-    const int grid = min(sm_count(), (total + kTileRows - 1) / kTileRows);
+    const int grid = min(sm_count(), (total + tile_rows - 1) / tile_rows);
     if (router) {
         const RouterArgs& r = *router;
         const size_t row_bytes = (size_t)r.H * (r.w_dtype == W_F32 ? 4 : 2);

@@ -6,10 +6,13 @@
 namespace vib3 {
 
 constexpr int kConsumerWarps = 16;
-constexpr int kTileRows = 4;       // row pairs per gate/up stage
 constexpr int kPairsPerWarp = 2;   // a consumer warp takes two row pairs (4 rows share each activation load)
-constexpr int kGroupWarps = kTileRows / kPairsPerWarp;  // 2 warps consume a stage
-constexpr int kGroups = kConsumerWarps / kGroupWarps;   // 8 groups; group g takes tiles g, g+8, ...
+// Row pairs per gate/up stage, by the kernel's NCH (32-column chunks per lane and row; 0 = any width).  A stage costs
+// the producer warp a fixed time whatever its size (the walk, the barrier, issuing the copies: about 0.7 us), so
+// short rows (hidden <= 4096) take eight pairs per stage and four warps consume it — measured on the Mixtral shape
+// (hidden 4096): 35.7 -> 26.3 us for the launch; the Kimi shape keeps four (eight would leave its ring two stages).
+constexpr int gateup_tile_rows(int nch) { return nch >= 1 && nch <= 4 ? 8 : 4; }
+constexpr int gateup_nch(int hidden) { return (hidden / kGroupSize) % 32 == 0 ? (hidden / kGroupSize) / 32 : 0; }
 constexpr int kPipeThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 12;
 constexpr unsigned kSpinLimit = 1u << 22;
@@ -56,7 +59,7 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned b
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// A tile: up to kTileRows consecutive rows of one page of one slot.
+// A tile: up to tile_rows consecutive rows of one page of one slot.
 struct Tile {
     int slot, page, rin, nrows, row;  // row = first row inside the slot's matrix
 };
@@ -67,7 +70,7 @@ struct Tile {
 struct TileWalk {
     int g, g_end, rows_per_slot, rpp, tile_rows;
     int slot, row, page, rin;
-    __device__ __forceinline__ TileWalk(int g0, int g1, int rows_per_slot_, int rpp_, int tile_rows_ = kTileRows)
+    __device__ __forceinline__ TileWalk(int g0, int g1, int rows_per_slot_, int rpp_, int tile_rows_)
         : g(g0), g_end(g1), rows_per_slot(rows_per_slot_), rpp(rpp_), tile_rows(tile_rows_) {
         slot = g0 / rows_per_slot;
         row = g0 - slot * rows_per_slot;
