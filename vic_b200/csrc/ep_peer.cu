@@ -75,6 +75,9 @@ __global__ void __launch_bounds__(32) peer_select_pairs_kernel(const unsigned in
                                                                const unsigned char* ids, int ids_stride, const unsigned char* w, int w_stride,
                                                                int top_k, int lo, int hi, unsigned short* pe, float* pw, unsigned short* pt,
                                                                int capacity, int* count_out) {
+    // The expert kernels behind this launch may become resident now: what they do before their own dependency wait
+    // (barriers, the shared expert of the rank's own token, whose vector an earlier launch wrote) needs no message.
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const unsigned step = *step_counter + 1u;
     if (!peer_wait_warp(flags, step, world) && threadIdx.x == 0) flag(status, kStatusTimeout);
     __syncwarp();

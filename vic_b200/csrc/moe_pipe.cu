@@ -79,7 +79,8 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
     }
     // Grouped mode: the slots are (token, expert) pairs of several tokens.  A CTA's contiguous share of the
     // row space touches at most two slots, so it keeps two quantised activation vectors; which tokens they
-    // belong to is known only after the wait, so there is no pass 0 (the shared expert is the last slot).
+    // belong to is known only after the wait.  The shared expert's token (shared_token) is an argument, so
+    // pass 0 runs as in the single-token form — under whatever the pair list is still waiting for.
     const bool grouped = !ROUTED && a.slot_token != nullptr;
     const unsigned xbytes = (unsigned)nchunks * MATH::kStride;
 
@@ -127,7 +128,9 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
     // everything that reads the token waits for that kernel first; the weights do not depend on it, so the
     // producer warp fills the ring meanwhile.
     if (ROUTED && warp != kConsumerWarps) pdl_wait();
-    if (warp < kConsumerWarps && !grouped) stage_activation<MATH>(xs, a.x, a.x_dtype, a.H, tid, kConsumerWarps * 32);
+    if (warp < kConsumerWarps && (!grouped || a.shared_pages))
+        stage_activation<MATH>(xs, reinterpret_cast<const unsigned char*>(a.x) + (grouped ? (size_t)a.shared_token * a.x_stride : (size_t)0),
+                               a.x_dtype, a.H, tid, kConsumerWarps * 32);
     if (ROUTED && warp < kConsumerWarps) {
         const int n16 = (a.H * (a.x_dtype == X_F32 ? 4 : 2)) >> 4;
         for (int i = tid; i < n16; i += kConsumerWarps * 32) reinterpret_cast<uint4*>(xraw)[i] = __ldg(reinterpret_cast<const uint4*>(a.x) + i);
@@ -146,8 +149,7 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
     }
 
     int n = 0;  // tiles of this CTA so far, over both passes (producer and consumers count alike)
-    const int first_pass = (a.shared_pages && !grouped) ? 0 : 1;
-    const int shared_in_pass1 = (grouped && a.shared_pages) ? 1 : 0;
+    const int first_pass = a.shared_pages ? 0 : 1;
 
     if (warp == kConsumerWarps) {
         // ── producer warp: every lane walks the tiles; lane 0 arms the stage's barrier, lanes 0..3 each
@@ -189,7 +191,7 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tab_ready);  // release: the consumers acquire the table through this barrier
-                cta_share((a.top_k + shared_in_pass1) * a.I, g0, g1);
+                cta_share(a.top_k * a.I, g0, g1);
             }
             TileWalk walk(g0, g1, a.I, a.rpp_gu, kTileRows);
             Tile t;
@@ -313,8 +315,10 @@ __global__ void __maxnreg__(ROUTED ? 104 : 80) moe_gateup_pipe_kernel(MoeLayerAr
             }
             a.top_k = active_top_k(a);
             const bool ready = mbar_wait(tab_ready, 0);
-            cta_share((a.top_k + shared_in_pass1) * a.I, g0, g1);
+            cta_share(a.top_k * a.I, g0, g1);
             if (grouped) {
+                // pass 0 read the first activation buffer: every consumer warp must be through with it
+                if (first_pass == 0) asm volatile("bar.sync 1, %0;" ::"r"(kConsumerWarps * 32) : "memory");
                 // quantise the activation vectors of the (at most two) slots this CTA's rows belong to
                 if (ready && g1 > g0) {
                     slot_a = g0 / a.I;
