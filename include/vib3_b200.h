@@ -264,6 +264,14 @@ int vib3_peer_free(void* ptr);
 int vib3_launch_peer_publish(const void* src, size_t src_stride_bytes, int bytes, void* const* dst_table,
                              size_t dst_stride_bytes, unsigned int* const* flag_table, const unsigned int* step_counter,
                              int step_offset, int rank, int world, void* stream);
+/* The same for rows of fp32 values with a second addend: destination d receives src[d] + add_src[d] if
+ * *add_count > add_threshold, else src[d] (rows src_stride_bytes apart in both; bytes a multiple of 16).  For the partial
+ * rows of an expert-parallel step whose launch windows beyond the first ran beside the first one into a buffer of their
+ * own: they hold pairs only when the rank's pair count exceeds the first window. */
+int vib3_launch_peer_publish_rows(const float* src, const float* add_src, size_t src_stride_bytes, int bytes,
+                                  const int* add_count, int add_threshold, void* const* dst_table, size_t dst_stride_bytes,
+                                  unsigned int* const* flag_table, const unsigned int* step_counter, int step_offset,
+                                  int rank, int world, void* stream);
 /* Wait (bounded: about two seconds, then VIB3_STATUS_TIMEOUT in *status) until each of flags[0 .. world) has
  * reached *step_counter + 1; advance != 0 then stores that step into *step_counter.  Kernels launched after this
  * one read what the peers stored before their flags. */

@@ -36,15 +36,28 @@ constexpr unsigned kPeerSpinLimit = 1u << 24;
 
 // grid = world (one CTA per destination).  Destination d receives `bytes` bytes from src + d * src_stride at
 // dst_table[d] + rank * dst_stride, then the step number in flag_table[d][rank].  bytes may be 0 (a bare signal).
+// add_src (optional; rows of fp32 values, bytes a multiple of 16): when *add_count > add_threshold, row d of add_src is
+// added to what is sent — the partial sums of the launch windows beyond the first, which a step almost never needs.
 __global__ void __launch_bounds__(256) peer_publish_kernel(const unsigned char* src, size_t src_stride, int bytes,
                                                            unsigned char* const* dst_table, size_t dst_stride,
                                                            unsigned int* const* flag_table, const unsigned int* step_counter,
-                                                           unsigned step_offset, int rank) {
+                                                           unsigned step_offset, int rank, const unsigned char* add_src,
+                                                           const int* add_count, int add_threshold) {
     const int d = blockIdx.x;
     const unsigned char* s = src + (size_t)d * src_stride;
     unsigned char* t = dst_table[d] + (size_t)rank * dst_stride;
     const int n16 = bytes >> 4;
-    for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(t)[i] = reinterpret_cast<const uint4*>(s)[i];
+    if (add_src != nullptr && *add_count > add_threshold) {
+        const float4* s2 = reinterpret_cast<const float4*>(add_src + (size_t)d * src_stride);
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(s)[i];
+            const float4 w = s2[i];
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+            reinterpret_cast<float4*>(t)[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(t)[i] = reinterpret_cast<const uint4*>(s)[i];
+    }
     for (int i = (n16 << 4) + threadIdx.x; i < bytes; i += blockDim.x) t[i] = s[i];
     __threadfence_system();
     __syncthreads();
@@ -166,7 +179,23 @@ extern "C" int vib3_launch_peer_publish(const void* src, size_t src_stride_bytes
     if (bytes > 0 && (((uintptr_t)src | src_stride_bytes | dst_stride_bytes) & 15)) return VIB3_ERR_ALIGN;
     peer_publish_kernel<<<world, 256, 0, (cudaStream_t)stream>>>((const unsigned char*)src, src_stride_bytes, bytes,
                                                                 (unsigned char* const*)dst_table, dst_stride_bytes, flag_table,
-                                                                step_counter, (unsigned)step_offset, rank);
+                                                                step_counter, (unsigned)step_offset, rank, nullptr, nullptr, 0);
+    return (int)cudaGetLastError();
+}
+
+// vib3_launch_peer_publish for rows of fp32 values with a second addend: destination d receives
+// src[d] + (*add_count > add_threshold ? add_src[d] : 0), rows src_stride_bytes apart in both sources.
+extern "C" int vib3_launch_peer_publish_rows(const float* src, const float* add_src, size_t src_stride_bytes, int bytes,
+                                             const int* add_count, int add_threshold, void* const* dst_table,
+                                             size_t dst_stride_bytes, unsigned int* const* flag_table,
+                                             const unsigned int* step_counter, int step_offset, int rank, int world, void* stream) {
+    if (!src || !add_src || !add_count || !dst_table || !flag_table || !step_counter) return VIB3_ERR_NULL;
+    if (world <= 0 || rank < 0 || rank >= world || bytes <= 0) return VIB3_ERR_COUNT;
+    if ((((uintptr_t)src | (uintptr_t)add_src | src_stride_bytes | dst_stride_bytes) & 15) || (bytes & 15)) return VIB3_ERR_ALIGN;
+    peer_publish_kernel<<<world, 256, 0, (cudaStream_t)stream>>>((const unsigned char*)src, src_stride_bytes, bytes,
+                                                                (unsigned char* const*)dst_table, dst_stride_bytes, flag_table,
+                                                                step_counter, (unsigned)step_offset, rank,
+                                                                (const unsigned char*)add_src, add_count, add_threshold);
     return (int)cudaGetLastError();
 }
 

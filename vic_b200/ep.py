@@ -185,11 +185,17 @@ class PeerExchange:
         kernels.peer_select_pairs(self.flags1, self.counter, self.world, status, ids, self.msg_bytes, weights, self.msg_bytes, top_k,
                                   lo, hi, pair_e, pair_w, pair_t, pair_e.numel(), n_pairs)
 
-    def publish_rows(self, partial: torch.Tensor) -> None:
-        """Row t of `partial` ([G, H] fp32) goes to rank t's row `rank`, flagged with the current step."""
+    def publish_rows(self, partial: torch.Tensor, overflow: Optional[torch.Tensor] = None, n_pairs: Optional[torch.Tensor] = None,
+                     first_window: int = 0) -> None:
+        """Row t of `partial` ([G, H] fp32) goes to rank t's row `rank`, flagged with the current step.  ``overflow``:
+        a second [G, H] buffer that is added when ``*n_pairs > first_window`` (the later launch windows' sums)."""
         from . import kernels
-        kernels.peer_publish(partial, self.hidden * 4, self.hidden * 4, self.rows_table, self.hidden * 4, self.flags2_table,
-                             self.counter, 0, self.rank, self.world)
+        if overflow is None:
+            kernels.peer_publish(partial, self.hidden * 4, self.hidden * 4, self.rows_table, self.hidden * 4, self.flags2_table,
+                                 self.counter, 0, self.rank, self.world)
+        else:
+            kernels.peer_publish_rows(partial, overflow, self.hidden * 4, n_pairs, first_window, self.rows_table, self.hidden * 4,
+                                      self.flags2_table, self.counter, 0, self.rank, self.world)
 
     def wait_sum_rows(self, status, out: torch.Tensor) -> None:
         """Wait for every rank's partial row of the current step, then add the rows in rank order."""
@@ -243,6 +249,10 @@ class ExpertParallelDecoder:
         self.pair_t = torch.zeros(cap, dtype=torch.int16, device=dev)
         self.n_pairs = torch.zeros(1, dtype=torch.int32, device=dev)
         self.act = torch.zeros((PAIRS_PER_LAUNCH + 1) * sh.intermediate, dtype=torch.float16, device=dev)
+        # Peer form with more than one launch window: the windows beyond the first — empty in all but a few steps
+        # in a thousand, but their launches still cost a dependency hop each — run on a second stream beside
+        # the first window, with scratch and partial sums of their own; the row exchange adds the two.
+        self.side = None
         mine = local_experts(rank, sh.num_experts, world)
         self.expert_lo, self.expert_hi = (mine[0], mine[-1] + 1) if mine else (0, 0)
         self.grouped_launches = (cap + PAIRS_PER_LAUNCH - 1) // PAIRS_PER_LAUNCH
@@ -250,6 +260,10 @@ class ExpertParallelDecoder:
         self.launches_per_step = 2 + 2 * self.grouped_launches + (1 if self.collectives == "a2a" else 0)
         if self.peer is not None:   # router (2), publish, wait + pair selection, grouped pairs, publish, wait + row sum
             self.launches_per_step = 2 + 1 + 1 + 2 * self.grouped_launches + 1 + 1
+            if self.grouped_launches > 1 and dev.type == "cuda":
+                self.side = torch.cuda.Stream(device=dev)
+                self.act2 = torch.zeros_like(self.act)
+                self.partial2 = torch.zeros_like(self.partial)
 
     def step(self, layer: int, x: torch.Tensor, logit_offset: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: this rank's token [H] bf16.  Returns this rank's token's layer output [H] fp32."""
@@ -285,16 +299,30 @@ class ExpertParallelDecoder:
             kernels.select_local_pairs(self.recv_ids, self.msg_bytes, self.recv_w, self.msg_bytes, self.world, sh.top_k,
                                        self.expert_lo, self.expert_hi, self.pair_e, self.pair_w, self.pair_t,
                                        self.pair_e.numel(), self.n_pairs)
-        for j in range(self.grouped_launches):
+        def window(j, act, out, accumulate):
             kernels.moe_layer_int4_paged_grouped(
                 self.recv_x, X_BF16, self.msg_bytes, self.world, dec.tables[layer], sh.num_experts,
                 dec.shared_tables[layer] if j == 0 else 0, self.rank, self.pair_e, self.pair_w, self.pair_t,
-                PAIRS_PER_LAUNCH, j * PAIRS_PER_LAUNCH, self.n_pairs, 1.0, self.act, self.partial, H, j > 0, H,
+                PAIRS_PER_LAUNCH, j * PAIRS_PER_LAUNCH, self.n_pairs, 1.0, act, out, H, accumulate, H,
                 sh.intermediate, sh.pages_per_segment, sh.gate_up.rows_per_page, sh.down.rows_per_page, dec.status)
+        if self.side is not None:
+            main = torch.cuda.current_stream()
+            self.side.wait_stream(main)            # after the pair list
+            with torch.cuda.stream(self.side):
+                for j in range(1, self.grouped_launches):
+                    window(j, self.act2, self.partial2, j > 1)
+            window(0, self.act, self.partial, False)
+            main.wait_stream(self.side)
+            return
+        for j in range(self.grouped_launches):
+            window(j, self.act, self.partial, j > 0)
 
     def combine(self) -> torch.Tensor:
         if self.peer is not None:
-            self.peer.publish_rows(self.partial)
+            if self.side is not None:
+                self.peer.publish_rows(self.partial, self.partial2, self.n_pairs, PAIRS_PER_LAUNCH)
+            else:
+                self.peer.publish_rows(self.partial)
             self.peer.wait_sum_rows(self.dec.status, self.out)
             return self.out
         combine_partials(self.out, self.partial, self.rank, self.world, self.group, self.partial_in)

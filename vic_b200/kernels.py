@@ -268,6 +268,15 @@ def peer_publish(src: torch.Tensor, src_stride_bytes: int, nbytes: int, dst_tabl
                                                          _ptr(flag_table), _ptr(step_counter), step_offset, rank, world, _stream(stream)))
 
 
+def peer_publish_rows(src: torch.Tensor, add_src: torch.Tensor, row_bytes: int, add_count: torch.Tensor, add_threshold: int,
+                      dst_table: torch.Tensor, dst_stride_bytes: int, flag_table: torch.Tensor, step_counter: torch.Tensor,
+                      step_offset: int, rank: int, world: int, stream: Optional[int] = None) -> None:
+    """peer_publish of fp32 rows: rank d receives src[d] + (add_src[d] if *add_count > add_threshold)."""
+    check("peer_publish_rows", lib().vib3_launch_peer_publish_rows(
+        _ptr(src), _ptr(add_src), src.stride(0) * 4, row_bytes, _ptr(add_count), add_threshold, _ptr(dst_table), dst_stride_bytes,
+        _ptr(flag_table), _ptr(step_counter), step_offset, rank, world, _stream(stream)))
+
+
 def peer_wait(flags: torch.Tensor, step_counter: torch.Tensor, world: int, advance: bool, status, stream: Optional[int] = None) -> None:
     """Wait (bounded) until every peer's flag has reached the next step; advance the step counter."""
     check("peer_wait", lib().vib3_launch_peer_wait(_ptr(flags), _ptr(step_counter), world, int(advance), _ptr(status), _stream(stream)))

@@ -77,6 +77,7 @@ SIGNATURES = {
     "vib3_peer_close": (_i, [_vp]),
     "vib3_peer_free": (_i, [_vp]),
     "vib3_launch_peer_publish": (_i, [_vp, C.c_size_t, _i, _vp, C.c_size_t, _vp, _vp, _i, _i, _i, _vp]),
+    "vib3_launch_peer_publish_rows": (_i, [_vp, _vp, C.c_size_t, _i, _vp, _i, _vp, C.c_size_t, _vp, _vp, _i, _i, _i, _vp]),
     "vib3_launch_peer_select_pairs": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp]),
     "vib3_launch_peer_sum_rows": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp]),
     "vib3_launch_peer_wait": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
