@@ -226,7 +226,9 @@ void vib3_moe_step_destroy(void* handle);
  * pair_begin > 0 normally pass out_accumulate = 1 and no shared expert).  x: n_tokens activation vectors
  * x_stride_bytes apart (16-byte multiples); out: n_tokens fp32 rows out_stride floats apart, every
  * token's row is written (zero where the token has no pair here).  The shared expert, if given, belongs
- * to token shared_token.  act_scratch: (pair_capacity + 1) * expert_hidden_dim fp16 values.  Only for
+ * to token shared_token; its vector is read, and its rows of act_scratch are written, BEFORE the launch
+ * waits for its predecessor in the stream (so that it runs under whatever still produces the pair lists): that
+ * vector must come from an older launch than the predecessor.  act_scratch: (pair_capacity + 1) * expert_hidden_dim fp16 values.  Only for
  * shapes the staged kernels take (hidden and expert dimensions multiples of 256, expert dimension 1024
  * or 2048); VIB3_ERR_UNSUPPORTED otherwise. */
 int vib3_launch_moe_layer_int4_paged_grouped(const void* x, int x_dtype, int x_stride_bytes, int n_tokens,
