@@ -575,28 +575,54 @@ def bench_main(args) -> None:
     ms_step, timed_steps = timed_graph(step, chunk, max(K, B.MIN_TIMED_STEPS), B.MIN_TIMED_MS)
     clocks = sampler.stop() if sampler else None
 
-    # e2e: token from pinned host memory in, layer output back to the host, every step
+    # e2e: token from pinned host memory in, layer output back to the host, every step.  As on one GPU
+    # (vib3_moe_step_run) the step of a bound layer is ONE CUDA graph — copy in from a pinned staging buffer, the whole
+    # expert-parallel step with both exchanges, copy out into pinned memory — so the host pays one host-to-host copy
+    # of the token, one graph launch and one wait per step instead of a dozen separate launches.
     x_host = [xs[i].cpu().pin_memory() for i in range(B.N_TOKENS)]
+    x_stage = torch.zeros(sh.hidden, dtype=torch.bfloat16).pin_memory()
     out_host = torch.zeros(sh.hidden, dtype=torch.float32).pin_memory()
+    out_np = out_host.numpy()
     x_dev = torch.zeros(sh.hidden, dtype=torch.bfloat16, device=dev)
+    e2e_stream = torch.cuda.Stream(device=dev)
+    e2e_stream.wait_stream(torch.cuda.current_stream())
+    bound = []
+    with torch.cuda.stream(e2e_stream):
+        def body(l):
+            x_dev.copy_(x_stage, non_blocking=True)
+            out_host.copy_(ep.step(l, x_dev), non_blocking=True)
+        for l in range(layers):
+            body(l)                      # eager once: every rank runs the same steps, so the exchanges stay in step
+        e2e_stream.synchronize()
+        dist.barrier()
+        for l in range(layers):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=e2e_stream):
+                body(l)
+            bound.append(g)
+        checksum = 0.0
 
-    def e2e_step(i):
-        x_dev.copy_(x_host[i % B.N_TOKENS], non_blocking=True)
-        out_host.copy_(ep.step(i % layers, x_dev), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-    for i in range(4):
-        e2e_step(i)
-    dist.barrier()
-    e2e_steps = max(K, B.MIN_TIMED_STEPS)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e1.record()
-    torch.cuda.synchronize()
+        def e2e_step(i):
+            x_stage.copy_(x_host[i % B.N_TOKENS])          # the caller's token (host memory) into the staging buffer
+            bound[i % layers].replay()
+            e2e_stream.synchronize()
+            return float(out_np[0])                      # the host reads the result
+        for i in range(4):
+            e2e_step(i)
+        dist.barrier()
+        e2e_steps = max(K, B.MIN_TIMED_STEPS)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(e2e_stream)
+        for i in range(e2e_steps):
+            checksum += e2e_step(i)
+        e1.record(e2e_stream)
+        e2e_stream.synchronize()
+    torch.cuda.current_stream().wait_stream(e2e_stream)
+    assert checksum == checksum
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0]) / e2e_steps
+    del bound
 
     # where the step's time goes: the step cut short after each phase (every rank runs the same prefix, so an
     # exchange always finds its partners), each prefix in a CUDA graph of its own; a phase is the difference
@@ -651,7 +677,8 @@ def bench_main(args) -> None:
                       "collectives": "peer memory: stores and flags over NVLink (csrc/ep_peer.cu)" if ep.peer is not None else f"NCCL ({ep.collectives})",
                       "experts_per_gpu": sh.num_experts // world},
             "e2e": {"value": world / (e2e_ms * 1e-3), "unit": B.UNIT, "h2d_bytes_per_step": world * sh.hidden * 2,
-                    "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
+                    "d2h_bytes_per_step": world * sh.hidden * 4, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "api": "one CUDA graph per bound layer and rank: copy in, ExpertParallelDecoder.step, copy out"},
             "gpu_launches": timed_steps * ep.launches_per_step * world,
             "phase_us_rank0": phases, "parity": parity,
             "imbalance_bound": imbalance_bound(sh.num_experts, sh.top_k, world, world, trials=400),
