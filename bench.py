@@ -425,7 +425,8 @@ def main():
 
     K, W = args.steps, args.warmup
     stream = torch.cuda.Stream(device=dev)
-    chunk = max(1, min(K, 64))
+    K = max(1, K)
+    chunk = 64 if K >= 64 else K * (64 // K)   # whole groups of K steps, about 64 per graph whatever --steps is
     # ── value: device-resident inputs, graph replay, CUDA events on the launching stream ──
     timer = GraphTimer(stream, step, chunk, warm=W)
     assert int(dec.status.item()) == 0, "device status word set"
