@@ -607,10 +607,10 @@ def bench_main(args) -> None:
             bound[i % layers].replay()
             e2e_stream.synchronize()
             return float(out_np[0])                      # the host reads the result
-        for i in range(4):
+        for i in range(32):
             e2e_step(i)
         dist.barrier()
-        e2e_steps = max(K, B.MIN_TIMED_STEPS)
+        e2e_steps = max(K, 2 * B.MIN_TIMED_STEPS)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(e2e_stream)
         for i in range(e2e_steps):
