@@ -52,11 +52,13 @@ constexpr int kGrpXWarp = kGrpFirstConvWarp + kGrpConvWarps;   // issues the tok
 constexpr int kGrpThreads = (kGrpXWarp + 1) * 32;
 constexpr int kGrpStages = 8;                   // weight ring
 constexpr int kGrpSlabK = 256;                  // columns of K per pipeline step
-constexpr int kGrpMaxN = 16;                    // tokens of one expert per pass over its tile
+constexpr int kGrpMaxN = 16;                    // tokens of one expert per accumulator (a "pass"); a slab is converted once for
+                                                // up to TWO passes: the second token group goes to the other D buffer
 constexpr int kGrpABufs = 3;                    // A-operand buffers in tensor memory: the converting warps run up to two slabs ahead
 constexpr int kGrpXStages = kGrpABufs;          // token ring: stage i is released together with A buffer i (one commit frees both)
 constexpr int kGrpRawBytes = 18 * 1024;         // a weight stage: codes 16 KB + scales 2 KB of 128 rows x 256 columns
-constexpr int kGrpXBytes = kGrpMaxN * kGrpSlabK * 2;   // a token stage: 16 tokens x 256 columns fp16 = 8 KB
+constexpr int kGrpXGroupBytes = kGrpMaxN * kGrpSlabK * 2;   // 16 tokens x 256 columns fp16 = 8 KB
+constexpr int kGrpXBytes = 2 * kGrpXGroupBytes;         // a token stage: the two token groups of a double pass
 constexpr int kGrpTmemCols = 512;
 constexpr int kGrpACols = kGrpSlabK / 2;        // 128 columns: 256 fp16 per row
 constexpr int kGrpDCol0 = kGrpABufs * kGrpACols;   // the A buffers, then two D buffers of kGrpMmaWarps partial accumulators of kGrpMaxN columns
@@ -77,6 +79,8 @@ struct GroupedWork {
 };
 
 struct Unit;
+// Trips over a unit's slabs: its passes are taken two at a time (each converted slab feeds both).
+__host__ __device__ constexpr int grp_double_passes(int n_tok) { return (n_tok + 2 * kGrpMaxN - 1) / (2 * kGrpMaxN); }
 struct GroupedArgs {
     const GroupedWork* work;
     __half* act;             // [pairs][I], K order permuted
@@ -258,7 +262,9 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
     pdl_wait();   // the work lists, the gathered tokens and (down) the intermediate are earlier kernels' outputs
     UnitWalk walk(DOWN ? a.units_dn : a.units_gu, a.work->n_active * (DOWN ? a.tiles_dn : a.tiles_gu));
 
-    // Every role walks the same sequence: units blockIdx.x, + gridDim.x, ...; per unit ceil(n_tok / 16) passes;
+    // Every role walks the same sequence: units blockIdx.x, + gridDim.x, ...; per unit ceil(n_tok / 16) passes, taken
+    // two at a time (a converted slab feeds the MMAs of both token groups: an expert with 17 to 32 tokens is
+    // converted once, the shared expert of 128 tokens four times instead of eight);
     // per pass nslab slabs.  `it` counts slabs (weight stage it % 8, token stage it % 8, A buffer it % 3), `pc`
     // passes (D buffer pc & 1).
     bool ok = true;
@@ -270,7 +276,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
             const CUtensorMap* codes = DOWN ? &maps.dn_codes : &maps.gu_codes;
             const CUtensorMap* scales = DOWN ? (t.scales_last ? &maps.dn_scales_last : &maps.dn_scales_full)
                                              : (t.scales_last ? &maps.gu_scales_last : &maps.gu_scales_full);
-            const int total = ((t.n_tok + kGrpMaxN - 1) / kGrpMaxN) * nslab;
+            const int total = grp_double_passes(t.n_tok) * nslab;
             // One instruction for all issuing lanes (each lane's copy is a different box): the same copies issued
             // from one branch per lane cost four times as much of the warp's time.
             //   gate/up: lane 0/1 codes of gate/up, lane 2/3 their scales;   down: lane 0 codes, lane 1 scales
@@ -302,15 +308,17 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
         Unit t;
         const CUtensorMap* xmap = DOWN ? &maps.act16 : &maps.xg16;
         while (ok && walk.next(t)) {
-            for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN) {
+            for (int p0 = 0; ok && p0 < t.n_tok; p0 += 2 * kGrpMaxN) {
+                const int ng = t.n_tok - p0 > kGrpMaxN ? 2 : 1;   // token groups of this double pass
                 for (int s = 0; s < nslab; ++s, ++it) {
                     const int xs = it % kGrpXStages;
                     if (it >= kGrpXStages) ok = mbar_wait_hint(a_empty + xs, ((it / kGrpXStages) - 1) & 1);
                     if (!ok) break;
-                    if (lane == 0) {
-                        mbar_expect_tx(xfull + xs, kGrpXBytes);
-                        tma_load_3d(xring + (size_t)xs * kGrpXBytes, xmap, 0, t.pair_off + p0, s * (kGrpSlabK / 64), xfull + xs);
-                    }
+                    if (lane == 0) mbar_expect_tx(xfull + xs, ng * kGrpXGroupBytes);
+                    __syncwarp();
+                    if (lane < ng)   // one instruction for both groups' copies
+                        tma_load_3d(xring + (size_t)xs * kGrpXBytes + lane * kGrpXGroupBytes, xmap, 0, t.pair_off + p0 + lane * kGrpMaxN,
+                                    s * (kGrpSlabK / 64), xfull + xs);
                     __syncwarp();
                 }
             }
@@ -326,34 +334,41 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
         int it = 0, pc = 0;
         Unit t;
         while (ok && walk.next(t)) {
-            for (int p0 = 0; ok && p0 < t.n_tok; p0 += kGrpMaxN, ++pc) {
+            for (int p0 = 0; ok && p0 < t.n_tok; p0 += 2 * kGrpMaxN) {
                 const uint32_t idesc = (1u << 4) | ((uint32_t)(kGrpMaxN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-                const int db = pc & 1;
-                if (pc >= 2) ok = mbar_wait_hint(d_empty + db, ((pc >> 1) - 1) & 1);
+                // a double pass: token group g accumulates into D buffer (pc + g) & 1 — with two groups both buffers
+                const int ng = t.n_tok - p0 > kGrpMaxN ? 2 : 1;
+                for (int g = 0; ok && g < ng; ++g)
+                    if (pc + g >= 2) ok = mbar_wait_hint(d_empty + ((pc + g) & 1), (((pc + g) >> 1) - 1) & 1);
                 for (int s = 0; ok && s < nslab; ++s, ++it) {
                     const int xs = it % kGrpXStages, ab = it % kGrpABufs;
                     ok = mbar_wait_hint(xfull + xs, (it / kGrpXStages) & 1) && mbar_wait_hint(a_full + ab, (it / kGrpABufs) & 1);
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
-                        const uint32_t xaddr = smem_u32(xring + (size_t)xs * kGrpXBytes);
+                        for (int g = 0; g < ng; ++g) {
+                            const int db = (pc + g) & 1;
+                            const uint32_t xaddr = smem_u32(xring + (size_t)xs * kGrpXBytes + g * kGrpXGroupBytes);
 #pragma unroll
-                        for (int kk = 0; kk < kGrpSlabK / 16 / kGrpMmaWarps; ++kk) {
-                            const int k = mw * (kGrpSlabK / 16 / kGrpMmaWarps) + kk;
-                            const uint32_t baddr = xaddr + (k >> 2) * kGrpMaxN * 128 + (k & 3) * 32;
-                            const uint64_t bdesc = (uint64_t)((baddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-                                                   ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-                            const uint32_t acc = (s > 0 || kk > 0) ? 1u : 0u;
-                            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                                         ::"r"(tmem + kGrpDCol0 + (db * kGrpMmaWarps + mw) * kGrpMaxN), "r"(tmem + ab * kGrpACols + 8 * k), "l"(bdesc),
-                                         "r"(idesc), "r"(acc)
-                                         : "memory");
+                            for (int kk = 0; kk < kGrpSlabK / 16 / kGrpMmaWarps; ++kk) {
+                                const int k = mw * (kGrpSlabK / 16 / kGrpMmaWarps) + kk;
+                                const uint32_t baddr = xaddr + (k >> 2) * kGrpMaxN * 128 + (k & 3) * 32;
+                                const uint64_t bdesc = (uint64_t)((baddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+                                                       ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+                                const uint32_t acc = (s > 0 || kk > 0) ? 1u : 0u;
+                                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                                             ::"r"(tmem + kGrpDCol0 + (db * kGrpMmaWarps + mw) * kGrpMaxN), "r"(tmem + ab * kGrpACols + 8 * k), "l"(bdesc),
+                                             "r"(idesc), "r"(acc)
+                                             : "memory");
+                            }
                         }
                         umma_commit(a_empty + ab);
-                        if (s == nslab - 1) umma_commit(d_full + db);
+                        if (s == nslab - 1)
+                            for (int g = 0; g < ng; ++g) umma_commit(d_full + ((pc + g) & 1));
                     }
                     __syncwarp();
                 }
+                pc += ng;
             }
         }
         if (!ok && lane == 0) flag(a.status, kStatusTimeout);
@@ -373,7 +388,7 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
         int it = 0;
         Unit t;
         while (ok && walk.next(t)) {
-            const int total = ((t.n_tok + kGrpMaxN - 1) / kGrpMaxN) * nslab;
+            const int total = grp_double_passes(t.n_tok) * nslab;
             // a warp whose 32 rows all lie beyond the tile's last row has nothing to convert: its lanes of the
             // accumulator are never read
             const bool work = first_row < t.rows;
