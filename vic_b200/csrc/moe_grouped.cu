@@ -314,11 +314,13 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
                     const int xs = it % kGrpXStages;
                     if (it >= kGrpXStages) ok = mbar_wait_hint(a_empty + xs, ((it / kGrpXStages) - 1) & 1);
                     if (!ok) break;
-                    if (lane == 0) mbar_expect_tx(xfull + xs, ng * kGrpXGroupBytes);
-                    __syncwarp();
-                    if (lane < ng)   // one instruction for both groups' copies
-                        tma_load_3d(xring + (size_t)xs * kGrpXBytes + lane * kGrpXGroupBytes, xmap, 0, t.pair_off + p0 + lane * kGrpMaxN,
-                                    s * (kGrpSlabK / 64), xfull + xs);
+                    if (lane == 0) {
+                        mbar_expect_tx(xfull + xs, ng * kGrpXGroupBytes);
+                        tma_load_3d(xring + (size_t)xs * kGrpXBytes, xmap, 0, t.pair_off + p0, s * (kGrpSlabK / 64), xfull + xs);
+                        if (ng == 2)
+                            tma_load_3d(xring + (size_t)xs * kGrpXBytes + kGrpXGroupBytes, xmap, 0, t.pair_off + p0 + kGrpMaxN,
+                                        s * (kGrpSlabK / 64), xfull + xs);
+                    }
                     __syncwarp();
                 }
             }
@@ -346,7 +348,9 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
-                        for (int g = 0; g < ng; ++g) {
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) {
+                            if (g >= ng) break;
                             const int db = (pc + g) & 1;
                             const uint32_t xaddr = smem_u32(xring + (size_t)xs * kGrpXBytes + g * kGrpXGroupBytes);
 #pragma unroll
@@ -363,8 +367,10 @@ __global__ void __launch_bounds__(kGrpThreads, 1) moe_grouped_kernel(const __gri
                             }
                         }
                         umma_commit(a_empty + ab);
-                        if (s == nslab - 1)
-                            for (int g = 0; g < ng; ++g) umma_commit(d_full + ((pc + g) & 1));
+                        if (s == nslab - 1) {
+                            umma_commit(d_full + (pc & 1));
+                            if (ng == 2) umma_commit(d_full + ((pc + 1) & 1));
+                        }
                     }
                     __syncwarp();
                 }
